@@ -1,0 +1,351 @@
+/*
+ * raf_b200 - C ABI of the B200-native ZeRO optimizer step for RAF's operator API.
+ *
+ * One shared library (libraf_b200.so) exports everything below with C linkage,
+ * plain pointers and sizes.  A RAF dialect (an OpEnv per operator, see
+ * raf_b200/csrc/raf_dialect) forwards DLTensor::data pointers to these entry
+ * points; the Python mirror under raf_b200/ binds them with ctypes.
+ *
+ * Conventions
+ *   - every function returns a rafb200_status (0 = success); the message of
+ *     the last failure on the calling thread is rafb200_last_error().
+ *     Nothing in this library calls exit() or abort() (the reference's
+ *     NCCL_CALL does, include/raf/communicator.h:41-49).
+ *   - all device work is enqueued on the cudaStream_t the caller passes
+ *     (as `void*`, like the reference's OpEnv stream requests, include/raf/op.h:86-93);
+ *     no call synchronises the device unless its comment says so.
+ *   - step calls allocate nothing.  Objects (tensor lists, plans, communicators)
+ *     allocate their small device tables when they are created, which is the
+ *     moment the reference constructs an OpEnv (once per call site and shape).
+ *   - parameters, momenta and second moments are fp32.  Gradients may be
+ *     fp32 / fp16 / bf16; the optional parameter copy written for the
+ *     all-gather may be fp32 / fp16 / bf16.
+ *   - citations "file:line" refer to the awslabs/raf source tree.
+ */
+#ifndef RAF_B200_H_
+#define RAF_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RAFB200_API __attribute__((visibility("default")))
+
+typedef enum {
+  RAFB200_OK = 0,
+  RAFB200_INVALID_ARGUMENT = 1,
+  RAFB200_CUDA_ERROR = 2,
+  RAFB200_NCCL_ERROR = 3,
+  RAFB200_TIMEOUT = 4,          /* host-side deadline (rendezvous, communicator init) */
+  RAFB200_DEVICE_WAIT_EXPIRED = 5, /* a bounded wait inside a kernel gave up */
+  RAFB200_UNSUPPORTED = 6,
+  RAFB200_IO_ERROR = 7
+} rafb200_status;
+
+/* Element types.  The reference's DType codes for the same types are
+ * kDLFloat/32, kDLFloat/16 and kDLBfloat/16 (include/raf/device.h:27-36). */
+typedef enum { RAFB200_F32 = 0, RAFB200_F16 = 1, RAFB200_BF16 = 2 } rafb200_dtype;
+
+RAFB200_API const char* rafb200_last_error(void);
+RAFB200_API int rafb200_version(void);
+
+/* ------------------------------------------------------------------------- */
+/* Tensor lists                                                               */
+/* ------------------------------------------------------------------------- */
+/*
+ * A tensor list is the device-resident form of the `tensor_list` argument of
+ * raf.op.lans ([g..., p..., m..., v...], python/raf/optim/lans.py:267) and of
+ * the per-parameter (x, dx, v) triples of raf.op.sgd.  It replaces the
+ * reference's TensorListMetadata, which is rebuilt and passed by value on
+ * every launch (src/op/dialect/cuda/kernels/multi_tensor_apply.cuh:20-92):
+ * geometry (element counts, work items) is fixed at creation, pointers are
+ * (re)bound with rafb200_tensor_list_bind.
+ *
+ * numel[i] may be 0.  g_dtype is the dtype of every gradient, out_dtype of
+ * every optional parameter copy.
+ */
+typedef struct rafb200_tensor_list_s* rafb200_tensor_list_t;
+
+RAFB200_API int rafb200_tensor_list_create(int k, const int64_t* numel, int g_dtype, int out_dtype,
+                                           rafb200_tensor_list_t* list);
+/* Host arrays of k device pointers each.  m may be NULL for SGD without
+ * momentum state... it is required by every optimizer here (SGD: momentum
+ * buffer; Adam/LANS: first moment); v is required by Adam and LANS; out may
+ * be NULL (no parameter copy) or hold NULL entries.  The table is copied to
+ * the device on `stream` only when a pointer changed since the last bind. */
+RAFB200_API int rafb200_tensor_list_bind(rafb200_tensor_list_t list, const void* const* g,
+                                         float* const* p, float* const* m, float* const* v,
+                                         void* const* out, void* stream);
+RAFB200_API int rafb200_tensor_list_destroy(rafb200_tensor_list_t list);
+RAFB200_API int64_t rafb200_tensor_list_total_elems(rafb200_tensor_list_t list);
+
+/* Scheduling knobs of the LANS kernel for this list (see rafb200_lans):
+ * window_elems = how far (in elements) the norm pass may run ahead of the
+ * update pass so that the re-read hits L2; slack_items = work items placed
+ * between the last norm item of a tensor and its first update item;
+ * max_blocks = cap on the persistent grid (0 = fill the GPU), used to leave
+ * SMs to a concurrent collective.  Defaults are chosen at creation. */
+RAFB200_API int rafb200_tensor_list_tune(rafb200_tensor_list_t list, int64_t window_elems,
+                                         int slack_items, int max_blocks);
+
+/* ------------------------------------------------------------------------- */
+/* Optimizer updates (shard-local)                                            */
+/* ------------------------------------------------------------------------- */
+/*
+ * raf.op.sgd  - schema SgdArgs{x, dx, v, learning_rate, mu}
+ *   (scripts/src_codegen/def_schema.py:671-677; compute python/raf/_tvm_op/sgd.py:13-33;
+ *    the traced chain multiply/add/multiply/subtract of python/raf/optim/sgd.py:198-201):
+ *       v1 = mu*v0 + dx ;  x1 = x0 - learning_rate*v1
+ *   evaluated in fp32 without fused multiply-add, in place on x and v.
+ * Fused neighbours (no counterpart inside the reference op; pass the neutral
+ * value to get the reference op exactly):
+ *   grad_scale   dx is multiplied by it first (1/loss_scale, 1/n after a sum
+ *                reduce-scatter; replaces the `divide` of partition_gradient.cc:274-279)
+ *   weight_decay dx += weight_decay*x0 (torch.optim.SGD convention; 0 = reference)
+ *   dx_dtype     fp16/bf16 gradients are widened on load (the cast of sgd.py:193-195)
+ *   out          receives cast(x1, out_dtype) (the cast of sgd.py:203-204 written
+ *                straight into the all-gather buffer); may be NULL.
+ */
+RAFB200_API int rafb200_sgd(float* x, const void* dx, int dx_dtype, float* v, int64_t numel,
+                            float learning_rate, float mu, float weight_decay, float grad_scale,
+                            void* out, int out_dtype, void* stream);
+/* The same update over a bound tensor list in ONE launch (x = p, v = m of the list). */
+RAFB200_API int rafb200_sgd_list(rafb200_tensor_list_t list, float learning_rate, float mu,
+                                 float weight_decay, float grad_scale, void* stream);
+
+/*
+ * raf.op.lans - schema LansArgs{tensor_list, step, learning_rate, beta1, beta2, eps,
+ *   bias_correction, weight_decay, grad_averaging, mode, normalize_grad}
+ *   (scripts/src_codegen/def_schema.py:678-694; host src/op/dialect/cuda/lans.cc:25-165;
+ *    kernels src/op/dialect/cuda/kernels/multi_tensor_lans.cu:95-450).
+ * Same argument meaning and per-element arithmetic (true divisions, sqrtf, no
+ * fused multiply-add).  Differences, all deliberate:
+ *   - one persistent launch instead of about fifty; per-tensor norms are
+ *     reduced warp-shuffle-then-block in the same kernel, in a fixed order
+ *     (bitwise reproducible run to run) that differs from the reference's
+ *     chunk/tree order: trust ratios agree to ~1e-7 relative;
+ *   - `step` is a host integer, or - when step_dev is not NULL - is read on the
+ *     device from a 0-d fp32 tensor as the reference schema has it, without the
+ *     blocking device-to-host copy of lans.cc:97-99;
+ *   - gradients may be 16-bit and grad_scale is applied on load (replaces
+ *     group_cast, python/raf/optim/lans.py:261-265); g is NOT overwritten
+ *     (the reference leaves update_m in it);
+ *   - `out` of the list receives cast(p_new) (python/raf/optim/lans.py:289-290);
+ *   - the scratch regions of different tensors never overlap (the reference's
+ *     q pointers do for three or more tensors, lans.cc:116-119).
+ * workspace: rafb200_lans_workspace_bytes(list) bytes of device memory owned
+ * by the caller (the reference requests its workspace the same way,
+ * lans.cc:66-78); contents need not be preserved between calls.
+ */
+RAFB200_API size_t rafb200_lans_workspace_bytes(rafb200_tensor_list_t list);
+RAFB200_API int rafb200_lans(rafb200_tensor_list_t list, int step, const float* step_dev,
+                             float learning_rate, float beta1, float beta2, float eps,
+                             int bias_correction, float weight_decay, int grad_averaging, int mode,
+                             int normalize_grad, float grad_scale, void* workspace,
+                             size_t workspace_bytes, void* stream);
+/* Synchronises `stream`, then reports whether the last rafb200_lans on this
+ * workspace completed (RAFB200_OK) or a bounded device wait expired.
+ * norms_host (optional, 4*k floats, tensor-major) receives
+ * ||g||, ||p||, ||update_m||, ||update_g|| of every tensor. */
+RAFB200_API int rafb200_lans_status(rafb200_tensor_list_t list, const void* workspace,
+                                    float* norms_host, void* stream);
+
+/*
+ * Adam / AdamW.  The reference has NO Adam operator; schema modelled on
+ * raf.op.lans, arithmetic = LANS stage 1 without gradient normalisation and
+ * trust ratios (multi_tensor_lans.cu:281-306):
+ *   mode 1: m=b1*m+(1-b1)*g; v=b2*v+(1-b2)*g*g; p -= lr*((m/bc1)/(sqrt(v/bc2)+eps) + wd*p)
+ *   mode 0: g += wd*p first, no decoupled term.
+ */
+RAFB200_API int rafb200_adam(rafb200_tensor_list_t list, int step, const float* step_dev,
+                             float learning_rate, float beta1, float beta2, float eps,
+                             int bias_correction, float weight_decay, int mode, float grad_scale,
+                             void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Casts and bucket packing                                                   */
+/* ------------------------------------------------------------------------- */
+/* raf.op.cast (src/op/declare/transform.cc:868-890): round to nearest even. */
+RAFB200_API int rafb200_cast(const void* src, int src_dtype, void* dst, int dst_dtype,
+                             int64_t numel, void* stream);
+/* raf.op.group_cast (src/op/declare/transform.cc:892-913): k tensors, one launch. */
+RAFB200_API int rafb200_group_cast(int k, const void* const* src, int src_dtype, void* const* dst,
+                                   int dst_dtype, const int64_t* numel, void* stream);
+/*
+ * raf.op.fuse_tensor / raf.op.defuse_tensor (src/op/dialect/cuda/memory.cc:20-134):
+ * concatenate k tensors into one flat buffer and back, one launch instead of
+ * one cudaMemcpyAsync per tensor.  offsets[i] is the element offset of tensor
+ * i inside the flat buffer; elem_size in bytes.
+ */
+RAFB200_API int rafb200_fuse_tensor(int k, const void* const* src, const int64_t* numel,
+                                    const int64_t* offsets, int elem_size, void* flat,
+                                    void* stream);
+RAFB200_API int rafb200_defuse_tensor(int k, void* const* dst, const int64_t* numel,
+                                      const int64_t* offsets, int elem_size, const void* flat,
+                                      void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Communicator and collectives                                               */
+/* ------------------------------------------------------------------------- */
+/*
+ * Replaces NCCLCommunicator::make (src/distributed/cuda/nccl_communicator.cc:75-161)
+ * for the global communicator.  The 128-byte NCCL id travels through a file
+ * store as in the reference (NCCLIdSyncHelper, :20-69; SimpleFileStore,
+ * src/distributed/cuda/nccl_utils.h:209-262): rank 0 writes
+ * <store_path>/<seq>, the others poll for it.  store_path NULL reads
+ * $RAF_FILE_STORE_PATH and falls back to /tmp/.raf_file_store.  Unlike the
+ * reference (3 s, then LOG(FATAL)) the deadline is a parameter and expiry is
+ * a returned RAFB200_TIMEOUT.  world_size 1 creates a communicator without
+ * NCCL whose collectives degenerate to copies (the reference's
+ * VoidCommunicator, src/distributed/common/communicator.cc:96-115).
+ * Sets the calling thread's current device to `device`.
+ */
+typedef struct rafb200_comm_s* rafb200_comm_t;
+
+RAFB200_API int rafb200_comm_create(int world_size, int rank, int device, const char* store_path,
+                                    int timeout_ms, rafb200_comm_t* comm);
+/* Same, with the id supplied by the caller (e.g. broadcast by its own launcher). */
+RAFB200_API int rafb200_unique_id(void* id128);
+RAFB200_API int rafb200_comm_create_with_id(int world_size, int rank, int device,
+                                            const void* id128, int timeout_ms,
+                                            rafb200_comm_t* comm);
+RAFB200_API int rafb200_comm_destroy(rafb200_comm_t comm);
+RAFB200_API int rafb200_comm_size(rafb200_comm_t comm);
+RAFB200_API int rafb200_comm_rank(rafb200_comm_t comm);
+/* Polls NCCL's asynchronous error state (the reference never does). */
+RAFB200_API int rafb200_comm_check(rafb200_comm_t comm);
+
+/*
+ * raf.op._allreduce / _reduce_scatter / _group_reduce_scatter / _allgather /
+ * _group_allgather (schemas scripts/src_codegen/def_schema.py:699-738; NCCL
+ * dialect src/op/dialect/nccl/nccl.cc:40-399).  `computation` is one of
+ * "sum", "prod", "min", "max", "avg" as in nccl.cc:57-72.  Counts are in
+ * elements.  dtype may be any rafb200_dtype (bf16 is an addition: the
+ * reference's map, communication_utils.h:31-48, has none).
+ * reduce_scatter: recvcount elements per rank, rank r receives block r of
+ * sendbuf (dim 0 split, src/op/declare/collective_comm.cc:112-158); in place
+ * when recvbuf == sendbuf + rank*recvcount.  allgather: in place when
+ * sendbuf == recvbuf + rank*sendcount.  The group forms issue all k
+ * collectives between ncclGroupStart/End (nccl.cc:231-242, :382-390).
+ */
+RAFB200_API int rafb200_allreduce(rafb200_comm_t comm, const void* sendbuf, void* recvbuf,
+                                  int64_t count, int dtype, const char* computation, void* stream);
+RAFB200_API int rafb200_reduce_scatter(rafb200_comm_t comm, const void* sendbuf, void* recvbuf,
+                                       int64_t recvcount, int dtype, const char* computation,
+                                       void* stream);
+RAFB200_API int rafb200_group_reduce_scatter(rafb200_comm_t comm, int k,
+                                             const void* const* sendbuf, void* const* recvbuf,
+                                             const int64_t* recvcount, int dtype,
+                                             const char* computation, void* stream);
+RAFB200_API int rafb200_allgather(rafb200_comm_t comm, const void* sendbuf, void* recvbuf,
+                                  int64_t sendcount, int dtype, void* stream);
+RAFB200_API int rafb200_group_allgather(rafb200_comm_t comm, int k, const void* const* sendbuf,
+                                        void* const* recvbuf, const int64_t* sendcount, int dtype,
+                                        void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* ZeRO plan: shard geometry and buckets                                      */
+/* ------------------------------------------------------------------------- */
+/*
+ * Restates what GradientPartitioner (src/pass/partition_gradient.cc:177-205,
+ * :241-330) and CommGrouper (src/pass/group_allgather.cc:60-160) decide at
+ * compile time, for k parameter tensors of shape (dim0[i], row_elems[i]):
+ *   shard rows   = ceil(dim0/n)  (python/raf/optim/utils.py:46-47;
+ *                  partition_gradient.cc:191-197), rank r owns rows
+ *                  [r*shard_rows, (r+1)*shard_rows) of the zero-padded tensor;
+ *   buckets      = consecutive tensors; a tensor joins the open bucket while
+ *                  open_elems + numel < bucket_elems (unpadded counts,
+ *                  partition_gradient.cc:289-300, group_allgather.cc:110-145);
+ *                  the last bucket is always flushed.
+ * Host-only: usable without a GPU.
+ */
+typedef struct rafb200_plan_s* rafb200_plan_t;
+
+RAFB200_API int rafb200_plan_create(int k, const int64_t* dim0, const int64_t* row_elems,
+                                    int n_ranks, int rank, int64_t bucket_elems,
+                                    rafb200_plan_t* plan);
+RAFB200_API int rafb200_plan_destroy(rafb200_plan_t plan);
+RAFB200_API int rafb200_plan_num_buckets(rafb200_plan_t plan);
+/* Per-tensor queries; arrays of k entries, any may be NULL. */
+RAFB200_API int rafb200_plan_query(rafb200_plan_t plan, int64_t* shard_rows, int64_t* shard_elems,
+                                   int64_t* padded_elems, int* bucket_of);
+/* Totals: unpadded, padded and per-rank shard element counts. */
+RAFB200_API int rafb200_plan_totals(rafb200_plan_t plan, int64_t* elems, int64_t* padded_elems,
+                                    int64_t* shard_elems);
+
+/* ------------------------------------------------------------------------- */
+/* ZeRO step                                                                  */
+/* ------------------------------------------------------------------------- */
+/*
+ * The op sequence the reference's ZeRO pass emits after backward
+ * (python/raf/optim/sgd.py:186-221, lans.py:230-313 after PartitionGradient
+ * and GroupAllgather), as one call:
+ *   per bucket:  [pad] -> grouped reduce-scatter of the local gradients
+ *                -> shard-local update (SGD-momentum / Adam / LANS) that also
+ *                   writes the model-dtype parameter block in place into the
+ *                   all-gather destination
+ *                -> grouped all-gather of the parameter blocks [-> slice]
+ * with the collectives on `comm_stream`, the updates on `compute_stream`, and
+ * events between them so that bucket b+1's reduce-scatter and bucket b-1's
+ * all-gather overlap bucket b's update (the discipline EnforceSync encodes,
+ * src/pass/enforce_sync.cc:45-68: compute stream 1, communication stream 4).
+ *
+ * Buffers (all device memory owned by the caller, k entries each):
+ *   grads[i]   local gradient of tensor i, dim0 x row_elems, g_dtype.  It is
+ *              reduced IN PLACE: after the step rank r's row block holds the
+ *              reduced shard, the rest is unspecified.
+ *   params[i]  full model parameter, dim0 x row_elems, param_dtype: the
+ *              all-gather destination.
+ *   p/m/v[i]   fp32 master shard and optimizer state, shard_elems[i] each.
+ * Tensors whose dim0 does not divide by n are staged through padded buffers
+ * the state object owns (raf.op.pad before, strided_slice after).
+ */
+typedef enum { RAFB200_OPT_SGD = 0, RAFB200_OPT_ADAM = 1, RAFB200_OPT_LANS = 2 } rafb200_optimizer;
+
+typedef struct {
+  int optimizer;        /* rafb200_optimizer */
+  float learning_rate;
+  float mu;             /* SGD momentum */
+  float beta1, beta2, eps;
+  float weight_decay;
+  int bias_correction;  /* Adam / LANS */
+  int grad_averaging;   /* LANS */
+  int mode;             /* Adam / LANS: 0 = L2, 1 = decoupled */
+  int normalize_grad;   /* LANS */
+  float grad_scale;     /* extra gradient scale (1/loss_scale); the 1/n of a mean is added internally */
+  int average;          /* 1: gradients are averaged over ranks ("avg"), 0: summed */
+} rafb200_hyper;
+
+typedef struct rafb200_zero_s* rafb200_zero_t;
+
+RAFB200_API int rafb200_zero_create(rafb200_plan_t plan, rafb200_comm_t comm, int g_dtype,
+                                    int param_dtype, int optimizer, rafb200_zero_t* zero);
+RAFB200_API int rafb200_zero_destroy(rafb200_zero_t zero);
+RAFB200_API int rafb200_zero_bind(rafb200_zero_t zero, void* const* grads, void* const* params,
+                                  float* const* p, float* const* m, float* const* v);
+/* Enqueues one step; returns without waiting.  On return of the call the
+ * compute stream has been made to wait for the last all-gather. */
+RAFB200_API int rafb200_zero_step(rafb200_zero_t zero, const rafb200_hyper* hyper, int step,
+                                  void* compute_stream, void* comm_stream);
+/* Kernel launches and NCCL calls one step enqueues (for accounting). */
+RAFB200_API int rafb200_zero_launch_counts(rafb200_zero_t zero, int* kernels, int* collectives);
+/* Cap on the persistent update grids while collectives are in flight (0 = no cap). */
+RAFB200_API int rafb200_zero_set_update_blocks(rafb200_zero_t zero, int max_blocks);
+
+/* ------------------------------------------------------------------------- */
+/* Host-buffer convenience: one optimizer step with the gradients in host      */
+/* memory and the updated model-dtype parameters read back, the form a         */
+/* caller without device buffers (a CPU executor) would use.  Copies run on    */
+/* `stream`; pinned host memory makes them asynchronous.                       */
+/* ------------------------------------------------------------------------- */
+RAFB200_API int rafb200_zero_step_host(rafb200_zero_t zero, const rafb200_hyper* hyper, int step,
+                                       const void* const* grads_host, void* const* params_host,
+                                       void* compute_stream, void* comm_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RAF_B200_H_ */

@@ -1,0 +1,342 @@
+// Communicator lifecycle and the collective entry points.
+//
+// One process per GPU.  The global communicator is an NCCL communicator whose
+// 128-byte id is published by rank 0 through a file store, as the reference
+// does when no MPI is present (src/distributed/cuda/nccl_communicator.cc:20-69),
+// or handed in by the caller.  Differences from the reference, all on the
+// failure path: the id exchange and ncclCommInitRank have a host-side deadline
+// (the latter runs on a helper thread that is abandoned when the deadline
+// passes), errors are returned instead of exit(), and rafb200_comm_check polls
+// NCCL's asynchronous error state.
+#include <nccl.h>
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <chrono>
+#include <cstdlib>
+#include <cstring>
+#include <condition_variable>
+#include <memory>
+#include <mutex>
+#include <thread>
+
+#include "common.h"
+
+struct rafb200_comm_s {
+  int size = 1;
+  int rank = 0;
+  int device = 0;
+  bool is_void = true;  // world of one: no NCCL underneath
+  ncclComm_t nccl = nullptr;
+  std::string store_file;  // file this rank published (removed on destroy)
+};
+
+namespace rafb200 {
+
+using Clock = std::chrono::steady_clock;
+
+static int nccl_fail(ncclResult_t r, const char* what) {
+  return set_error(RAFB200_NCCL_ERROR, "%s: %s", what, ncclGetErrorString(r));
+}
+
+#define RAFB200_NCCL(comm, expr)                       \
+  do {                                                 \
+    ncclResult_t r__ = (expr);                         \
+    if (r__ != ncclSuccess) return nccl_fail(r__, #expr); \
+  } while (0)
+
+static int to_nccl_dtype(int dtype, ncclDataType_t* out) {
+  switch (dtype) {
+    case RAFB200_F32: *out = ncclFloat32; return RAFB200_OK;
+    case RAFB200_F16: *out = ncclFloat16; return RAFB200_OK;
+    case RAFB200_BF16: *out = ncclBfloat16; return RAFB200_OK;
+  }
+  return set_error(RAFB200_INVALID_ARGUMENT, "unsupported dtype %d", dtype);
+}
+
+// "sum" | "prod" | "min" | "max" | "avg"  (src/op/dialect/nccl/nccl.cc:57-72)
+static int to_nccl_op(const char* computation, ncclRedOp_t* out) {
+  if (!computation) return set_error(RAFB200_INVALID_ARGUMENT, "NULL computation");
+  if (!strcmp(computation, "sum")) *out = ncclSum;
+  else if (!strcmp(computation, "prod")) *out = ncclProd;
+  else if (!strcmp(computation, "min")) *out = ncclMin;
+  else if (!strcmp(computation, "max")) *out = ncclMax;
+  else if (!strcmp(computation, "avg")) *out = ncclAvg;
+  else return set_error(RAFB200_INVALID_ARGUMENT, "Invalid computation %s", computation);
+  return RAFB200_OK;
+}
+
+// ---- file store ---------------------------------------------------------------
+static std::atomic<int> g_store_seq{0};
+
+static std::string store_dir(const char* store_path) {
+  if (store_path && *store_path) return store_path;
+  const char* env = getenv("RAF_FILE_STORE_PATH");
+  if (env && *env) return env;
+  return "/tmp/.raf_file_store";
+}
+
+static int store_publish(const std::string& file, const void* data, size_t n) {
+  const std::string tmp = file + ".tmp." + std::to_string((long)getpid());
+  int fd = ::open(tmp.c_str(), O_WRONLY | O_CREAT | O_TRUNC, 0644);
+  if (fd < 0) return set_error(RAFB200_IO_ERROR, "cannot create %s: %s", tmp.c_str(), strerror(errno));
+  ssize_t w = ::write(fd, data, n);
+  ::close(fd);
+  if (w != (ssize_t)n) {
+    ::unlink(tmp.c_str());
+    return set_error(RAFB200_IO_ERROR, "short write to %s", tmp.c_str());
+  }
+  if (::rename(tmp.c_str(), file.c_str()) != 0) {  // atomic: readers see nothing or all of it
+    ::unlink(tmp.c_str());
+    return set_error(RAFB200_IO_ERROR, "cannot publish %s: %s", file.c_str(), strerror(errno));
+  }
+  return RAFB200_OK;
+}
+
+static int store_fetch(const std::string& file, void* data, size_t n, int timeout_ms) {
+  const auto deadline = Clock::now() + std::chrono::milliseconds(timeout_ms);
+  while (true) {
+    int fd = ::open(file.c_str(), O_RDONLY);
+    if (fd >= 0) {
+      ssize_t r = ::read(fd, data, n);
+      ::close(fd);
+      if (r == (ssize_t)n) return RAFB200_OK;
+    }
+    if (Clock::now() > deadline)
+      return set_error(RAFB200_TIMEOUT, "no communicator id at %s after %d ms", file.c_str(),
+                       timeout_ms);
+    std::this_thread::sleep_for(std::chrono::milliseconds(10));  // nccl_utils.h:247
+  }
+}
+
+// ncclCommInitRank blocks until every rank has joined.  It runs on a helper
+// thread so that a peer that never arrives costs `timeout_ms`, not forever; a
+// helper that is still blocked at the deadline is left behind (it owns its
+// state through the shared_ptr) and the caller gets RAFB200_TIMEOUT.
+struct InitState {
+  std::mutex mu;
+  std::condition_variable cv;
+  bool done = false;
+  ncclResult_t result = ncclSuccess;
+  ncclComm_t comm = nullptr;
+};
+
+static int init_rank(rafb200_comm_s* c, const ncclUniqueId& id, int timeout_ms) {
+  auto st = std::make_shared<InitState>();
+  const int size = c->size, rank = c->rank, device = c->device;
+  std::thread([st, id, size, rank, device]() {
+    ncclComm_t comm = nullptr;
+    ncclResult_t r = ncclSuccess;
+    if (cudaSetDevice(device) != cudaSuccess) r = ncclUnhandledCudaError;
+    if (r == ncclSuccess) r = ncclCommInitRank(&comm, size, id, rank);
+    std::lock_guard<std::mutex> lk(st->mu);
+    st->result = r;
+    st->comm = comm;
+    st->done = true;
+    st->cv.notify_all();
+  }).detach();
+  std::unique_lock<std::mutex> lk(st->mu);
+  if (!st->cv.wait_for(lk, std::chrono::milliseconds(timeout_ms), [&] { return st->done; }))
+    return set_error(RAFB200_TIMEOUT, "ncclCommInitRank: not every rank joined within %d ms",
+                     timeout_ms);
+  if (st->result != ncclSuccess) return nccl_fail(st->result, "ncclCommInitRank");
+  c->nccl = st->comm;
+  return RAFB200_OK;
+}
+
+}  // namespace rafb200
+
+using namespace rafb200;
+
+extern "C" {
+
+int rafb200_unique_id(void* id128) {
+  RAFB200_REQUIRE(id128, "rafb200_unique_id: NULL buffer");
+  static_assert(sizeof(ncclUniqueId) == 128, "NCCL id is 128 bytes");
+  ncclUniqueId id;
+  ncclResult_t r = ncclGetUniqueId(&id);
+  if (r != ncclSuccess) return nccl_fail(r, "ncclGetUniqueId");
+  memcpy(id128, &id, sizeof(id));
+  return RAFB200_OK;
+}
+
+int rafb200_comm_create_with_id(int world_size, int rank, int device, const void* id128,
+                                int timeout_ms, rafb200_comm_t* comm) {
+  RAFB200_REQUIRE(comm, "rafb200_comm_create: NULL result pointer");
+  *comm = nullptr;
+  RAFB200_REQUIRE(world_size >= 1 && rank >= 0 && rank < world_size,
+                  "rafb200_comm_create: rank %d outside world of %d", rank, world_size);
+  RAFB200_REQUIRE(timeout_ms > 0, "rafb200_comm_create: timeout must be positive");
+  RAFB200_CUDA(cudaSetDevice(device));
+  auto* c = new rafb200_comm_s();
+  c->size = world_size;
+  c->rank = rank;
+  c->device = device;
+  if (world_size > 1) {
+    if (!id128) {
+      delete c;
+      return set_error(RAFB200_INVALID_ARGUMENT, "rafb200_comm_create: NULL id");
+    }
+    c->is_void = false;
+    ncclUniqueId id;
+    memcpy(&id, id128, sizeof(id));
+    int rc = init_rank(c, id, timeout_ms);
+    if (rc != RAFB200_OK) {
+      delete c;
+      return rc;
+    }
+  }
+  *comm = c;
+  return RAFB200_OK;
+}
+
+int rafb200_comm_create(int world_size, int rank, int device, const char* store_path,
+                        int timeout_ms, rafb200_comm_t* comm) {
+  RAFB200_REQUIRE(comm, "rafb200_comm_create: NULL result pointer");
+  *comm = nullptr;
+  RAFB200_REQUIRE(world_size >= 1 && rank >= 0 && rank < world_size,
+                  "rafb200_comm_create: rank %d outside world of %d", rank, world_size);
+  RAFB200_REQUIRE(timeout_ms > 0, "rafb200_comm_create: timeout must be positive");
+  if (world_size == 1) return rafb200_comm_create_with_id(1, 0, device, nullptr, timeout_ms, comm);
+
+  const std::string dir = store_dir(store_path);
+  ::mkdir(dir.c_str(), 0777);  // nccl_communicator.cc:28-33; fine if it exists
+  const int seq = ++g_store_seq;  // every rank creates its communicators in the same order
+  const std::string file = dir + "/" + std::to_string(seq);
+  ncclUniqueId id;
+  if (rank == 0) {
+    ncclResult_t r = ncclGetUniqueId(&id);
+    if (r != ncclSuccess) return nccl_fail(r, "ncclGetUniqueId");
+    int rc = store_publish(file, &id, sizeof(id));
+    if (rc != RAFB200_OK) return rc;
+  } else {
+    int rc = store_fetch(file, &id, sizeof(id), timeout_ms);
+    if (rc != RAFB200_OK) return rc;
+  }
+  int rc = rafb200_comm_create_with_id(world_size, rank, device, &id, timeout_ms, comm);
+  if (rank == 0) {
+    if (rc == RAFB200_OK) (*comm)->store_file = file;  // every rank has joined: safe to remove later
+    else ::unlink(file.c_str());
+  }
+  return rc;
+}
+
+int rafb200_comm_destroy(rafb200_comm_t c) {
+  if (!c) return RAFB200_OK;
+  int rc = RAFB200_OK;
+  if (c->nccl) {
+    ncclResult_t r = ncclCommDestroy(c->nccl);
+    if (r != ncclSuccess) rc = nccl_fail(r, "ncclCommDestroy");
+  }
+  if (!c->store_file.empty()) ::unlink(c->store_file.c_str());
+  delete c;
+  return rc;
+}
+
+int rafb200_comm_size(rafb200_comm_t c) { return c ? c->size : 0; }
+int rafb200_comm_rank(rafb200_comm_t c) { return c ? c->rank : -1; }
+
+int rafb200_comm_check(rafb200_comm_t c) {
+  RAFB200_REQUIRE(c, "rafb200_comm_check: NULL communicator");
+  if (c->is_void) return RAFB200_OK;
+  ncclResult_t st = ncclSuccess;
+  ncclResult_t r = ncclCommGetAsyncError(c->nccl, &st);
+  if (r != ncclSuccess) return nccl_fail(r, "ncclCommGetAsyncError");
+  if (st != ncclSuccess) return nccl_fail(st, "asynchronous NCCL error");
+  return RAFB200_OK;
+}
+
+static int local_copy(const void* src, void* dst, size_t bytes, cudaStream_t s) {
+  if (src != dst && bytes)
+    RAFB200_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, s));
+  return RAFB200_OK;
+}
+
+int rafb200_allreduce(rafb200_comm_t c, const void* sendbuf, void* recvbuf, int64_t count,
+                      int dtype, const char* computation, void* stream) {
+  RAFB200_REQUIRE(c && count >= 0, "rafb200_allreduce: bad arguments");
+  ncclDataType_t dt;
+  ncclRedOp_t op;
+  int rc = to_nccl_dtype(dtype, &dt);
+  if (rc == RAFB200_OK) rc = to_nccl_op(computation, &op);
+  if (rc != RAFB200_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (c->is_void) return local_copy(sendbuf, recvbuf, (size_t)count * dtype_size(dtype), s);
+  RAFB200_NCCL(c, ncclAllReduce(sendbuf, recvbuf, (size_t)count, dt, op, c->nccl, s));
+  return RAFB200_OK;
+}
+
+int rafb200_group_reduce_scatter(rafb200_comm_t c, int k, const void* const* sendbuf,
+                                 void* const* recvbuf, const int64_t* recvcount, int dtype,
+                                 const char* computation, void* stream) {
+  RAFB200_REQUIRE(c && k >= 0 && (k == 0 || (sendbuf && recvbuf && recvcount)),
+                  "rafb200_group_reduce_scatter: bad arguments");
+  ncclDataType_t dt;
+  ncclRedOp_t op;
+  int rc = to_nccl_dtype(dtype, &dt);
+  if (rc == RAFB200_OK) rc = to_nccl_op(computation, &op);
+  if (rc != RAFB200_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (c->is_void) {
+    for (int i = 0; i < k; ++i) {
+      rc = local_copy(sendbuf[i], recvbuf[i], (size_t)recvcount[i] * dtype_size(dtype), s);
+      if (rc != RAFB200_OK) return rc;
+    }
+    return RAFB200_OK;
+  }
+  if (k == 0) return RAFB200_OK;
+  RAFB200_NCCL(c, ncclGroupStart());
+  for (int i = 0; i < k; ++i) {
+    ncclResult_t r = ncclReduceScatter(sendbuf[i], recvbuf[i], (size_t)recvcount[i], dt, op, c->nccl, s);
+    if (r != ncclSuccess) {
+      ncclGroupEnd();
+      return nccl_fail(r, "ncclReduceScatter");
+    }
+  }
+  RAFB200_NCCL(c, ncclGroupEnd());
+  return RAFB200_OK;
+}
+
+int rafb200_reduce_scatter(rafb200_comm_t c, const void* sendbuf, void* recvbuf,
+                           int64_t recvcount, int dtype, const char* computation, void* stream) {
+  return rafb200_group_reduce_scatter(c, 1, &sendbuf, &recvbuf, &recvcount, dtype, computation,
+                                      stream);
+}
+
+int rafb200_group_allgather(rafb200_comm_t c, int k, const void* const* sendbuf,
+                            void* const* recvbuf, const int64_t* sendcount, int dtype,
+                            void* stream) {
+  RAFB200_REQUIRE(c && k >= 0 && (k == 0 || (sendbuf && recvbuf && sendcount)),
+                  "rafb200_group_allgather: bad arguments");
+  ncclDataType_t dt;
+  int rc = to_nccl_dtype(dtype, &dt);
+  if (rc != RAFB200_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (c->is_void) {
+    for (int i = 0; i < k; ++i) {
+      rc = local_copy(sendbuf[i], recvbuf[i], (size_t)sendcount[i] * dtype_size(dtype), s);
+      if (rc != RAFB200_OK) return rc;
+    }
+    return RAFB200_OK;
+  }
+  if (k == 0) return RAFB200_OK;
+  RAFB200_NCCL(c, ncclGroupStart());
+  for (int i = 0; i < k; ++i) {
+    ncclResult_t r = ncclAllGather(sendbuf[i], recvbuf[i], (size_t)sendcount[i], dt, c->nccl, s);
+    if (r != ncclSuccess) {
+      ncclGroupEnd();
+      return nccl_fail(r, "ncclAllGather");
+    }
+  }
+  RAFB200_NCCL(c, ncclGroupEnd());
+  return RAFB200_OK;
+}
+
+int rafb200_allgather(rafb200_comm_t c, const void* sendbuf, void* recvbuf, int64_t sendcount,
+                      int dtype, void* stream) {
+  return rafb200_group_allgather(c, 1, &sendbuf, &recvbuf, &sendcount, dtype, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,155 @@
+// Chunk-level building blocks shared by the SGD / Adam kernels and the LANS
+// persistent kernel: a block of kBlockThreads threads walks one chunk
+// (<= kChunkElems elements of one tensor) with 16-byte accesses, two vector
+// passes in flight per thread, and falls back to scalar accesses for unaligned
+// tensors and ragged tails.
+#pragma once
+#include "common.h"
+#include "vec_io.cuh"
+
+namespace rafb200 {
+
+constexpr int kVec = 4;                              // elements per thread per pass
+constexpr int kPassElems = kBlockThreads * kVec;     // 1024
+constexpr int kUnroll = 2;                           // passes in flight
+constexpr uint32_t kFlagAligned = 1u;
+
+// ---- per-element arithmetic -------------------------------------------------
+// All three follow the reference expression by expression; see the C ABI
+// header for the citations.  Every operation is a separately rounded fp32 op.
+
+struct SgdOp {
+  float lr, mu, wd, gscale;
+  // v1 = mu*v0 + dx ; x1 = x0 - lr*v1      (python/raf/_tvm_op/sgd.py:21-29)
+  __device__ __forceinline__ void operator()(float g, float& p, float& m, float& /*v*/) const {
+    if (gscale != 1.0f) g = mul(g, gscale);
+    if (wd != 0.0f) g = add(g, mul(wd, p));
+    float v1 = add(mul(mu, m), g);
+    p = sub(p, mul(lr, v1));
+    m = v1;
+  }
+};
+
+struct AdamOp {
+  float lr, beta1, beta2, beta3, one_minus_beta2, eps, bc1, bc2, wd, gscale;
+  int mode;
+  __device__ __forceinline__ void operator()(float g, float& p, float& m, float& v) const {
+    if (gscale != 1.0f) g = mul(g, gscale);
+    if (mode == 0) g = add(g, mul(wd, p));
+    m = add(mul(m, beta1), mul(beta3, g));
+    v = add(mul(v, beta2), mul(mul(one_minus_beta2, g), g));
+    float denom = add(fsqrt(fdiv(v, bc2)), eps);
+    float update = fdiv(fdiv(m, bc1), denom);
+    if (mode != 0) update = add(update, mul(wd, p));
+    p = sub(p, mul(lr, update));
+  }
+};
+
+// LANS stage 1 (src/op/dialect/cuda/kernels/multi_tensor_lans.cu:281-306).
+struct LansStage1 {
+  float beta1, beta2, beta3, one_minus_beta2, eps, bc1, bc2, wd, gscale;
+  int mode, normalize;
+  // in: g (raw), p, m, v, gnorm   out: m, v updated; um, ug
+  __device__ __forceinline__ void operator()(float g, float p, float& m, float& v, float gnorm,
+                                             float& um, float& ug) const {
+    if (gscale != 1.0f) g = mul(g, gscale);
+    float rp = (wd == 0.0f) ? 0.0f : p;  // :263-268
+    float sg = g;
+    if (normalize && gnorm != 0.0f) sg = fdiv(sg, add(gnorm, eps));
+    if (mode == 0) {
+      sg = add(sg, mul(wd, rp));
+      m = add(mul(m, beta1), mul(beta3, sg));
+      v = add(mul(v, beta2), mul(mul(one_minus_beta2, sg), sg));
+      float denom = add(fsqrt(fdiv(v, bc2)), eps);
+      um = fdiv(fdiv(m, bc1), denom);
+      ug = fdiv(sg, denom);
+    } else {
+      m = add(mul(m, beta1), mul(beta3, sg));
+      v = add(mul(v, beta2), mul(mul(one_minus_beta2, sg), sg));
+      float denom = add(fsqrt(fdiv(v, bc2)), eps);
+      float sp = mul(wd, rp);
+      um = add(fdiv(fdiv(m, bc1), denom), sp);
+      ug = add(fdiv(sg, denom), sp);
+    }
+  }
+};
+
+// ---- chunk walkers ------------------------------------------------------------
+struct ChunkView {
+  const void* g;
+  float* p;
+  float* m;
+  float* v;
+  void* out;
+  int len;       // elements in this chunk
+  bool aligned;  // vector path allowed
+};
+
+__device__ __forceinline__ ChunkView chunk_view(const TensorDesc& d, uint32_t chunk, int g_size,
+                                                int out_size) {
+  ChunkView c;
+  const int64_t start = (int64_t)chunk * kChunkElems;
+  const int64_t left = d.numel - start;
+  c.len = left < kChunkElems ? (int)left : kChunkElems;
+  c.g = static_cast<const char*>(d.g) + start * g_size;
+  c.p = d.p + start;
+  c.m = d.m + start;
+  c.v = d.v ? d.v + start : nullptr;
+  c.out = d.out ? static_cast<char*>(d.out) + start * out_size : nullptr;
+  c.aligned = (d.flags & kFlagAligned) != 0;
+  return c;
+}
+
+// Read-modify-write of p, m (and v when NSTATE == 2) over one chunk.
+template <int NSTATE, typename GT, typename OT, typename Op>
+__device__ __forceinline__ void update_chunk(const ChunkView& c, const Op& op,
+                                             const Policies& pol) {
+  const GT* g = static_cast<const GT*>(c.g);
+  OT* out = static_cast<OT*>(c.out);
+  const int tid = threadIdx.x;
+  int done = 0;
+  if (c.aligned) {
+    const int len4 = c.len & ~(kVec - 1);
+    for (int base = 0; base < len4; base += kUnroll * kPassElems) {
+      F4 rg[kUnroll], rp[kUnroll], rm[kUnroll], rv[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int e = base + u * kPassElems + tid * kVec;
+        if (e < len4) {
+          rg[u] = Elem<GT>::template load4<kStream>(g + e, pol);
+          rp[u] = Elem<float>::template load4<kStream>(c.p + e, pol);
+          rm[u] = Elem<float>::template load4<kStream>(c.m + e, pol);
+          if (NSTATE == 2) rv[u] = Elem<float>::template load4<kStream>(c.v + e, pol);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int e = base + u * kPassElems + tid * kVec;
+        if (e < len4) {
+#pragma unroll
+          for (int j = 0; j < kVec; ++j) {
+            float vv = NSTATE == 2 ? rv[u].x[j] : 0.f;
+            op(rg[u].x[j], rp[u].x[j], rm[u].x[j], vv);
+            if (NSTATE == 2) rv[u].x[j] = vv;
+          }
+          Elem<float>::template store4<kDefault>(c.p + e, rp[u], pol);
+          Elem<float>::template store4<kDefault>(c.m + e, rm[u], pol);
+          if (NSTATE == 2) Elem<float>::template store4<kDefault>(c.v + e, rv[u], pol);
+          if (out) Elem<OT>::template store4<kDefault>(out + e, rp[u], pol);
+        }
+      }
+    }
+    done = len4;
+  }
+  for (int e = done + tid; e < c.len; e += kBlockThreads) {
+    float gg = Elem<GT>::to_f32(g[e]);
+    float pp = c.p[e], mm = c.m[e], vv = NSTATE == 2 ? c.v[e] : 0.f;
+    op(gg, pp, mm, vv);
+    c.p[e] = pp;
+    c.m[e] = mm;
+    if (NSTATE == 2) c.v[e] = vv;
+    if (out) out[e] = Elem<OT>::from_f32(pp);
+  }
+}
+
+}  // namespace rafb200

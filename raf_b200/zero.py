@@ -1,0 +1,219 @@
+"""ZeRO plan and step driver bindings, and the parameter-shape tables of the
+benchmark workloads."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import OPT_ADAM, OPT_LANS, OPT_SGD, Hyper, check
+from .op import dtype_code, stream_ptr, torch_dtype
+
+
+def _dim0_row(shape) -> Tuple[int, int]:
+    shape = tuple(int(s) for s in shape)
+    if len(shape) == 0:
+        return 1, 1
+    row = 1
+    for s in shape[1:]:
+        row *= s
+    return shape[0], row
+
+
+class Plan:
+    """Shard geometry and buckets of a parameter list (host only; no GPU needed).
+
+    Follows GradientPartitioner / CommGrouper of the reference
+    (src/pass/partition_gradient.cc:177-205,289-300; src/pass/group_allgather.cc:110-145).
+    """
+
+    def __init__(self, shapes: Sequence[Sequence[int]], n_ranks: int, rank: int, bucket_elems: int):
+        self.shapes = [tuple(int(x) for x in s) for s in shapes]
+        self.k = len(self.shapes)
+        self.n_ranks, self.rank, self.bucket_elems = n_ranks, rank, bucket_elems
+        d0r = [_dim0_row(s) for s in self.shapes]
+        h = C.c_void_p()
+        lib = _lib.load()
+        check(lib.rafb200_plan_create(self.k, _lib.i64_array([d for d, _ in d0r]),
+                                      _lib.i64_array([r for _, r in d0r]), n_ranks, rank,
+                                      int(bucket_elems), C.byref(h)))
+        self.handle = h
+        rows = np.zeros(self.k, np.int64)
+        elems = np.zeros(self.k, np.int64)
+        padded = np.zeros(self.k, np.int64)
+        bucket = np.zeros(self.k, np.int32)
+        check(lib.rafb200_plan_query(h, rows.ctypes.data, elems.ctypes.data, padded.ctypes.data,
+                                     bucket.ctypes.data))
+        self.shard_rows, self.shard_elems, self.padded_elems, self.bucket_of = rows, elems, padded, bucket
+        self.num_buckets = lib.rafb200_plan_num_buckets(h)
+        a, b, c = C.c_int64(), C.c_int64(), C.c_int64()
+        check(lib.rafb200_plan_totals(h, C.byref(a), C.byref(b), C.byref(c)))
+        self.total_elems, self.total_padded, self.total_shard = a.value, b.value, c.value
+
+    def shard_shape(self, i: int) -> Tuple[int, ...]:
+        s = self.shapes[i]
+        return (int(self.shard_rows[i]),) + s[1:] if len(s) else (1,)
+
+    def close(self):
+        if self.handle:
+            _lib.load().rafb200_plan_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def make_hyper(optimizer: str, **kw) -> Hyper:
+    opt = {"sgd": OPT_SGD, "adam": OPT_ADAM, "lans": OPT_LANS}[optimizer]
+    h = Hyper()
+    h.optimizer = opt
+    h.learning_rate = kw.get("learning_rate", kw.get("lr", 1e-3))
+    h.mu = kw.get("mu", kw.get("momentum", 0.0))
+    h.beta1 = kw.get("beta1", 0.9)
+    h.beta2 = kw.get("beta2", 0.999)
+    h.eps = kw.get("eps", 1e-6)
+    h.weight_decay = kw.get("weight_decay", 0.0)
+    h.bias_correction = int(kw.get("bias_correction", 1))
+    h.grad_averaging = int(kw.get("grad_averaging", 1))
+    h.mode = int(kw.get("mode", 1))
+    h.normalize_grad = int(kw.get("normalize_grad", 1))
+    h.grad_scale = kw.get("grad_scale", 1.0)
+    h.average = int(kw.get("average", 1))
+    return h
+
+
+class ZeroStep:
+    """reduce-scatter -> shard update -> all-gather over a Plan (rafb200_zero_*)."""
+
+    def __init__(self, plan: Plan, comm, g_dtype, param_dtype, optimizer: str):
+        self.plan, self.comm = plan, comm
+        self.g_dtype, self.param_dtype = torch_dtype(g_dtype), torch_dtype(param_dtype)
+        self.optimizer = optimizer
+        h = C.c_void_p()
+        opt = {"sgd": OPT_SGD, "adam": OPT_ADAM, "lans": OPT_LANS}[optimizer]
+        check(_lib.load().rafb200_zero_create(plan.handle, comm.handle, dtype_code(self.g_dtype),
+                                              dtype_code(self.param_dtype), opt, C.byref(h)))
+        self.handle = h
+        self._keep = None
+
+    def bind(self, grads, params, p, m, v=None):
+        pa = _lib.ptr_array
+        for ts, dt in ((grads, self.g_dtype), (params, self.param_dtype), (p, torch.float32),
+                       (m, torch.float32), (v, torch.float32)):
+            if ts is None:
+                continue
+            assert len(ts) == self.plan.k
+            for t in ts:
+                assert t.is_cuda and t.is_contiguous() and t.dtype == dt, (t.dtype, dt)
+        check(_lib.load().rafb200_zero_bind(
+            self.handle, pa([t.data_ptr() for t in grads]), pa([t.data_ptr() for t in params]),
+            pa([t.data_ptr() for t in p]), pa([t.data_ptr() for t in m]),
+            pa([t.data_ptr() for t in v]) if v is not None else None))
+        self._keep = (grads, params, p, m, v)
+
+    def step(self, hyper: Hyper, step: int, compute_stream=None, comm_stream=None):
+        from .distributed import comm_stream as default_comm_stream
+
+        cs = compute_stream if compute_stream is not None else torch.cuda.current_stream()
+        ms = comm_stream if comm_stream is not None else default_comm_stream()
+        check(_lib.load().rafb200_zero_step(self.handle, C.byref(hyper), int(step), cs.cuda_stream,
+                                            ms.cuda_stream))
+
+    def step_host(self, hyper: Hyper, step: int, grads_host, params_host, compute_stream=None,
+                  comm_stream=None):
+        """Host-buffer form: gradients come from (pinned) host tensors, the updated
+        model-dtype parameters are copied back into host tensors."""
+        from .distributed import comm_stream as default_comm_stream
+
+        cs = compute_stream if compute_stream is not None else torch.cuda.current_stream()
+        ms = comm_stream if comm_stream is not None else default_comm_stream()
+        pa = _lib.ptr_array
+        check(_lib.load().rafb200_zero_step_host(
+            self.handle, C.byref(hyper), int(step), pa([t.data_ptr() for t in grads_host]),
+            pa([t.data_ptr() for t in params_host]), cs.cuda_stream, ms.cuda_stream))
+
+    def launch_counts(self) -> Tuple[int, int]:
+        a, b = C.c_int(), C.c_int()
+        check(_lib.load().rafb200_zero_launch_counts(self.handle, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def set_update_blocks(self, max_blocks: int):
+        check(_lib.load().rafb200_zero_set_update_blocks(self.handle, int(max_blocks)))
+
+    def close(self):
+        if self.handle:
+            torch.cuda.synchronize()
+            _lib.load().rafb200_zero_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# --------------------------------------------------------------------------- workloads
+def resnet50_shapes() -> List[Tuple[int, ...]]:
+    """161 parameter tensors, 25,557,032 elements: conv weights O x I x k x k, a
+    (gamma, beta) pair after every conv, fc 1000 x 2048 + bias."""
+    shapes: List[Tuple[int, ...]] = []
+
+    def conv_bn(o, i, k):
+        shapes.append((o, i, k, k))
+        shapes.append((o,))
+        shapes.append((o,))
+
+    conv_bn(64, 3, 7)
+    inplanes = 64
+    for planes, blocks in ((64, 3), (128, 4), (256, 6), (512, 3)):
+        for b in range(blocks):
+            conv_bn(planes, inplanes, 1)
+            conv_bn(planes, planes, 3)
+            conv_bn(planes * 4, planes, 1)
+            if b == 0:
+                conv_bn(planes * 4, inplanes, 1)  # downsample
+            inplanes = planes * 4
+    shapes.append((1000, 2048))
+    shapes.append((1000,))
+    return shapes
+
+
+def bert_large_shapes() -> List[Tuple[int, ...]]:
+    """391 tensors, 335,141,888 elements (24 layers, hidden 1024, FFN 4096, vocab 30522)."""
+    h, ffn = 1024, 4096
+    shapes: List[Tuple[int, ...]] = [(30522, h), (512, h), (2, h), (h,), (h,)]
+    for _ in range(24):
+        for _ in range(4):
+            shapes += [(h, h), (h,)]
+        shapes += [(h,), (h,)]
+        shapes += [(ffn, h), (ffn,), (h, ffn), (h,)]
+        shapes += [(h,), (h,)]
+    shapes += [(h, h), (h,)]
+    return shapes
+
+
+def gpt2_medium_shapes() -> List[Tuple[int, ...]]:
+    """292 tensors, 354,823,168 elements (24 layers, d_model 1024, vocab 50257, ctx 1024)."""
+    d = 1024
+    shapes: List[Tuple[int, ...]] = [(50257, d), (1024, d)]
+    for _ in range(24):
+        shapes += [(d,), (d,)]
+        shapes += [(d, 3 * d), (3 * d,), (d, d), (d,)]
+        shapes += [(d,), (d,)]
+        shapes += [(d, 4 * d), (4 * d,), (4 * d, d), (d,)]
+    shapes += [(d,), (d,)]
+    return shapes
+
+
+def numel(shape) -> int:
+    n = 1
+    for s in shape:
+        n *= int(s)
+    return n
