@@ -62,13 +62,17 @@ constexpr int kChunkElems = 4096;  // elements per work item
 constexpr int kBlockThreads = 256;
 
 // Per-tensor control words of the LANS kernel (zeroed at the start of every call).
+// A norm word is "final" when its top bit is set: the publisher stores the bits of
+// the (non-negative) norm with the sign bit on, in one 4-byte store.  Validity and
+// value travel in the same word, so readers need no acquire ordering between a flag
+// and the data - a plain load that sees the bit sees the value.
 struct LansCtl {
   unsigned int arrived_a;  // chunks of phase A that have published their partial
   unsigned int arrived_b;
-  unsigned int ready_a;    // 1 once ||g|| is final
-  unsigned int ready_b;    // 1 once ||p||, ||update_m||, ||update_g|| are final
-  float norm[4];           // ||g||, ||p||, ||update_m||, ||update_g||
+  unsigned int pad_[2];
+  unsigned int norm[4];    // ||g||, ||p||, ||update_m||, ||update_g||: bits | 0x80000000 once final
 };
+constexpr unsigned int kNormValid = 0x80000000u;
 static_assert(sizeof(LansCtl) == 32, "LansCtl is 32 bytes");
 
 struct LansHeader {
@@ -76,6 +80,8 @@ struct LansHeader {
   unsigned int error;    // 0, or the code of the bounded wait that expired
   unsigned int error_item;
   unsigned int pad_;
+  float inv_bc1;         // reciprocal bias corrections when `step` lives on the device
+  float inv_bc2;
 };
 
 }  // namespace rafb200

@@ -7,8 +7,8 @@
 //   phase A  sum of squares of the (scaled) gradient chunk            -> ||g||
 //   phase B  stage 1 on the chunk, results NOT stored: sums of squares of
 //            p, update_m, update_g                                     -> norms
-//   phase C  stage 1 again (bit-identical), then stage 2 with the trust
-//            ratios; writes p, m, v and the model-dtype parameter copy.
+//   phase C  stage 1 again (same instructions, same bits), then stage 2 with the
+//            trust ratios; writes p, m, v and the model-dtype parameter copy.
 // Blocks draw items from a ticket counter in list order.  An item depends only
 // on items with smaller tickets (B of a tensor on all its A items, C on all its
 // B items), and a ticket is only ever held by a running block, so the bounded
@@ -22,6 +22,8 @@
 // Results are therefore bitwise reproducible run to run.
 #include <algorithm>
 #include <cmath>
+#include <cstring>
+#include <type_traits>
 
 #include "common.h"
 #include "update_core.cuh"
@@ -32,7 +34,7 @@ void bias_corrections(float beta1, float beta2, int step, int bias_correction, f
                       float* bc2);
 
 constexpr int kPhaseA = 0, kPhaseB = 1, kPhaseC = 2;
-constexpr unsigned kErrWaitA = 1, kErrWaitB = 2;
+constexpr unsigned kErrWaitA = 1, kErrWaitB = 2, kErrRing = 3;
 
 struct LansParams {
   const TensorDesc* descs;
@@ -47,21 +49,244 @@ struct LansParams {
   float lr;
   const float* step_dev;
   int bias_correction;
-  unsigned spin_limit;
+  uint64_t wait_ns;  // bound of every wait inside the kernel
+  unsigned long long* stats;  // development builds only (RAFB200_LANS_STATS): cycle counters
 };
 
-// Bounded wait for *flag != 0.  Returns false when it gave up (or another
-// block already reported an error).
-__device__ __forceinline__ bool wait_flag(const unsigned* flag, LansHeader* hdr, unsigned code,
-                                          uint32_t ticket, unsigned limit) {
-  unsigned spins = 0, ns = 32;
-  while (ld_acquire(flag) == 0) {
-    __nanosleep(ns);
-    if (ns < 1024) ns <<= 1;
-    ++spins;
-    if ((spins & 31u) == 0 && *reinterpret_cast<volatile unsigned*>(&hdr->error) != 0) return false;
-    if (spins > limit) {
-      if (atomicCAS(&hdr->error, 0u, code) == 0u) hdr->error_item = ticket;
+#ifdef RAFB200_LANS_STATS
+#define LANS_STAT_BEGIN() const long long stat_t0__ = clock64()
+#define LANS_STAT_END(acc) (acc) += (unsigned long long)(clock64() - stat_t0__)
+#else
+#define LANS_STAT_BEGIN() ((void)0)
+#define LANS_STAT_END(acc) ((void)0)
+#endif
+
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// The four norm words of a tensor, read with one relaxed 16-byte load.
+__device__ __forceinline__ uint4 ld_norms(const LansCtl* c) {
+  uint4 r;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(c->norm));
+  return r;
+}
+// B needs ||g|| (word 0), C needs ||p||, ||update_m||, ||update_g|| (words 1-3; they
+// are published together with, or after, word 0).
+__device__ __forceinline__ bool norms_final(const uint4& n, bool phase_c) {
+  return phase_c ? ((n.y & n.z & n.w) >> 31) != 0 : (n.x >> 31) != 0;
+}
+__device__ __forceinline__ float norm_value(unsigned bits) {
+  return __uint_as_float(bits & ~kNormValid);
+}
+
+// Bounded wait until the norms a phase needs are final: gives up after `wait_ns`
+// nanoseconds (or as soon as another block has reported an error) and returns false.
+__device__ __forceinline__ bool wait_norms(const LansCtl* c, bool phase_c, uint4* out,
+                                           LansHeader* hdr, unsigned code, uint32_t ticket,
+                                           uint64_t wait_ns) {
+  uint4 n = ld_norms(c);
+  if (!norms_final(n, phase_c)) {
+    const uint64_t t0 = global_ns();
+    unsigned spins = 0, ns = 32;
+    do {
+      __nanosleep(ns);
+      if (ns < 1024) ns <<= 1;
+      if ((++spins & 15u) == 0) {
+        if (*reinterpret_cast<volatile unsigned*>(&hdr->error) != 0) return false;
+        if (global_ns() - t0 > wait_ns) {
+          if (atomicCAS(&hdr->error, 0u, code) == 0u) hdr->error_item = ticket;
+          return false;
+        }
+      }
+      n = ld_norms(c);
+    } while (!norms_final(n, phase_c));
+  }
+  *out = n;
+  return true;
+}
+
+// `step` as a 0-d fp32 device tensor (python/raf/optim/lans.py:239): the bias
+// corrections of lans.cc:100-105 (float base, int exponent, evaluated in
+// double) are computed by one thread into the workspace header instead of
+// copying the step to the host.  Runs after the header was zeroed.
+__global__ void lans_bias_kernel(LansHeader* hdr, const float* step_dev, float beta1, float beta2,
+                                 int bias_correction) {
+  float bc1 = 1.0f, bc2 = 1.0f;
+  if (bias_correction == 1) {
+    const int step = (int)(*step_dev);
+    bc1 = (float)(1.0 - pow((double)beta1, (double)step));
+    bc2 = (float)(1.0 - pow((double)beta2, (double)step));
+  }
+  hdr->inv_bc1 = 1.0f / bc1;
+  hdr->inv_bc2 = 1.0f / bc2;
+}
+
+// ---- TMA / mbarrier primitives (sm_90+; written for sm_100a) -------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded: try_wait blocks for a short hardware-defined time per call; the loop
+// gives up after `wait_ns` nanoseconds and returns false.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_t wait_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  while (!mbar_try_wait(bar, parity))
+    if (global_ns() - t0 > wait_ns) return false;
+  return true;
+}
+// One-dimensional bulk copy global -> this CTA's shared memory through the TMA
+// unit; completion is signalled on `bar` by byte count.  Both addresses are
+// 16-byte aligned and `bytes` is a multiple of 16.
+__device__ __forceinline__ void tma_load_1d(uint32_t dst, const void* src, uint32_t bytes,
+                                            uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1], %2, [%3], %4;" ::"r"(dst),
+      "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+      : "memory");
+}
+
+// ---- kernel geometry ---------------------------------------------------------------
+// A work item is one chunk (kChunkElems elements) of one tensor in one phase.  It is
+// streamed as stages: the g, p, m and v slices of kStageElems elements (phases B, C),
+// or the whole chunk of g (phase A), copied into shared memory by TMA.  kStages stages
+// form a ring per block.  Three kinds of warps share a block:
+//   warps 0-7  consumers: wait for a stage, pull their elements into registers, give
+//              the slot back, compute, store p/m/v and the parameter copy (phase C) or
+//              accumulate sums of squares (A, B).  They never touch a block-wide
+//              barrier and never wait on global memory.
+//   warp 8     producer (one thread): draws tickets, resolves each item's dependency
+//              (bounded wait on the tensor's flag), fills the ring with bulk copies.
+//   warp 9     publisher: adds the consumers' per-warp partial sums of an item, writes
+//              them to global memory, counts arrivals per tensor and - for the last
+//              chunk of a tensor - adds all chunk partials in a fixed order, takes the
+//              square root and releases the tensor's flag.
+// Two blocks are resident per SM: ~170 KB of copies in flight per SM.
+constexpr int kStageVecs = 2;  // 4-element vectors per consumer thread per B/C stage
+constexpr int kStageElems = kBlockThreads * 4 * kStageVecs;  // 2048
+#ifndef RAFB200_LANS_STAGES
+#define RAFB200_LANS_STAGES 3  // ring depth per block
+#endif
+#ifndef RAFB200_LANS_BLOCKS
+#define RAFB200_LANS_BLOCKS 2  // resident blocks per SM the ring and registers are sized for
+#endif
+constexpr int kStages = RAFB200_LANS_STAGES;
+constexpr int kConsumers = kBlockThreads;        // 256
+constexpr int kConsumerWarps = kConsumers / 32;  // 8
+constexpr int kLansThreads = kConsumers + 64;    // + producer warp + publisher warp
+constexpr int kRedSlots = 4;                     // ring of pending reductions
+constexpr uint32_t kTicketEnd = 0xffffffffu;
+constexpr uint32_t kRedEnd = 3u;
+static_assert(kChunkElems % kStageElems == 0, "a chunk is a whole number of stages");
+static_assert(kChunkElems % (kConsumers * kVec) == 0, "phase A walks a chunk in whole passes");
+
+struct __align__(16) StageMeta {
+  const void* g;  // global addresses of the stage's first element (stores, unaligned fallback)
+  float* p;
+  float* m;
+  float* v;
+  void* out;
+  uint32_t ticket;      // kTicketEnd: no more work (or a wait expired) - consumers leave
+  uint32_t n;           // elements in this stage
+  uint32_t nbulk;       // leading elements that were delivered into shared memory
+  uint32_t flags;       // bits 0-1 phase, bit 2 first stage of its item, bit 3 last stage
+  uint32_t tensor;
+  uint32_t part_index;  // slot of the item's partial sums
+  uint32_t nchunks;
+  uint32_t first_chunk;
+  float cs;             // gradient multiplier  grad_scale / (||g|| + eps)
+  float ratio_m;        // -beta1 * lr * ||p|| / ||update_m||   (phase C)
+  float ratio_g;        // -beta3 * lr * ||p|| / ||update_g||
+  uint32_t pad_;
+};
+static_assert(sizeof(StageMeta) == 96, "StageMeta is 96 bytes");
+
+struct __align__(16) RedSlot {
+  float val[3][kConsumerWarps];  // per consumer warp: sums of squares of this item
+  uint32_t phase;                // kPhaseA, kPhaseB or kRedEnd (consumers have left)
+  uint32_t tensor;
+  uint32_t part_index;
+  uint32_t nchunks;
+  uint32_t first_chunk;
+  uint32_t pad_[3];
+};
+static_assert(sizeof(RedSlot) == 128, "RedSlot is 128 bytes");
+
+// Metadata of one of the (up to four) tickets a block holds, filled by cp.async.
+struct __align__(16) ChainSlot {
+  uint32_t ticket;
+  uint32_t pad_;
+  Item item;
+  unsigned int norm[4];
+  TensorDesc d;
+};
+static_assert(sizeof(ChainSlot) == 96, "ChainSlot is 96 bytes");
+
+__device__ __forceinline__ void cp_async8(void* smem_dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async16_ca(void* smem_dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async16_cg(void* smem_dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.wait_all;" ::: "memory");
+}
+
+template <typename GT>
+struct LansSmem {
+  static constexpr int kGBytes = kStageElems * sizeof(GT);
+  static constexpr int kFBytes = kStageElems * 4;
+  static constexpr int kStageBytes = kGBytes + 3 * kFBytes;
+  static_assert(kChunkElems * sizeof(GT) <= kStageBytes, "a phase-A stage holds a chunk of g");
+  static constexpr int kMetaOff = kStages * kStageBytes;
+  static constexpr int kRedOff = kMetaOff + kStages * (int)sizeof(StageMeta);
+  static constexpr int kChainOff = kRedOff + kRedSlots * (int)sizeof(RedSlot);
+  static constexpr int kBarOff = kChainOff + 4 * (int)sizeof(ChainSlot);
+  static constexpr int kTotal = kBarOff + (2 * kStages + 2 * kRedSlots) * 8;
+};
+
+// Bounded wait on an mbarrier that also gives up as soon as any block has reported an
+// error; a timeout reports kErrRing itself.
+__device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, LansHeader* hdr,
+                                          uint32_t where, uint64_t wait_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*reinterpret_cast<volatile unsigned*>(&hdr->error) != 0) return false;
+    if (global_ns() - t0 > wait_ns) {
+      if (atomicCAS(&hdr->error, 0u, kErrRing) == 0u) hdr->error_item = where;
       return false;
     }
   }
@@ -69,232 +294,479 @@ __device__ __forceinline__ bool wait_flag(const unsigned* flag, LansHeader* hdr,
 }
 
 template <typename GT, typename OT>
-__global__ void __launch_bounds__(kBlockThreads, 4) lans_kernel(const LansParams P) {
-  __shared__ float s_red[3 * (kBlockThreads / 32)];
-  __shared__ uint32_t s_ticket;
-  __shared__ int s_flag;
-  __shared__ float s_bc[2];
+__global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel(const LansParams P) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  using L = LansSmem<GT>;
+  StageMeta* s_meta = reinterpret_cast<StageMeta*>(smem + L::kMetaOff);
+  RedSlot* s_red = reinterpret_cast<RedSlot*>(smem + L::kRedOff);
+  const uint32_t bar_full = smem_u32(smem + L::kBarOff);
+  const uint32_t bar_empty = bar_full + kStages * 8;
+  const uint32_t red_full = bar_empty + kStages * 8;
+  const uint32_t red_empty = red_full + kRedSlots * 8;
+  const uint32_t data_base = smem_u32(smem);
 
   const int tid = threadIdx.x;
-  Policies pol;
-  pol.init();
-  LansStage1 s1 = P.s1;
-  if (P.step_dev != nullptr) {
-    // step lives on the device as a 0-d fp32 tensor (python/raf/optim/lans.py:239):
-    // same expression as the host code, evaluated in double.
-    if (tid == 0) {
-      float bc1 = 1.0f, bc2 = 1.0f;
-      if (P.bias_correction == 1) {
-        const int step = (int)(*P.step_dev);
-        bc1 = (float)(1.0 - pow((double)s1.beta1, (double)step));
-        bc2 = (float)(1.0 - pow((double)s1.beta2, (double)step));
-      }
-      s_bc[0] = bc1;
-      s_bc[1] = bc2;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);                // the producer's arrive (+ transaction bytes)
+      mbar_init(bar_empty + 8 * s, kConsumerWarps);  // one arrive per consumer warp
     }
-    __syncthreads();
-    s1.bc1 = s_bc[0];
-    s1.bc2 = s_bc[1];
+    for (int s = 0; s < kRedSlots; ++s) {
+      mbar_init(red_full + 8 * s, kConsumerWarps);
+      mbar_init(red_empty + 8 * s, 1);               // the publisher
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  LansStage1 s1 = P.s1;
+  if (P.step_dev != nullptr) {  // bias corrections were computed on the device, see above
+    s1.inv_bc1 = __ldcg(&P.hdr->inv_bc1);
+    s1.inv_bc2 = __ldcg(&P.hdr->inv_bc2);
   }
 
-  uint32_t next = 0;
-  if (tid == 0) next = atomicAdd(&P.hdr->ticket, 1u);
-  while (true) {
-    if (tid == 0) s_ticket = next;
-    __syncthreads();
-    const uint32_t ticket = s_ticket;
-    if (ticket >= P.nitems) break;
-    // Draw the following ticket now: its latency hides behind this item.
-    if (tid == 0) next = atomicAdd(&P.hdr->ticket, 1u);
+  if (warp == kConsumerWarps) {
+    // =============================== producer ===============================
+    // Resolving an item is a chain of dependent L2 round trips: ticket -> item ->
+    // descriptor and norms.  It is software-pipelined three items deep through shared
+    // memory with cp.async, so that no instruction ever waits for a load issued in
+    // the same iteration (a register pipeline cannot do that across lanes: the
+    // scoreboard tracks registers per warp):
+    //   iteration i   draws the ticket of item i+3,
+    //                 starts the copy of item i+2's table entry (its ticket was drawn
+    //                 in iteration i-1),
+    //                 starts the copies of item i+1's descriptor and norm words,
+    //                 issues item i, whose metadata landed during iteration i-1.
+    // A block thus holds at most four tickets and works them off in order.  Lane 0
+    // runs the chain; lanes 0-3 issue the four bulk copies of a stage (g, p, m, v).
+    const uint64_t pol_keep = make_policy_keep(), pol_stream = make_policy_stream();
+    uint32_t stage_ctr = 0;
+    int failed = 0;
+    unsigned long long st_empty = 0, st_flag = 0, st_pref = 0, st_total = 0, st_x0 = 0, st_x1 = 0;
+    (void)st_empty; (void)st_flag; (void)st_pref; (void)st_total; (void)st_x0; (void)st_x1;
+#ifdef RAFB200_LANS_STATS
+    const long long prod_t0 = clock64();
+#endif
+    ChainSlot* chain = reinterpret_cast<ChainSlot*>(smem + L::kChainOff);
+    uint32_t tk_even = kTicketEnd, tk_odd = kTicketEnd;  // tickets drawn in even / odd iterations
+    auto fetch_item = [&](uint32_t seq, uint32_t ticket) {  // lane 0
+      ChainSlot& c = chain[seq & 3u];
+      c.ticket = ticket;
+      if (ticket < P.nitems) cp_async8(&c.item, P.items + ticket);
+    };
+    auto fetch_desc = [&](uint32_t seq) {  // lane 0; the slot's item has landed
+      ChainSlot& c = chain[seq & 3u];
+      if (c.ticket < P.nitems) {
+        const uint32_t t = c.item.tensor_phase & kTensorMask;
+        const char* src = reinterpret_cast<const char*>(P.descs + t);
+        char* dst = reinterpret_cast<char*>(&c.d);
+        cp_async16_ca(dst, src);
+        cp_async16_ca(dst + 16, src + 16);
+        cp_async16_ca(dst + 32, src + 32);
+        cp_async16_ca(dst + 48, src + 48);
+        cp_async16_cg(c.norm, P.ctl[t].norm);  // L2 copy: the publisher may just have written it
+      }
+    };
+    if (lane == 0) {  // prologue: items 0, 1, 2
+      const uint32_t t0 = atomicAdd(&P.hdr->ticket, 1u);
+      const uint32_t t1 = atomicAdd(&P.hdr->ticket, 1u);
+      tk_odd = atomicAdd(&P.hdr->ticket, 1u);  // item 2: "drawn in iteration -1"
+      fetch_item(0, t0);
+      fetch_item(1, t1);
+      cp_async_wait_all();
+      fetch_desc(0);
+      cp_async_wait_all();
+    }
+    __syncwarp();
 
-    const Item item = P.items[ticket];
-    const uint32_t t = item.tensor_phase & kTensorMask;
-    const int phase = (int)(item.tensor_phase >> kPhaseShift);
-    const TensorDesc d = P.descs[t];
-    LansCtl* ctl = P.ctl + t;
-    const ChunkView c = chunk_view(d, item.chunk, sizeof(GT), sizeof(OT));
-    const GT* g = static_cast<const GT*>(c.g);
-    const int len4 = c.aligned ? (c.len & ~(kVec - 1)) : 0;
+    // One iteration; PAR = seq & 1 selects which ticket register is written / read.
+    auto iteration = [&](auto par_tag, uint32_t seq) -> bool {
+      constexpr bool PAR = decltype(par_tag)::value;
+      uint32_t& tk_new = PAR ? tk_odd : tk_even;
+      uint32_t& tk_old = PAR ? tk_even : tk_odd;
+      { LANS_STAT_BEGIN();
+      if (lane == 0) {
+        cp_async_wait_all();               // copies started in the previous iteration
+        const uint32_t t_prev = tk_old;    // drawn in the previous iteration
+        tk_new = atomicAdd(&P.hdr->ticket, 1u);
+        fetch_item(seq + 2, t_prev);
+        fetch_desc(seq + 1);
+      }
+      __syncwarp();
+      LANS_STAT_END(st_x0); }
+      const ChainSlot& c = chain[seq & 3u];
+      const uint32_t ticket = c.ticket;
+      if (ticket >= P.nitems) return false;
+      const uint32_t tp = c.item.tensor_phase, chunk = c.item.chunk;
+      const TensorDesc d = c.d;
+      uint4 nrm = *reinterpret_cast<const uint4*>(c.norm);
+      const uint32_t t = tp & kTensorMask;
+      const uint32_t phase = tp >> kPhaseShift;
+      LansCtl* ctl = P.ctl + t;
+
+      // B needs ||g|| (when gradients are normalised), C needs all four norms.  They were
+      // fetched an iteration ago; only if they were not final yet does lane 0 wait (bounded).
+      const bool need_wait = (phase == kPhaseB && s1.normalize && !norms_final(nrm, false)) ||
+                             (phase == kPhaseC && !norms_final(nrm, true));
+      if (need_wait) {
+        LANS_STAT_BEGIN();
+        if (lane == 0)
+          failed = wait_norms(ctl, phase == kPhaseC, &nrm, P.hdr,
+                              phase == kPhaseC ? kErrWaitB : kErrWaitA, ticket, P.wait_ns) ? 0 : 1;
+        failed = __shfl_sync(0xffffffffu, failed, 0);
+        nrm.x = __shfl_sync(0xffffffffu, nrm.x, 0);
+        nrm.y = __shfl_sync(0xffffffffu, nrm.y, 0);
+        nrm.z = __shfl_sync(0xffffffffu, nrm.z, 0);
+        nrm.w = __shfl_sync(0xffffffffu, nrm.w, 0);
+        LANS_STAT_END(st_flag);
+        if (failed) return false;
+      }
+      float cs = s1.gscale, ratio_m = 0.f, ratio_g = 0.f;
+      if (phase != kPhaseA) cs = s1.grad_multiplier(norm_value(nrm.x));
+      if (phase == kPhaseC) {  // multi_tensor_lans.cu:347-353
+        const float pn = norm_value(nrm.y), umn = norm_value(nrm.z), ugn = norm_value(nrm.w);
+        ratio_m = (umn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, umn)) : P.lr;
+        ratio_g = (ugn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, ugn)) : P.lr;
+        ratio_m = -mul(ratio_m, s1.beta1);
+        ratio_g = -mul(ratio_g, s1.beta3);
+      }
+
+      const int64_t start = (int64_t)chunk * kChunkElems;
+      const int64_t left = d.numel - start;
+      const int len = left < kChunkElems ? (int)left : kChunkElems;
+      const bool bulk_ok = (d.flags & kFlagBulk) != 0;
+      const uint64_t pol = (phase == kPhaseC) ? pol_stream : pol_keep;
+      const int stage_cap = (phase == kPhaseA) ? kChunkElems : kStageElems;
+      const int gran = 16 / (int)sizeof(GT);  // elements per 16 bytes of gradient
+      // lane q (0..3) copies array q of every stage: g, p, m, v
+      const char* my_src = lane == 0   ? static_cast<const char*>(d.g)
+                           : lane == 1 ? reinterpret_cast<const char*>(d.p)
+                           : lane == 2 ? reinterpret_cast<const char*>(d.m)
+                                       : reinterpret_cast<const char*>(d.v);
+      const uint32_t my_esize = lane == 0 ? (uint32_t)sizeof(GT) : 4u;
+      const uint32_t my_dst_off = lane == 0 ? 0u : (uint32_t)(L::kGBytes + (lane - 1) * L::kFBytes);
+      const bool my_copy = lane < (phase == kPhaseA ? 1 : 4);
+      for (int off = 0; off < len; off += stage_cap) {
+        const uint32_t slot = stage_ctr % kStages;
+        const uint32_t use = stage_ctr / kStages;
+        {
+          LANS_STAT_BEGIN();
+          if (lane == 0)
+            failed = ring_wait(bar_empty + 8 * slot, (use & 1u) ^ 1u, P.hdr, ticket, P.wait_ns) ? 0 : 1;
+          failed = __shfl_sync(0xffffffffu, failed, 0);
+          LANS_STAT_END(st_empty);
+        }
+        if (failed) return false;
+        const int n = (len - off) < stage_cap ? (len - off) : stage_cap;
+        const int nbulk = bulk_ok ? (n / gran) * gran : 0;
+        const uint32_t full = bar_full + 8 * slot;
+        LANS_STAT_BEGIN();
+        if (lane == 0) {
+          StageMeta& mt = s_meta[slot];
+          const int64_t e = start + off;
+          mt.g = static_cast<const char*>(d.g) + e * (int64_t)sizeof(GT);
+          mt.p = d.p + e;
+          mt.m = d.m + e;
+          mt.v = d.v + e;
+          mt.out = d.out ? static_cast<char*>(d.out) + e * (int64_t)sizeof(OT) : nullptr;
+          mt.ticket = ticket;
+          mt.n = (uint32_t)n;
+          mt.nbulk = (uint32_t)nbulk;
+          mt.flags = phase | (off == 0 ? 4u : 0u) | (off + stage_cap >= len ? 8u : 0u);
+          mt.tensor = t;
+          mt.part_index = d.first_chunk + chunk;
+          mt.nchunks = d.nchunks;
+          mt.first_chunk = d.first_chunk;
+          mt.cs = cs;
+          mt.ratio_m = ratio_m;
+          mt.ratio_g = ratio_g;
+          if (nbulk > 0) {
+            const uint32_t gb = (uint32_t)nbulk * (uint32_t)sizeof(GT), fb = (uint32_t)nbulk * 4u;
+            mbar_arrive_expect_tx(full, phase == kPhaseA ? gb : gb + 3u * fb);
+          } else {
+            mbar_arrive(full);
+          }
+        }
+        __syncwarp();
+        LANS_STAT_END(st_x1);
+        {
+          LANS_STAT_BEGIN();
+          if (my_copy && nbulk > 0)
+            tma_load_1d(data_base + slot * L::kStageBytes + my_dst_off,
+                        my_src + (start + off) * (int64_t)my_esize, (uint32_t)nbulk * my_esize, full,
+                        pol);
+          __syncwarp();
+          LANS_STAT_END(st_pref);
+        }
+        ++stage_ctr;
+      }
+      return true;
+    };
+    for (uint32_t seq = 0;; seq += 2) {
+      if (!iteration(std::false_type{}, seq)) break;
+      if (!iteration(std::true_type{}, seq + 1)) break;
+    }
+    if (lane == 0) cp_async_wait_all();  // nothing of this thread may still be in flight
+#ifdef RAFB200_LANS_STATS
+    st_total = (unsigned long long)(clock64() - prod_t0);
+    if (P.stats && lane == 0) {
+      atomicAdd(P.stats + 0, st_total);
+      atomicAdd(P.stats + 1, st_empty);
+      atomicAdd(P.stats + 2, st_flag);
+      atomicAdd(P.stats + 3, st_pref);
+      atomicAdd(P.stats + 4, 1ull);
+      atomicAdd(P.stats + 7, st_x0);
+      atomicAdd(P.stats + 8, st_x1);
+    }
+#endif
+    // Terminator.  Every stage published before it is consumed (its copies have
+    // landed) before the consumers see it, so nothing is in flight when they leave.
+    if (lane == 0) {
+      const uint32_t slot = stage_ctr % kStages;
+      if (ring_wait(bar_empty + 8 * slot, ((stage_ctr / kStages) & 1u) ^ 1u, P.hdr, kTicketEnd,
+                    P.wait_ns)) {
+        s_meta[slot].ticket = kTicketEnd;
+        mbar_arrive(bar_full + 8 * slot);
+      }
+    }
+    return;
+  }
+
+  if (warp == kConsumerWarps + 1) {
+    // =============================== publisher ===============================
+    for (uint32_t r = 0;; ++r) {
+      const uint32_t buf = r % kRedSlots, use = r / kRedSlots;
+      if (!ring_wait(red_full + 8 * buf, use & 1u, P.hdr, r, P.wait_ns)) return;
+      const RedSlot& rs = s_red[buf];
+      const uint32_t phase = rs.phase;
+      if (phase == kRedEnd) return;
+      const uint32_t t = rs.tensor, part_index = rs.part_index, nchunks = rs.nchunks,
+                     first_chunk = rs.first_chunk;
+      const int nq = (phase == kPhaseA) ? 1 : 3;
+      float sum = 0.f;
+      if (lane < nq) {
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) sum += rs.val[lane][w];
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(red_empty + 8 * buf);  // the slot has been read
+      // lane q owns quantity q: A -> ||g||^2 ; B -> ||p||^2, ||update_m||^2, ||update_g||^2
+      float* part = (phase == kPhaseA) ? P.part_a : P.part_b + (size_t)lane * P.total_chunks;
+      if (lane < nq) {
+        part[part_index] = sum;
+        __threadfence();
+      }
+      __syncwarp();
+      LansCtl* ctl = P.ctl + t;
+      unsigned is_last = 0;
+      if (lane == 0) {
+        const unsigned old = atomicAdd(phase == kPhaseA ? &ctl->arrived_a : &ctl->arrived_b, 1u);
+        is_last = (old + 1u == nchunks);
+      }
+      is_last = __shfl_sync(0xffffffffu, is_last, 0);
+      if (is_last) {
+        // Last chunk of the tensor: add all chunk partials, lane-strided then a shuffle
+        // tree - a fixed order, so the norm is reproducible bit for bit.
+        __threadfence();
+        float tot[3] = {0.f, 0.f, 0.f};
+        for (uint32_t j = lane; j < nchunks; j += 32) {
+          const uint32_t ci = first_chunk + j;
+          if (phase == kPhaseA) {
+            tot[0] += __ldcg(P.part_a + ci);
+          } else {
+            tot[0] += __ldcg(P.part_b + ci);
+            tot[1] += __ldcg(P.part_b + P.total_chunks + ci);
+            tot[2] += __ldcg(P.part_b + 2 * (size_t)P.total_chunks + ci);
+          }
+        }
+        tot[0] = warp_sum(tot[0]);
+        tot[1] = warp_sum(tot[1]);
+        tot[2] = warp_sum(tot[2]);
+        if (lane == 0) {
+          volatile unsigned* nw = ctl->norm;  // value and "final" bit in one word each
+          if (phase == kPhaseA) {
+            nw[0] = __float_as_uint(sqrtf(tot[0])) | kNormValid;
+          } else {
+            nw[1] = __float_as_uint(sqrtf(tot[0])) | kNormValid;
+            nw[2] = __float_as_uint(sqrtf(tot[1])) | kNormValid;
+            nw[3] = __float_as_uint(sqrtf(tot[2])) | kNormValid;
+          }
+        }
+      }
+    }
+  }
+
+  // ================================ consumers ================================
+  // Thread `tid` owns, in every stage, the vectors of four elements at q*1024 + 4*tid:
+  // 16-byte shared-memory reads without bank conflicts, coalesced 16-byte stores.
+  // Lanes past the end of a ragged stage hold zeros, which add nothing to any sum.
+  Policies pol;
+  pol.init();
+  float acc[3] = {0.f, 0.f, 0.f};
+  uint32_t red_ctr = 0;
+  // Hands this warp's sums of the finished item (or the end marker) to the publisher.
+  auto hand_over = [&](uint32_t phase, uint32_t tensor, uint32_t part_index, uint32_t nchunks,
+                       uint32_t first_chunk) {
+    float v0 = 0.f, v1 = 0.f, v2 = 0.f;
+    if (phase != kRedEnd) v0 = warp_sum(acc[0]);
+    if (phase == kPhaseB) {
+      v1 = warp_sum(acc[1]);
+      v2 = warp_sum(acc[2]);
+    }
+    if (lane == 0) {
+      const uint32_t buf = red_ctr % kRedSlots, use = red_ctr / kRedSlots;
+      ring_wait(red_empty + 8 * buf, (use & 1u) ^ 1u, P.hdr, red_ctr, P.wait_ns);
+      RedSlot& rs = s_red[buf];
+      rs.val[0][warp] = v0;
+      rs.val[1][warp] = v1;
+      rs.val[2][warp] = v2;
+      if (warp == 0) {
+        rs.phase = phase;
+        rs.tensor = tensor;
+        rs.part_index = part_index;
+        rs.nchunks = nchunks;
+        rs.first_chunk = first_chunk;
+      }
+      mbar_arrive(red_full + 8 * buf);
+    }
+    ++red_ctr;
+  };
+
+  unsigned long long st_full = 0, st_hand = 0;
+  (void)st_full; (void)st_hand;
+#ifdef RAFB200_LANS_STATS
+  const long long cons_t0 = clock64();
+#endif
+  for (uint32_t stage_ctr = 0;; ++stage_ctr) {
+    const uint32_t slot = stage_ctr % kStages;
+    { LANS_STAT_BEGIN();
+    if (!ring_wait(bar_full + 8 * slot, (stage_ctr / kStages) & 1u, P.hdr, stage_ctr, P.wait_ns))
+      break;
+    LANS_STAT_END(st_full); }
+    const StageMeta& mt = s_meta[slot];
+    if (mt.ticket == kTicketEnd) break;
+    const uint32_t phase = mt.flags & 3u;
+    const bool first = (mt.flags & 4u) != 0, last = (mt.flags & 8u) != 0;
+    const int n = (int)mt.n, nbulk = (int)mt.nbulk;
+    const GT* gg = static_cast<const GT*>(mt.g);
+    const uint32_t tensor = mt.tensor, part_index = mt.part_index, nchunks = mt.nchunks,
+                   first_chunk = mt.first_chunk;
+    const unsigned char* sbase = smem + slot * L::kStageBytes;
+    if (first) acc[0] = acc[1] = acc[2] = 0.f;
 
     if (phase == kPhaseA) {
-      float acc[1] = {0.f};
-      for (int base = 0; base < len4; base += kUnroll * kPassElems) {
-        F4 rg[kUnroll];
+      // The whole chunk of g sits in the stage: four vectors per thread.
+      constexpr int kPasses = kChunkElems / (kConsumers * kVec);
+      F4 rg[kPasses];
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-          const int e = base + u * kPassElems + tid * kVec;
-          if (e < len4) rg[u] = Elem<GT>::template load4<kKeep>(g + e, pol);
-        }
+      for (int q = 0; q < kPasses; ++q) {
+        const int e = q * (kConsumers * kVec) + tid * kVec;
+        if (e < nbulk) {
+          rg[q] = Elem<GT>::smem4(sbase + e * sizeof(GT));
+        } else {
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-          const int e = base + u * kPassElems + tid * kVec;
-          if (e < len4) {
-#pragma unroll
-            for (int j = 0; j < kVec; ++j) {
-              float x = rg[u].x[j];
-              if (s1.gscale != 1.0f) x = mul(x, s1.gscale);
-              acc[0] = fmaf(x, x, acc[0]);
-            }
-          }
+          for (int j = 0; j < kVec; ++j)
+            rg[q].x[j] = (e + j < n) ? Elem<GT>::to_f32(gg[e + j]) : 0.f;
         }
       }
-      for (int e = len4 + tid; e < c.len; e += kBlockThreads) {
-        float x = Elem<GT>::to_f32(g[e]);
-        if (s1.gscale != 1.0f) x = mul(x, s1.gscale);
-        acc[0] = fmaf(x, x, acc[0]);
-      }
-      block_sum<1>(acc, s_red);
-      if (tid == 0) {
-        P.part_a[d.first_chunk + item.chunk] = acc[0];
-        __threadfence();
-        const unsigned old = atomicAdd(&ctl->arrived_a, 1u);
-        s_flag = (old + 1u == d.nchunks);
-      }
-      __syncthreads();
-      if (s_flag) {  // this block published the last partial of the tensor
-        __threadfence();
-        float tot[1] = {0.f};
-        for (uint32_t i = tid; i < d.nchunks; i += kBlockThreads)
-          tot[0] += __ldcg(P.part_a + d.first_chunk + i);
-        block_sum<1>(tot, s_red);
-        if (tid == 0) {
-          ctl->norm[0] = sqrtf(tot[0]);
-          __threadfence();
-          st_release(&ctl->ready_a, 1u);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_empty + 8 * slot);  // values are in registers
+#pragma unroll
+      for (int q = 0; q < kPasses; ++q)
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+          const float x = rg[q].x[j] * s1.gscale;
+          acc[0] = fmaf(x, x, acc[0]);
         }
-      }
-    } else {
-      // B and C both need ||g|| (when gradients are normalised); C also the other three.
-      if (tid == 0) {
-        bool ok = true;
-        if (s1.normalize) ok = wait_flag(&ctl->ready_a, P.hdr, kErrWaitA, ticket, P.spin_limit);
-        if (ok && phase == kPhaseC)
-          ok = wait_flag(&ctl->ready_b, P.hdr, kErrWaitB, ticket, P.spin_limit);
-        s_flag = ok ? 0 : 1;
-      }
-      __syncthreads();
-      if (s_flag) return;  // a bounded wait expired: the whole block leaves, nothing in flight
-      const float gnorm = s1.normalize ? __ldcg(&ctl->norm[0]) : 0.f;
+      if (last) hand_over(kPhaseA, tensor, part_index, nchunks, first_chunk);
+      continue;
+    }
 
-      if (phase == kPhaseB) {
-        float acc[3] = {0.f, 0.f, 0.f};
-        for (int base = 0; base < len4; base += kUnroll * kPassElems) {
-          F4 rg[kUnroll], rp[kUnroll], rm[kUnroll], rv[kUnroll];
+    // ---- phases B and C: g, p, m, v of kStageElems elements ----
+    float* gp = mt.p;
+    float* gm = mt.m;
+    float* gv = mt.v;
+    OT* gout = static_cast<OT*>(mt.out);
+    const float cs = mt.cs, ratio_m = mt.ratio_m, ratio_g = mt.ratio_g;
+    const bool whole = nbulk == kStageElems;  // the common case: nothing ragged or unaligned
+    F4 rg[kStageVecs], rp[kStageVecs], rm[kStageVecs], rv[kStageVecs];
+    int cnt[kStageVecs];
 #pragma unroll
-          for (int u = 0; u < kUnroll; ++u) {
-            const int e = base + u * kPassElems + tid * kVec;
-            if (e < len4) {
-              rg[u] = Elem<GT>::template load4<kKeep>(g + e, pol);
-              rp[u] = Elem<float>::template load4<kKeep>(c.p + e, pol);
-              rm[u] = Elem<float>::template load4<kKeep>(c.m + e, pol);
-              rv[u] = Elem<float>::template load4<kKeep>(c.v + e, pol);
-            }
-          }
+    for (int q = 0; q < kStageVecs; ++q) {
+      const int e = q * (kConsumers * kVec) + tid * kVec;
+      if (whole || e < nbulk) {
+        cnt[q] = kVec;
+        rg[q] = Elem<GT>::smem4(sbase + e * sizeof(GT));
+        rp[q] = Elem<float>::smem4(sbase + L::kGBytes + e * 4);
+        rm[q] = Elem<float>::smem4(sbase + L::kGBytes + L::kFBytes + e * 4);
+        rv[q] = Elem<float>::smem4(sbase + L::kGBytes + 2 * L::kFBytes + e * 4);
+      } else {
+        cnt[q] = e < n ? ((n - e) < kVec ? (n - e) : kVec) : 0;
 #pragma unroll
-          for (int u = 0; u < kUnroll; ++u) {
-            const int e = base + u * kPassElems + tid * kVec;
-            if (e < len4) {
-#pragma unroll
-              for (int j = 0; j < kVec; ++j) {
-                float um, ug, mm = rm[u].x[j], vv = rv[u].x[j];
-                const float pp = rp[u].x[j];
-                s1(rg[u].x[j], pp, mm, vv, gnorm, um, ug);
-                acc[0] = fmaf(pp, pp, acc[0]);
-                acc[1] = fmaf(um, um, acc[1]);
-                acc[2] = fmaf(ug, ug, acc[2]);
-              }
-            }
-          }
+        for (int j = 0; j < kVec; ++j) {
+          const bool ok = j < cnt[q];
+          rg[q].x[j] = ok ? Elem<GT>::to_f32(gg[e + j]) : 0.f;
+          rp[q].x[j] = ok ? gp[e + j] : 0.f;
+          rm[q].x[j] = ok ? gm[e + j] : 0.f;
+          rv[q].x[j] = ok ? gv[e + j] : 0.f;
         }
-        for (int e = len4 + tid; e < c.len; e += kBlockThreads) {
-          float um, ug, mm = c.m[e], vv = c.v[e];
-          const float pp = c.p[e];
-          s1(Elem<GT>::to_f32(g[e]), pp, mm, vv, gnorm, um, ug);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_empty + 8 * slot);  // values are in registers
+
+    if (phase == kPhaseB) {
+#pragma unroll
+      for (int q = 0; q < kStageVecs; ++q)
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+          float um, ug, mm = rm[q].x[j], vv = rv[q].x[j];
+          const float pp = rp[q].x[j];
+          s1(rg[q].x[j], pp, mm, vv, cs, um, ug);
           acc[0] = fmaf(pp, pp, acc[0]);
           acc[1] = fmaf(um, um, acc[1]);
           acc[2] = fmaf(ug, ug, acc[2]);
         }
-        block_sum<3>(acc, s_red);
-        if (tid == 0) {
-          const uint32_t ci = d.first_chunk + item.chunk;
-          P.part_b[ci] = acc[0];
-          P.part_b[P.total_chunks + ci] = acc[1];
-          P.part_b[2 * P.total_chunks + ci] = acc[2];
-          __threadfence();
-          const unsigned old = atomicAdd(&ctl->arrived_b, 1u);
-          s_flag = (old + 1u == d.nchunks);
-        }
-        __syncthreads();
-        if (s_flag) {
-          __threadfence();
-          float tot[3] = {0.f, 0.f, 0.f};
-          for (uint32_t i = tid; i < d.nchunks; i += kBlockThreads) {
-            const uint32_t ci = d.first_chunk + i;
-            tot[0] += __ldcg(P.part_b + ci);
-            tot[1] += __ldcg(P.part_b + P.total_chunks + ci);
-            tot[2] += __ldcg(P.part_b + 2 * P.total_chunks + ci);
-          }
-          block_sum<3>(tot, s_red);
-          if (tid == 0) {
-            ctl->norm[1] = sqrtf(tot[0]);
-            ctl->norm[2] = sqrtf(tot[1]);
-            ctl->norm[3] = sqrtf(tot[2]);
-            __threadfence();
-            st_release(&ctl->ready_b, 1u);
-          }
-        }
-      } else {  // phase C
-        // multi_tensor_lans.cu:347-353
-        const float pn = __ldcg(&ctl->norm[1]);
-        const float umn = __ldcg(&ctl->norm[2]);
-        const float ugn = __ldcg(&ctl->norm[3]);
-        float ratio_m = (umn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, umn)) : P.lr;
-        float ratio_g = (ugn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, ugn)) : P.lr;
-        ratio_m = mul(ratio_m, s1.beta1);
-        ratio_g = mul(ratio_g, s1.beta3);
-        OT* out = static_cast<OT*>(c.out);
-        for (int base = 0; base < len4; base += kUnroll * kPassElems) {
-          F4 rg[kUnroll], rp[kUnroll], rm[kUnroll], rv[kUnroll];
+      if (last) hand_over(kPhaseB, tensor, part_index, nchunks, first_chunk);
+    } else {  // phase C
 #pragma unroll
-          for (int u = 0; u < kUnroll; ++u) {
-            const int e = base + u * kPassElems + tid * kVec;
-            if (e < len4) {
-              rg[u] = Elem<GT>::template load4<kStream>(g + e, pol);
-              rp[u] = Elem<float>::template load4<kStream>(c.p + e, pol);
-              rm[u] = Elem<float>::template load4<kStream>(c.m + e, pol);
-              rv[u] = Elem<float>::template load4<kStream>(c.v + e, pol);
+      for (int q = 0; q < kStageVecs; ++q) {
+        const int e = q * (kConsumers * kVec) + tid * kVec;
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+          float um, ug;
+          s1(rg[q].x[j], rp[q].x[j], rm[q].x[j], rv[q].x[j], cs, um, ug);
+          // p - ratio_m*update_m - ratio_g*update_g  (:385; the ratios carry the minus sign)
+          rp[q].x[j] = fmaf(ratio_g, ug, fmaf(ratio_m, um, rp[q].x[j]));
+        }
+        if (whole || e < nbulk) {  // aligned: 16-byte stores
+          Elem<float>::template store4<kStream>(gp + e, rp[q], pol);
+          Elem<float>::template store4<kStream>(gm + e, rm[q], pol);
+          Elem<float>::template store4<kStream>(gv + e, rv[q], pol);
+          if (gout) Elem<OT>::template store4<kStream>(gout + e, rp[q], pol);
+        } else {
+#pragma unroll
+          for (int j = 0; j < kVec; ++j)
+            if (j < cnt[q]) {
+              gp[e + j] = rp[q].x[j];
+              gm[e + j] = rm[q].x[j];
+              gv[e + j] = rv[q].x[j];
+              if (gout) gout[e + j] = Elem<OT>::from_f32(rp[q].x[j]);
             }
-          }
-#pragma unroll
-          for (int u = 0; u < kUnroll; ++u) {
-            const int e = base + u * kPassElems + tid * kVec;
-            if (e < len4) {
-#pragma unroll
-              for (int j = 0; j < kVec; ++j) {
-                float um, ug;
-                s1(rg[u].x[j], rp[u].x[j], rm[u].x[j], rv[u].x[j], gnorm, um, ug);
-                rp[u].x[j] = sub(sub(rp[u].x[j], mul(ratio_m, um)), mul(ratio_g, ug));  // :385
-              }
-              Elem<float>::template store4<kStream>(c.p + e, rp[u], pol);
-              Elem<float>::template store4<kStream>(c.m + e, rm[u], pol);
-              Elem<float>::template store4<kStream>(c.v + e, rv[u], pol);
-              if (out) Elem<OT>::template store4<kStream>(out + e, rp[u], pol);
-            }
-          }
-        }
-        for (int e = len4 + tid; e < c.len; e += kBlockThreads) {
-          float um, ug, mm = c.m[e], vv = c.v[e], pp = c.p[e];
-          s1(Elem<GT>::to_f32(g[e]), pp, mm, vv, gnorm, um, ug);
-          pp = sub(sub(pp, mul(ratio_m, um)), mul(ratio_g, ug));
-          c.p[e] = pp;
-          c.m[e] = mm;
-          c.v[e] = vv;
-          if (out) out[e] = Elem<OT>::from_f32(pp);
         }
       }
     }
-    __syncthreads();  // s_ticket / s_flag are rewritten at the top of the loop
   }
+#ifdef RAFB200_LANS_STATS
+  if (P.stats && tid == 0) {
+    atomicAdd(P.stats + 5, (unsigned long long)(clock64() - cons_t0));
+    atomicAdd(P.stats + 6, st_full);
+  }
+#endif
+  // No more stages (or a wait expired): release the publisher.
+  hand_over(kRedEnd, 0, 0, 0, 0);
 }
 
 // ---- host side -----------------------------------------------------------------
@@ -368,18 +840,21 @@ template <typename GT, typename OT>
 static int launch_lans_t(const rafb200_tensor_list_s* l, const LansParams& P, cudaStream_t s) {
   static int occ[64] = {0};
   const int dev = (l->device >= 0 && l->device < 64) ? l->device : 0;
+  const int smem = LansSmem<GT>::kTotal;
   if (occ[dev] == 0) {
+    RAFB200_CUDA(cudaFuncSetAttribute(lans_kernel<GT, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, lans_kernel<GT, OT>, kBlockThreads, 0) !=
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, lans_kernel<GT, OT>, kLansThreads, smem) !=
             cudaSuccess || n <= 0)
       n = 1;
     occ[dev] = n;
   }
+  // Persistent grid: every SM holds `occ` blocks; a cap leaves SMs to a concurrent collective.
   int64_t grid = (int64_t)l->sm_count * occ[dev];
   if (l->max_blocks > 0 && grid > l->max_blocks) grid = l->max_blocks;
   if (grid > (int64_t)P.nitems) grid = P.nitems;
   if (grid < 1) grid = 1;
-  lans_kernel<GT, OT><<<(unsigned)grid, kBlockThreads, 0, s>>>(P);
+  lans_kernel<GT, OT><<<(unsigned)grid, kLansThreads, smem, s>>>(P);
   RAFB200_CUDA(cudaGetLastError());
   return RAFB200_OK;
 }
@@ -441,7 +916,10 @@ int rafb200_lans(rafb200_tensor_list_t list, int step, const float* step_dev, fl
   P.s1.beta3 = (grad_averaging == 1) ? 1 - beta1 : 1.0f;  // lans.cc:106-109
   P.s1.one_minus_beta2 = 1 - beta2;
   P.s1.eps = eps;
-  bias_corrections(beta1, beta2, step_dev ? 1 : step, bias_correction, &P.s1.bc1, &P.s1.bc2);
+  float bc1, bc2;
+  bias_corrections(beta1, beta2, step_dev ? 1 : step, bias_correction, &bc1, &bc2);
+  P.s1.inv_bc1 = 1.0f / bc1;
+  P.s1.inv_bc2 = 1.0f / bc2;
   P.s1.wd = weight_decay;
   P.s1.gscale = grad_scale;
   P.s1.mode = mode;
@@ -449,9 +927,33 @@ int rafb200_lans(rafb200_tensor_list_t list, int step, const float* step_dev, fl
   P.lr = learning_rate;
   P.step_dev = step_dev;
   P.bias_correction = bias_correction;
-  P.spin_limit = 4u << 20;  // x ~1 us per poll: a few seconds
+  P.wait_ns = 2000000000ull;  // two seconds: far beyond any legitimate wait
+  P.stats = nullptr;
+#ifdef RAFB200_LANS_STATS
+  {
+    static unsigned long long* dev_stats = nullptr;
+    unsigned long long host[10];
+    if (!dev_stats) {
+      cudaMalloc(&dev_stats, sizeof(host));
+    } else {
+      cudaMemcpy(host, dev_stats, sizeof(host), cudaMemcpyDeviceToHost);
+      const double nb = host[4] ? (double)host[4] : 1.0;
+      fprintf(stderr, "[lans stats] producer: total %.0f cyc/block, empty-wait %.1f%%, flag-wait %.1f%%, "
+              "tma-issue %.1f%%, chain %.1f%%, meta %.1f%%; consumer: total %.0f cyc/block, full-wait %.1f%%\n",
+              host[0] / nb, 100.0 * host[1] / (host[0] + 1.0), 100.0 * host[2] / (host[0] + 1.0),
+              100.0 * host[3] / (host[0] + 1.0), 100.0 * host[7] / (host[0] + 1.0),
+              100.0 * host[8] / (host[0] + 1.0), host[5] / nb, 100.0 * host[6] / (host[5] + 1.0));
+    }
+    cudaMemset(dev_stats, 0, sizeof(host));
+    P.stats = dev_stats;
+  }
+#endif
 
   RAFB200_CUDA(cudaMemsetAsync(workspace, 0, lans_ctl_bytes(list->k), s));
+  if (step_dev) {
+    lans_bias_kernel<<<1, 1, 0, s>>>(P.hdr, step_dev, beta1, beta2, bias_correction);
+    RAFB200_CUDA(cudaGetLastError());
+  }
   switch (list->g_dtype) {
     case RAFB200_F32: return launch_lans_g<float>(list, P, s);
     case RAFB200_F16: return launch_lans_g<__half>(list, P, s);
@@ -470,7 +972,10 @@ int rafb200_lans_status(rafb200_tensor_list_t list, const void* workspace, float
   const LansCtl* ctl = reinterpret_cast<const LansCtl*>(host.data() + 64);
   if (norms_host) {
     for (int t = 0; t < list->k; ++t)
-      for (int j = 0; j < 4; ++j) norms_host[4 * t + j] = ctl[t].norm[j];
+      for (int j = 0; j < 4; ++j) {
+        const unsigned bits = ctl[t].norm[j] & ~kNormValid;
+        memcpy(&norms_host[4 * t + j], &bits, sizeof(float));
+      }
   }
   if (hdr->error != 0)
     return set_error(RAFB200_DEVICE_WAIT_EXPIRED,

@@ -141,6 +141,8 @@ int rafb200_tensor_list_bind(rafb200_tensor_list_t l, const void* const* g, floa
       RAFB200_REQUIRE(!v || d.v, "rafb200_tensor_list_bind: NULL v for tensor %d", i);
     }
     d.flags = pointers_aligned(d.g, l->g_dtype, d.p, d.m, d.v, d.out, l->out_dtype) ? 1u : 0u;
+    auto a16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    if ((d.flags & 1u) && a16(d.g) && a16(d.p) && a16(d.m) && a16(d.v)) d.flags |= 2u;  // kFlagBulk
     if (memcmp(&d, &l->host_desc[i], sizeof(d)) != 0) {
       l->host_desc[i] = d;
       changed = true;

@@ -12,7 +12,8 @@ namespace rafb200 {
 constexpr int kVec = 4;                              // elements per thread per pass
 constexpr int kPassElems = kBlockThreads * kVec;     // 1024
 constexpr int kUnroll = 2;                           // passes in flight
-constexpr uint32_t kFlagAligned = 1u;
+constexpr uint32_t kFlagAligned = 1u;  // vector accesses allowed (16 B fp32, 8 B 16-bit arrays)
+constexpr uint32_t kFlagBulk = 2u;     // every array is 16-byte aligned: TMA bulk copies allowed
 
 // ---- per-element arithmetic -------------------------------------------------
 // All three follow the reference expression by expression; see the C ABI
@@ -46,30 +47,55 @@ struct AdamOp {
 };
 
 // LANS stage 1 (src/op/dialect/cuda/kernels/multi_tensor_lans.cu:281-306).
+// The reference divides five times and takes one square root per element; at
+// 28 bytes per element that is more arithmetic than a B200 SM can issue in the
+// time HBM delivers the data (two passes need it).  The divisions by values
+// that are constant per call or per tensor (bias corrections, ||g||+eps) become
+// multiplications by reciprocals computed once, the two divisions by the
+// denominator share one reciprocal, and sqrt / reciprocal use the 1-ulp hardware
+// approximations (flush-to-zero forms: the square root's argument only matters
+// when it is far above the denormal range, and the reciprocal's is >= eps).
+// Each substitution moves a result by at most about one unit
+// in the last place (1.2e-7 relative); the tests bound the total against the
+// exact restatement at 2e-6 for m and v and far less for p.
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float sqrt_approx(float x) {
+  float r;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
 struct LansStage1 {
-  float beta1, beta2, beta3, one_minus_beta2, eps, bc1, bc2, wd, gscale;
+  float beta1, beta2, beta3, one_minus_beta2, eps, inv_bc1, inv_bc2, wd, gscale;
   int mode, normalize;
-  // in: g (raw), p, m, v, gnorm   out: m, v updated; um, ug
-  __device__ __forceinline__ void operator()(float g, float p, float& m, float& v, float gnorm,
+  // Multiplier that turns a raw gradient element into the scaled gradient:
+  // grad_scale / (||g|| + eps) when gradients are normalised and ||g|| != 0.
+  __device__ __forceinline__ float grad_multiplier(float gnorm) const {
+    if (normalize && gnorm != 0.0f) return gscale * fdiv(1.0f, add(gnorm, eps));
+    return gscale;
+  }
+  // in: g (raw), p, m, v, cs = grad_multiplier   out: m, v updated; um, ug
+  __device__ __forceinline__ void operator()(float g, float p, float& m, float& v, float cs,
                                              float& um, float& ug) const {
-    if (gscale != 1.0f) g = mul(g, gscale);
-    float rp = (wd == 0.0f) ? 0.0f : p;  // :263-268
-    float sg = g;
-    if (normalize && gnorm != 0.0f) sg = fdiv(sg, add(gnorm, eps));
+    float sg = g * cs;
     if (mode == 0) {
-      sg = add(sg, mul(wd, rp));
-      m = add(mul(m, beta1), mul(beta3, sg));
-      v = add(mul(v, beta2), mul(mul(one_minus_beta2, sg), sg));
-      float denom = add(fsqrt(fdiv(v, bc2)), eps);
-      um = fdiv(fdiv(m, bc1), denom);
-      ug = fdiv(sg, denom);
+      sg = fmaf(wd, p, sg);
+      m = fmaf(beta3, sg, m * beta1);
+      v = fmaf(one_minus_beta2 * sg, sg, v * beta2);
+      const float r = rcp_approx(sqrt_approx(v * inv_bc2) + eps);
+      um = (m * inv_bc1) * r;
+      ug = sg * r;
     } else {
-      m = add(mul(m, beta1), mul(beta3, sg));
-      v = add(mul(v, beta2), mul(mul(one_minus_beta2, sg), sg));
-      float denom = add(fsqrt(fdiv(v, bc2)), eps);
-      float sp = mul(wd, rp);
-      um = add(fdiv(fdiv(m, bc1), denom), sp);
-      ug = add(fdiv(sg, denom), sp);
+      m = fmaf(beta3, sg, m * beta1);
+      v = fmaf(one_minus_beta2 * sg, sg, v * beta2);
+      const float r = rcp_approx(sqrt_approx(v * inv_bc2) + eps);
+      const float sp = wd * p;
+      um = fmaf(m * inv_bc1, r, sp);
+      ug = fmaf(sg, r, sp);
     }
   }
 };

@@ -93,6 +93,11 @@ __device__ __forceinline__ void st8(void* p, uint2 v, const Policies& pol) {
 struct F4 {
   float x[4];
 };
+__device__ __forceinline__ F4 f4_zero() {
+  F4 o;
+  o.x[0] = o.x[1] = o.x[2] = o.x[3] = 0.f;
+  return o;
+}
 
 template <typename T>
 struct Elem;  // scalar conversion + raw vector width
@@ -101,6 +106,16 @@ template <>
 struct Elem<float> {
   static __device__ __forceinline__ float to_f32(float v) { return v; }
   static __device__ __forceinline__ float from_f32(float v) { return v; }
+  // four elements from (16-byte aligned) shared memory
+  static __device__ __forceinline__ F4 smem4(const void* p) {
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    F4 o;
+    o.x[0] = q.x;
+    o.x[1] = q.y;
+    o.x[2] = q.z;
+    o.x[3] = q.w;
+    return o;
+  }
   template <int H>
   static __device__ __forceinline__ F4 load4(const float* p, const Policies& pol) {
     uint4 r = ld16<H>(p, pol);
@@ -126,6 +141,17 @@ template <>
 struct Elem<__half> {
   static __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
   static __device__ __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
+  static __device__ __forceinline__ F4 smem4(const void* p) {  // 8-byte aligned shared memory
+    uint2 r = *reinterpret_cast<const uint2*>(p);
+    float2 fa = __half22float2(*reinterpret_cast<__half2*>(&r.x));
+    float2 fb = __half22float2(*reinterpret_cast<__half2*>(&r.y));
+    F4 o;
+    o.x[0] = fa.x;
+    o.x[1] = fa.y;
+    o.x[2] = fb.x;
+    o.x[3] = fb.y;
+    return o;
+  }
   template <int H>
   static __device__ __forceinline__ F4 load4(const __half* p, const Policies& pol) {
     uint2 r = ld8<H>(p, pol);
@@ -155,6 +181,15 @@ struct Elem<__nv_bfloat16> {
   static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
   static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) {
     return __float2bfloat16_rn(v);
+  }
+  static __device__ __forceinline__ F4 smem4(const void* p) {  // 8-byte aligned shared memory
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    F4 o;
+    o.x[0] = __uint_as_float(r.x << 16);
+    o.x[1] = __uint_as_float(r.x & 0xffff0000u);
+    o.x[2] = __uint_as_float(r.y << 16);
+    o.x[3] = __uint_as_float(r.y & 0xffff0000u);
+    return o;
   }
   template <int H>
   static __device__ __forceinline__ F4 load4(const __nv_bfloat16* p, const Policies& pol) {

@@ -1,0 +1,99 @@
+"""The C-ABI shared library: loads without a GPU, exports every symbol the header
+declares, and its host-only parts (plan geometry, argument checks) agree with the oracle."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from raf_b200 import _lib
+
+    return _lib.load()
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "raf_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"RAFB200_API\s+[\w\s\*]+?\b(rafb200_\w+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    from raf_b200 import _lib
+
+    names = _declared_symbols()
+    assert len(names) >= 35
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in include/raf_b200.h but not exported"
+    # the ctypes table binds exactly the declared set
+    assert sorted(_lib.SIGNATURES) == names
+
+
+def test_version_and_error_string(lib):
+    assert lib.rafb200_version() >= 100
+    assert isinstance(lib.rafb200_last_error(), bytes)
+
+
+@pytest.mark.parametrize("n_ranks", [1, 2, 4, 8])
+def test_plan_geometry_matches_oracle(n_ranks):
+    from raf_b200.zero import Plan, bert_large_shapes, gpt2_medium_shapes, numel, resnet50_shapes
+
+    for shapes, bucket in ((resnet50_shapes(), 6553600), (bert_large_shapes(), 13107200),
+                           (gpt2_medium_shapes(), 13107200), ([(7, 3), (1,), (0, 4), (9,)], 10)):
+        for rank in {0, n_ranks - 1}:
+            plan = Plan(shapes, n_ranks, rank, bucket)
+            sizes = [numel(s) for s in shapes]
+            nb, bucket_of = O.plan_buckets(sizes, bucket, rule=1)
+            assert plan.num_buckets == nb
+            assert plan.bucket_of.tolist() == bucket_of.tolist()
+            for i, s in enumerate(shapes):
+                rows = O.shard_rows(s[0], n_ranks)
+                assert plan.shard_rows[i] == rows
+                assert plan.shard_elems[i] == rows * (sizes[i] // s[0] if s[0] else numel(s[1:]))
+                assert plan.padded_elems[i] == plan.shard_elems[i] * n_ranks
+            assert plan.total_elems == sum(sizes)
+            assert plan.total_shard * n_ranks == plan.total_padded
+
+
+def test_plan_sizes_of_the_benchmark_configs():
+    from raf_b200.zero import Plan, bert_large_shapes, gpt2_medium_shapes, resnet50_shapes
+
+    rn = Plan(resnet50_shapes(), 8, 0, 6553600)
+    assert (rn.k, rn.total_elems, rn.total_padded, rn.num_buckets) == (161, 25557032, 25557032, 5)
+    bl8 = Plan(bert_large_shapes(), 8, 0, 13107200)
+    assert (bl8.k, bl8.total_elems, bl8.total_padded) == (391, 335141888, 335154176)
+    assert Plan(bert_large_shapes(), 4, 0, 13107200).total_padded == 335145984
+    g8 = Plan(gpt2_medium_shapes(), 8, 0, 13107200)
+    assert (g8.k, g8.total_elems, g8.total_padded) == (292, 354823168, 354830336)
+
+
+def test_plan_rejects_bad_arguments(lib):
+    h = C.c_void_p()
+    one = (C.c_int64 * 1)(4)
+    assert lib.rafb200_plan_create(1, one, one, 4, 4, 10, C.byref(h)) == 1  # rank outside world
+    assert b"rank" in lib.rafb200_last_error()
+    assert lib.rafb200_plan_create(1, one, one, 0, 0, 10, C.byref(h)) == 1
+    assert lib.rafb200_plan_create(1, None, one, 1, 0, 10, C.byref(h)) == 1
+
+
+def test_invalid_computation_and_null_handles(lib):
+    assert lib.rafb200_comm_size(None) == 0
+    assert lib.rafb200_comm_rank(None) == -1
+    assert lib.rafb200_tensor_list_total_elems(None) == 0
+    assert lib.rafb200_lans_workspace_bytes(None) == 0
+    assert lib.rafb200_sgd_list(None, 0.1, 0.9, 0.0, 1.0, None) == 1
+    assert lib.rafb200_comm_check(None) == 1
+    assert lib.rafb200_cast(None, 7, None, 0, 0, None) == 1  # bad dtype code
+
+
+def test_comm_create_argument_checks(lib):
+    h = C.c_void_p()
+    assert lib.rafb200_comm_create(2, 2, 0, None, 100, C.byref(h)) == 1
+    assert lib.rafb200_comm_create(2, 0, 0, None, 0, C.byref(h)) == 1
