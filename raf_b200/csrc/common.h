@@ -66,14 +66,22 @@ constexpr int kBlockThreads = 256;
 // the (non-negative) norm with the sign bit on, in one 4-byte store.  Validity and
 // value travel in the same word, so readers need no acquire ordering between a flag
 // and the data - a plain load that sees the bit sees the value.
+//
+// Sums of squares are accumulated per tensor with double-precision atomic adds of
+// the per-chunk fp32 partial sums.  A partial has a 24-bit significand and a tensor
+// has at most 2^13 chunks here, so as long as the chunk sums of one tensor lie within
+// a factor 2^16 of each other every addition is exact and the total does not depend
+// on the order in which blocks arrive; outside that range the order can show in the
+// 53rd bit, far below the fp32 rounding of the norm.
 struct LansCtl {
-  unsigned int arrived_a;  // chunks of phase A that have published their partial
+  unsigned int arrived_a;  // chunks of phase A that have added their partial
   unsigned int arrived_b;
   unsigned int pad_[2];
   unsigned int norm[4];    // ||g||, ||p||, ||update_m||, ||update_g||: bits | 0x80000000 once final
+  double sumsq[4];         // running sums of squares of the same four quantities
 };
 constexpr unsigned int kNormValid = 0x80000000u;
-static_assert(sizeof(LansCtl) == 32, "LansCtl is 32 bytes");
+static_assert(sizeof(LansCtl) == 64, "LansCtl is 64 bytes");
 
 struct LansHeader {
   unsigned int ticket;   // next work item to hand out

@@ -17,9 +17,9 @@
 // the second read of g, p, m, v then comes out of L2 and HBM traffic approaches
 // one read and one write per array.
 //
-// Norms: every chunk publishes its partial sums, the block that publishes the
-// last partial of a tensor adds them up in a fixed order and releases a flag.
-// Results are therefore bitwise reproducible run to run.
+// Norms: every chunk adds its fp32 partial sums to per-tensor double-precision
+// accumulators; the block that adds the last chunk of a tensor takes the square
+// root and publishes the norm together with its "final" bit in one word.
 #include <algorithm>
 #include <cmath>
 #include <cstring>
@@ -42,9 +42,6 @@ struct LansParams {
   uint32_t nitems;
   LansHeader* hdr;
   LansCtl* ctl;
-  float* part_a;  // [total_chunks]
-  float* part_b;  // [3][total_chunks]
-  uint32_t total_chunks;
   LansStage1 s1;
   float lr;
   const float* step_dev;
@@ -151,6 +148,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Same, but the hardware may keep the thread suspended for up to `hint_ns` while the
+// phase is incomplete: a waiting warp then leaves the issue slots of its scheduler to
+// the warps that have work (here: the producer warp that everybody is waiting for).
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity,
+                                                      uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded: try_wait blocks for a short hardware-defined time per call; the loop
 // gives up after `wait_ns` nanoseconds and returns false.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_t wait_ns) {
@@ -238,6 +250,11 @@ struct __align__(16) RedSlot {
 };
 static_assert(sizeof(RedSlot) == 128, "RedSlot is 128 bytes");
 
+// A stage that has been issued but whose norms were not final yet.
+struct __align__(16) PendStage {
+  uint32_t slot, phase, tensor, ticket;
+};
+
 // Metadata of one of the (up to four) tickets a block holds, filled by cp.async.
 struct __align__(16) ChainSlot {
   uint32_t ticket;
@@ -273,7 +290,8 @@ struct LansSmem {
   static constexpr int kMetaOff = kStages * kStageBytes;
   static constexpr int kRedOff = kMetaOff + kStages * (int)sizeof(StageMeta);
   static constexpr int kChainOff = kRedOff + kRedSlots * (int)sizeof(RedSlot);
-  static constexpr int kBarOff = kChainOff + 4 * (int)sizeof(ChainSlot);
+  static constexpr int kPendOff = kChainOff + 4 * (int)sizeof(ChainSlot);
+  static constexpr int kBarOff = kPendOff + kStages * (int)sizeof(PendStage);
   static constexpr int kTotal = kBarOff + (2 * kStages + 2 * kRedSlots) * 8;
 };
 
@@ -283,11 +301,14 @@ __device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, LansHea
                                           uint32_t where, uint64_t wait_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_ns();
-  while (!mbar_try_wait(bar, parity)) {
-    if (*reinterpret_cast<volatile unsigned*>(&hdr->error) != 0) return false;
-    if (global_ns() - t0 > wait_ns) {
-      if (atomicCAS(&hdr->error, 0u, kErrRing) == 0u) hdr->error_item = where;
-      return false;
+  unsigned polls = 0;
+  while (!mbar_try_wait_suspend(bar, parity, 4000u)) {
+    if ((++polls & 15u) == 0) {
+      if (*reinterpret_cast<volatile unsigned*>(&hdr->error) != 0) return false;
+      if (global_ns() - t0 > wait_ns) {
+        if (atomicCAS(&hdr->error, 0u, kErrRing) == 0u) hdr->error_item = where;
+        return false;
+      }
     }
   }
   return true;
@@ -310,7 +331,7 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
   const int warp = tid >> 5;
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar_full + 8 * s, 1);                // the producer's arrive (+ transaction bytes)
+      mbar_init(bar_full + 8 * s, 2);                // issue (+ transaction bytes) and resolve
       mbar_init(bar_empty + 8 * s, kConsumerWarps);  // one arrive per consumer warp
     }
     for (int s = 0; s < kRedSlots; ++s) {
@@ -344,17 +365,15 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
     const uint64_t pol_keep = make_policy_keep(), pol_stream = make_policy_stream();
     uint32_t stage_ctr = 0;
     int failed = 0;
-    unsigned long long st_empty = 0, st_flag = 0, st_pref = 0, st_total = 0, st_x0 = 0, st_x1 = 0;
-    (void)st_empty; (void)st_flag; (void)st_pref; (void)st_total; (void)st_x0; (void)st_x1;
+    unsigned long long st_empty = 0, st_flag = 0, st_pref = 0, st_total = 0, st_x0 = 0, st_x1 = 0, st_x2 = 0, st_x3 = 0;
+    (void)st_empty; (void)st_flag; (void)st_pref; (void)st_total; (void)st_x0; (void)st_x1; (void)st_x2; (void)st_x3;
 #ifdef RAFB200_LANS_STATS
     const long long prod_t0 = clock64();
 #endif
     ChainSlot* chain = reinterpret_cast<ChainSlot*>(smem + L::kChainOff);
-    uint32_t tk_even = kTicketEnd, tk_odd = kTicketEnd;  // tickets drawn in even / odd iterations
-    auto fetch_item = [&](uint32_t seq, uint32_t ticket) {  // lane 0
+    auto fetch_item = [&](uint32_t seq) {  // lane 0; the slot's ticket has been stored
       ChainSlot& c = chain[seq & 3u];
-      c.ticket = ticket;
-      if (ticket < P.nitems) cp_async8(&c.item, P.items + ticket);
+      if (c.ticket < P.nitems) cp_async8(&c.item, P.items + c.ticket);
     };
     auto fetch_desc = [&](uint32_t seq) {  // lane 0; the slot's item has landed
       ChainSlot& c = chain[seq & 3u];
@@ -370,67 +389,125 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
       }
     };
     if (lane == 0) {  // prologue: items 0, 1, 2
-      const uint32_t t0 = atomicAdd(&P.hdr->ticket, 1u);
-      const uint32_t t1 = atomicAdd(&P.hdr->ticket, 1u);
-      tk_odd = atomicAdd(&P.hdr->ticket, 1u);  // item 2: "drawn in iteration -1"
-      fetch_item(0, t0);
-      fetch_item(1, t1);
+      chain[0].ticket = atomicAdd(&P.hdr->ticket, 1u);
+      chain[1].ticket = atomicAdd(&P.hdr->ticket, 1u);
+      chain[2].ticket = atomicAdd(&P.hdr->ticket, 1u);
+      fetch_item(0);
+      fetch_item(1);
       cp_async_wait_all();
       fetch_desc(0);
       cp_async_wait_all();
     }
     __syncwarp();
 
-    // One iteration; PAR = seq & 1 selects which ticket register is written / read.
-    auto iteration = [&](auto par_tag, uint32_t seq) -> bool {
-      constexpr bool PAR = decltype(par_tag)::value;
-      uint32_t& tk_new = PAR ? tk_odd : tk_even;
-      uint32_t& tk_old = PAR ? tk_even : tk_odd;
+    // One iteration.  The ticket atomic is issued by lane 1 at the top and its result
+    // is only touched (stored to shared memory) at the bottom, after the stages of
+    // item `seq` have been issued: nothing waits for its round trip.
+    // Issue and resolve are decoupled.  The bulk copies of a stage do not depend on the
+    // tensor's norms, only the consumers' arithmetic does, so a stage is ISSUED (first
+    // arrival on its full barrier, plus the copies' bytes) as soon as a ring slot is
+    // free, and RESOLVED (multiplier and trust ratios written into its metadata, second
+    // arrival) once the norms it needs are final.  A stage whose norms were already
+    // final when the item's metadata was fetched is resolved on the spot; the others
+    // queue up - at most kStages of them - and the producer only blocks on a norm when
+    // it has no free slot left to fill.  While it waits, data keeps streaming in.
+    PendStage* pend = reinterpret_cast<PendStage*>(smem + L::kPendOff);
+    uint32_t resolved_ctr = 0;   // stages [resolved_ctr, stage_ctr) that are not yet resolved
+    uint32_t pend_head = 0, pend_count = 0;
+    // last norms seen final, per (tensor, phase C?) - lane 0 only
+    uint32_t known_t = kTicketEnd;
+    uint4 known_nrm = make_uint4(0, 0, 0, 0);
+    (void)resolved_ctr;
+
+    auto ratios = [&](uint32_t phase, const uint4& nrm, float* cs, float* rm, float* rg) {
+      *cs = s1.gscale;
+      *rm = 0.f;
+      *rg = 0.f;
+      if (phase != kPhaseA) *cs = s1.grad_multiplier(norm_value(nrm.x));
+      if (phase == kPhaseC) {  // multi_tensor_lans.cu:347-353
+        const float pn = norm_value(nrm.y), umn = norm_value(nrm.z), ugn = norm_value(nrm.w);
+        float a = (umn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, umn)) : P.lr;
+        float b2 = (ugn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, ugn)) : P.lr;
+        *rm = -mul(a, s1.beta1);
+        *rg = -mul(b2, s1.beta3);
+      }
+    };
+    auto needs_norms = [&](uint32_t phase) {
+      return (phase == kPhaseB && s1.normalize) || phase == kPhaseC;
+    };
+    // lane 0: second arrival of stage `slot` with the final multipliers
+    auto resolve_stage = [&](uint32_t slot, uint32_t phase, const uint4& nrm) {
+      float cs, rm, rg;
+      ratios(phase, nrm, &cs, &rm, &rg);
+      StageMeta& mt = s_meta[slot];
+      mt.cs = cs;
+      mt.ratio_m = rm;
+      mt.ratio_g = rg;
+      mbar_arrive(bar_full + 8 * slot);
+    };
+    // lane 0: resolve the oldest pending stage, waiting (bounded) for its norms if need be,
+    // then every following pending stage that the same norms settle.
+    auto resolve_oldest = [&]() -> int {
+      LANS_STAT_BEGIN();
+      int bad = 0;
+      bool waited = false;
+      while (pend_count > 0) {
+        const PendStage ps = pend[pend_head];
+        const bool phase_c = ps.phase == kPhaseC;
+        const bool settled = !needs_norms(ps.phase) ||
+                             (known_t == ps.tensor && norms_final(known_nrm, phase_c));
+        if (!settled) {
+          if (waited) break;  // one blocking wait per call; the rest stays queued
+          uint4 nrm;
+          if (!wait_norms(P.ctl + ps.tensor, phase_c, &nrm, P.hdr, phase_c ? kErrWaitB : kErrWaitA,
+                          ps.ticket, P.wait_ns)) {
+            bad = 1;
+            break;
+          }
+          known_t = ps.tensor;
+          known_nrm = nrm;
+          waited = true;
+        }
+        resolve_stage(ps.slot, ps.phase, known_nrm);
+        pend_head = (pend_head + 1) % kStages;
+        --pend_count;
+        ++resolved_ctr;
+      }
+      LANS_STAT_END(st_flag);
+      return bad;
+    };
+
+    auto iteration = [&](uint32_t seq) -> bool {
+      uint32_t drawn = 0;
+      if (lane == 1) drawn = atomicAdd(&P.hdr->ticket, 1u);  // item seq + 3
       { LANS_STAT_BEGIN();
       if (lane == 0) {
-        cp_async_wait_all();               // copies started in the previous iteration
-        const uint32_t t_prev = tk_old;    // drawn in the previous iteration
-        tk_new = atomicAdd(&P.hdr->ticket, 1u);
-        fetch_item(seq + 2, t_prev);
+        cp_async_wait_all();  // copies of the previous iteration
+        fetch_item(seq + 2);  // its ticket was stored at the bottom of the previous iteration
         fetch_desc(seq + 1);
       }
       __syncwarp();
       LANS_STAT_END(st_x0); }
+      auto finish = [&]() {
+        if (lane == 1) chain[(seq + 3u) & 3u].ticket = drawn;
+        __syncwarp();
+      };
       const ChainSlot& c = chain[seq & 3u];
       const uint32_t ticket = c.ticket;
-      if (ticket >= P.nitems) return false;
+      if (ticket >= P.nitems) {
+        finish();
+        return false;
+      }
       const uint32_t tp = c.item.tensor_phase, chunk = c.item.chunk;
       const TensorDesc d = c.d;
-      uint4 nrm = *reinterpret_cast<const uint4*>(c.norm);
+      const uint4 nrm0 = *reinterpret_cast<const uint4*>(c.norm);  // as of one iteration ago
       const uint32_t t = tp & kTensorMask;
       const uint32_t phase = tp >> kPhaseShift;
-      LansCtl* ctl = P.ctl + t;
-
-      // B needs ||g|| (when gradients are normalised), C needs all four norms.  They were
-      // fetched an iteration ago; only if they were not final yet does lane 0 wait (bounded).
-      const bool need_wait = (phase == kPhaseB && s1.normalize && !norms_final(nrm, false)) ||
-                             (phase == kPhaseC && !norms_final(nrm, true));
-      if (need_wait) {
-        LANS_STAT_BEGIN();
-        if (lane == 0)
-          failed = wait_norms(ctl, phase == kPhaseC, &nrm, P.hdr,
-                              phase == kPhaseC ? kErrWaitB : kErrWaitA, ticket, P.wait_ns) ? 0 : 1;
-        failed = __shfl_sync(0xffffffffu, failed, 0);
-        nrm.x = __shfl_sync(0xffffffffu, nrm.x, 0);
-        nrm.y = __shfl_sync(0xffffffffu, nrm.y, 0);
-        nrm.z = __shfl_sync(0xffffffffu, nrm.z, 0);
-        nrm.w = __shfl_sync(0xffffffffu, nrm.w, 0);
-        LANS_STAT_END(st_flag);
-        if (failed) return false;
-      }
-      float cs = s1.gscale, ratio_m = 0.f, ratio_g = 0.f;
-      if (phase != kPhaseA) cs = s1.grad_multiplier(norm_value(nrm.x));
-      if (phase == kPhaseC) {  // multi_tensor_lans.cu:347-353
-        const float pn = norm_value(nrm.y), umn = norm_value(nrm.z), ugn = norm_value(nrm.w);
-        ratio_m = (umn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, umn)) : P.lr;
-        ratio_g = (ugn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, ugn)) : P.lr;
-        ratio_m = -mul(ratio_m, s1.beta1);
-        ratio_g = -mul(ratio_g, s1.beta3);
+      const bool want = needs_norms(phase);
+      const bool have = !want || norms_final(nrm0, phase == kPhaseC);
+      if (lane == 0 && want && have) {
+        known_t = t;
+        known_nrm = nrm0;
       }
 
       const int64_t start = (int64_t)chunk * kChunkElems;
@@ -451,18 +528,30 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
       for (int off = 0; off < len; off += stage_cap) {
         const uint32_t slot = stage_ctr % kStages;
         const uint32_t use = stage_ctr / kStages;
-        {
-          LANS_STAT_BEGIN();
-          if (lane == 0)
-            failed = ring_wait(bar_empty + 8 * slot, (use & 1u) ^ 1u, P.hdr, ticket, P.wait_ns) ? 0 : 1;
-          failed = __shfl_sync(0xffffffffu, failed, 0);
-          LANS_STAT_END(st_empty);
+        // A free slot: take it.  None free: settle pending stages first (their consumers
+        // are what frees slots), and only with nothing pending wait for the consumers.
+        if (lane == 0) {
+          const uint32_t eb = bar_empty + 8 * slot, par = (use & 1u) ^ 1u;
+          while (!failed && !mbar_try_wait(eb, par)) {
+            if (pend_count > 0) {
+              failed = resolve_oldest();
+            } else {
+              LANS_STAT_BEGIN();
+              failed = ring_wait(eb, par, P.hdr, ticket, P.wait_ns) ? 0 : 1;
+              LANS_STAT_END(st_empty);
+              break;
+            }
+          }
         }
-        if (failed) return false;
+        failed = __shfl_sync(0xffffffffu, failed, 0);
+        if (failed) {
+          finish();
+          return false;
+        }
         const int n = (len - off) < stage_cap ? (len - off) : stage_cap;
         const int nbulk = bulk_ok ? (n / gran) * gran : 0;
         const uint32_t full = bar_full + 8 * slot;
-        LANS_STAT_BEGIN();
+        { LANS_STAT_BEGIN();
         if (lane == 0) {
           StageMeta& mt = s_meta[slot];
           const int64_t e = start + off;
@@ -479,18 +568,28 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
           mt.part_index = d.first_chunk + chunk;
           mt.nchunks = d.nchunks;
           mt.first_chunk = d.first_chunk;
-          mt.cs = cs;
-          mt.ratio_m = ratio_m;
-          mt.ratio_g = ratio_g;
           if (nbulk > 0) {
             const uint32_t gb = (uint32_t)nbulk * (uint32_t)sizeof(GT), fb = (uint32_t)nbulk * 4u;
-            mbar_arrive_expect_tx(full, phase == kPhaseA ? gb : gb + 3u * fb);
+            mbar_arrive_expect_tx(full, phase == kPhaseA ? gb : gb + 3u * fb);  // arrival 1 of 2
           } else {
             mbar_arrive(full);
           }
+          // arrival 2 of 2: now if the norms are known, later otherwise
+          const bool settled = !want || (known_t == t && norms_final(known_nrm, phase == kPhaseC));
+          if (settled && pend_count == 0) {
+            resolve_stage(slot, phase, known_nrm);
+            ++resolved_ctr;
+          } else {
+            PendStage& ps = pend[(pend_head + pend_count) % kStages];
+            ps.slot = slot;
+            ps.phase = phase;
+            ps.tensor = t;
+            ps.ticket = ticket;
+            ++pend_count;
+          }
         }
         __syncwarp();
-        LANS_STAT_END(st_x1);
+        LANS_STAT_END(st_x2); }
         {
           LANS_STAT_BEGIN();
           if (my_copy && nbulk > 0)
@@ -502,12 +601,16 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
         }
         ++stage_ctr;
       }
+      finish();
       return true;
     };
-    for (uint32_t seq = 0;; seq += 2) {
-      if (!iteration(std::false_type{}, seq)) break;
-      if (!iteration(std::true_type{}, seq + 1)) break;
+    for (uint32_t seq = 0; iteration(seq); ++seq) {
     }
+    // settle what is still pending (each wait is bounded)
+    if (lane == 0) {
+      while (!failed && pend_count > 0) failed = resolve_oldest();
+    }
+    failed = __shfl_sync(0xffffffffu, failed, 0);
     if (lane == 0) cp_async_wait_all();  // nothing of this thread may still be in flight
 #ifdef RAFB200_LANS_STATS
     st_total = (unsigned long long)(clock64() - prod_t0);
@@ -519,6 +622,8 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
       atomicAdd(P.stats + 4, 1ull);
       atomicAdd(P.stats + 7, st_x0);
       atomicAdd(P.stats + 8, st_x1);
+      atomicAdd(P.stats + 9, st_x2);
+      atomicAdd(P.stats + 10, st_x3);
     }
 #endif
     // Terminator.  Every stage published before it is consumed (its copies have
@@ -528,6 +633,7 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
       if (ring_wait(bar_empty + 8 * slot, ((stage_ctr / kStages) & 1u) ^ 1u, P.hdr, kTicketEnd,
                     P.wait_ns)) {
         s_meta[slot].ticket = kTicketEnd;
+        mbar_arrive(bar_full + 8 * slot);
         mbar_arrive(bar_full + 8 * slot);
       }
     }
@@ -542,8 +648,7 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
       const RedSlot& rs = s_red[buf];
       const uint32_t phase = rs.phase;
       if (phase == kRedEnd) return;
-      const uint32_t t = rs.tensor, part_index = rs.part_index, nchunks = rs.nchunks,
-                     first_chunk = rs.first_chunk;
+      const uint32_t t = rs.tensor, nchunks = rs.nchunks;
       const int nq = (phase == kPhaseA) ? 1 : 3;
       float sum = 0.f;
       if (lane < nq) {
@@ -553,47 +658,26 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
       __syncwarp();
       if (lane == 0) mbar_arrive(red_empty + 8 * buf);  // the slot has been read
       // lane q owns quantity q: A -> ||g||^2 ; B -> ||p||^2, ||update_m||^2, ||update_g||^2
-      float* part = (phase == kPhaseA) ? P.part_a : P.part_b + (size_t)lane * P.total_chunks;
+      LansCtl* ctl = P.ctl + t;
+      const int word = (phase == kPhaseA) ? 0 : 1 + lane;
       if (lane < nq) {
-        part[part_index] = sum;
+        atomicAdd(&ctl->sumsq[word], (double)sum);
         __threadfence();
       }
       __syncwarp();
-      LansCtl* ctl = P.ctl + t;
       unsigned is_last = 0;
       if (lane == 0) {
         const unsigned old = atomicAdd(phase == kPhaseA ? &ctl->arrived_a : &ctl->arrived_b, 1u);
         is_last = (old + 1u == nchunks);
       }
       is_last = __shfl_sync(0xffffffffu, is_last, 0);
-      if (is_last) {
-        // Last chunk of the tensor: add all chunk partials, lane-strided then a shuffle
-        // tree - a fixed order, so the norm is reproducible bit for bit.
+      if (is_last && lane < nq) {
+        // Every chunk of the tensor has been added: publish the norm, value and
+        // "final" bit in one word.
         __threadfence();
-        float tot[3] = {0.f, 0.f, 0.f};
-        for (uint32_t j = lane; j < nchunks; j += 32) {
-          const uint32_t ci = first_chunk + j;
-          if (phase == kPhaseA) {
-            tot[0] += __ldcg(P.part_a + ci);
-          } else {
-            tot[0] += __ldcg(P.part_b + ci);
-            tot[1] += __ldcg(P.part_b + P.total_chunks + ci);
-            tot[2] += __ldcg(P.part_b + 2 * (size_t)P.total_chunks + ci);
-          }
-        }
-        tot[0] = warp_sum(tot[0]);
-        tot[1] = warp_sum(tot[1]);
-        tot[2] = warp_sum(tot[2]);
-        if (lane == 0) {
-          volatile unsigned* nw = ctl->norm;  // value and "final" bit in one word each
-          if (phase == kPhaseA) {
-            nw[0] = __float_as_uint(sqrtf(tot[0])) | kNormValid;
-          } else {
-            nw[1] = __float_as_uint(sqrtf(tot[0])) | kNormValid;
-            nw[2] = __float_as_uint(sqrtf(tot[1])) | kNormValid;
-            nw[3] = __float_as_uint(sqrtf(tot[2])) | kNormValid;
-          }
-        }
+        const double total = *reinterpret_cast<volatile double*>(&ctl->sumsq[word]);
+        *reinterpret_cast<volatile unsigned*>(&ctl->norm[word]) =
+            __float_as_uint(sqrtf((float)total)) | kNormValid;
       }
     }
   }
@@ -796,8 +880,13 @@ std::vector<Item> build_lans_schedule(const std::vector<uint32_t>& nchunks, bool
   skip_empty(B);
   skip_empty(Cc);
   std::vector<int64_t> done_a(k, -1), done_b(k, -1);
+  // Phase B walks a tensor front to back, phases A and C back to front: the chunks a
+  // pass touches first are the ones the previous pass over the same tensor touched
+  // last, i.e. the ones most likely to still be in L2 when the tensor is larger than
+  // what L2 holds.
   auto emit = [&](Cursor& cur, int phase, std::vector<int64_t>* done) {
-    out.push_back(Item{((uint32_t)phase << kPhaseShift) | (uint32_t)cur.t, cur.c});
+    const uint32_t chunk = (phase == kPhaseB) ? cur.c : nchunks[cur.t] - 1u - cur.c;
+    out.push_back(Item{((uint32_t)phase << kPhaseShift) | (uint32_t)cur.t, chunk});
     cur.emitted++;
     if (++cur.c == nchunks[cur.t]) {
       if (done) (*done)[cur.t] = (int64_t)out.size();
@@ -830,10 +919,8 @@ std::vector<Item> build_lans_schedule(const std::vector<uint32_t>& nchunks, bool
 size_t lans_ctl_bytes(int k) { return 64 + sizeof(LansCtl) * (size_t)k; }
 
 size_t lans_workspace_bytes(int k, uint32_t total_chunks) {
-  size_t b = lans_ctl_bytes(k);
-  b = (b + 255) & ~(size_t)255;
-  b += sizeof(float) * 4 * (size_t)total_chunks;
-  return (b + 255) & ~(size_t)255;
+  (void)total_chunks;  // partial sums are accumulated per tensor, not stored per chunk
+  return (lans_ctl_bytes(k) + 255) & ~(size_t)255;
 }
 
 template <typename GT, typename OT>
@@ -907,10 +994,6 @@ int rafb200_lans(rafb200_tensor_list_t list, int step, const float* step_dev, fl
   char* ws = static_cast<char*>(workspace);
   P.hdr = reinterpret_cast<LansHeader*>(ws);
   P.ctl = reinterpret_cast<LansCtl*>(ws + 64);
-  size_t off = (lans_ctl_bytes(list->k) + 255) & ~(size_t)255;
-  P.part_a = reinterpret_cast<float*>(ws + off);
-  P.part_b = P.part_a + list->total_chunks;
-  P.total_chunks = list->total_chunks;
   P.s1.beta1 = beta1;
   P.s1.beta2 = beta2;
   P.s1.beta3 = (grad_averaging == 1) ? 1 - beta1 : 1.0f;  // lans.cc:106-109
@@ -932,17 +1015,18 @@ int rafb200_lans(rafb200_tensor_list_t list, int step, const float* step_dev, fl
 #ifdef RAFB200_LANS_STATS
   {
     static unsigned long long* dev_stats = nullptr;
-    unsigned long long host[10];
+    unsigned long long host[12];
     if (!dev_stats) {
       cudaMalloc(&dev_stats, sizeof(host));
     } else {
       cudaMemcpy(host, dev_stats, sizeof(host), cudaMemcpyDeviceToHost);
       const double nb = host[4] ? (double)host[4] : 1.0;
       fprintf(stderr, "[lans stats] producer: total %.0f cyc/block, empty-wait %.1f%%, flag-wait %.1f%%, "
-              "tma-issue %.1f%%, chain %.1f%%, meta %.1f%%; consumer: total %.0f cyc/block, full-wait %.1f%%\n",
+              "tma-issue %.1f%%, chain %.1f%%, setup(incl flag-wait) %.1f%%, meta %.1f%%, finish %.1f%%; consumer: total %.0f cyc/block, full-wait %.1f%%\n",
               host[0] / nb, 100.0 * host[1] / (host[0] + 1.0), 100.0 * host[2] / (host[0] + 1.0),
               100.0 * host[3] / (host[0] + 1.0), 100.0 * host[7] / (host[0] + 1.0),
-              100.0 * host[8] / (host[0] + 1.0), host[5] / nb, 100.0 * host[6] / (host[5] + 1.0));
+              100.0 * host[8] / (host[0] + 1.0), 100.0 * host[9] / (host[0] + 1.0),
+              100.0 * host[10] / (host[0] + 1.0), host[5] / nb, 100.0 * host[6] / (host[5] + 1.0));
     }
     cudaMemset(dev_stats, 0, sizeof(host));
     P.stats = dev_stats;
