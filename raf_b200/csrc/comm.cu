@@ -257,8 +257,8 @@ static int local_copy(const void* src, void* dst, size_t bytes, cudaStream_t s) 
 int rafb200_allreduce(rafb200_comm_t c, const void* sendbuf, void* recvbuf, int64_t count,
                       int dtype, const char* computation, void* stream) {
   RAFB200_REQUIRE(c && count >= 0, "rafb200_allreduce: bad arguments");
-  ncclDataType_t dt;
-  ncclRedOp_t op;
+  ncclDataType_t dt = ncclFloat32;
+  ncclRedOp_t op = ncclSum;
   int rc = to_nccl_dtype(dtype, &dt);
   if (rc == RAFB200_OK) rc = to_nccl_op(computation, &op);
   if (rc != RAFB200_OK) return rc;
@@ -273,8 +273,8 @@ int rafb200_group_reduce_scatter(rafb200_comm_t c, int k, const void* const* sen
                                  const char* computation, void* stream) {
   RAFB200_REQUIRE(c && k >= 0 && (k == 0 || (sendbuf && recvbuf && recvcount)),
                   "rafb200_group_reduce_scatter: bad arguments");
-  ncclDataType_t dt;
-  ncclRedOp_t op;
+  ncclDataType_t dt = ncclFloat32;
+  ncclRedOp_t op = ncclSum;
   int rc = to_nccl_dtype(dtype, &dt);
   if (rc == RAFB200_OK) rc = to_nccl_op(computation, &op);
   if (rc != RAFB200_OK) return rc;
@@ -310,7 +310,7 @@ int rafb200_group_allgather(rafb200_comm_t c, int k, const void* const* sendbuf,
                             void* stream) {
   RAFB200_REQUIRE(c && k >= 0 && (k == 0 || (sendbuf && recvbuf && sendcount)),
                   "rafb200_group_allgather: bad arguments");
-  ncclDataType_t dt;
+  ncclDataType_t dt = ncclFloat32;
   int rc = to_nccl_dtype(dtype, &dt);
   if (rc != RAFB200_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

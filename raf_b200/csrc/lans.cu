@@ -47,16 +47,8 @@ struct LansParams {
   const float* step_dev;
   int bias_correction;
   uint64_t wait_ns;  // bound of every wait inside the kernel
-  unsigned long long* stats;  // development builds only (RAFB200_LANS_STATS): cycle counters
 };
 
-#ifdef RAFB200_LANS_STATS
-#define LANS_STAT_BEGIN() const long long stat_t0__ = clock64()
-#define LANS_STAT_END(acc) (acc) += (unsigned long long)(clock64() - stat_t0__)
-#else
-#define LANS_STAT_BEGIN() ((void)0)
-#define LANS_STAT_END(acc) ((void)0)
-#endif
 
 __device__ __forceinline__ uint64_t global_ns() {
   uint64_t t;
@@ -365,11 +357,6 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
     const uint64_t pol_keep = make_policy_keep(), pol_stream = make_policy_stream();
     uint32_t stage_ctr = 0;
     int failed = 0;
-    unsigned long long st_empty = 0, st_flag = 0, st_pref = 0, st_total = 0, st_x0 = 0, st_x1 = 0, st_x2 = 0, st_x3 = 0;
-    (void)st_empty; (void)st_flag; (void)st_pref; (void)st_total; (void)st_x0; (void)st_x1; (void)st_x2; (void)st_x3;
-#ifdef RAFB200_LANS_STATS
-    const long long prod_t0 = clock64();
-#endif
     ChainSlot* chain = reinterpret_cast<ChainSlot*>(smem + L::kChainOff);
     auto fetch_item = [&](uint32_t seq) {  // lane 0; the slot's ticket has been stored
       ChainSlot& c = chain[seq & 3u];
@@ -448,7 +435,6 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
     // lane 0: resolve the oldest pending stage, waiting (bounded) for its norms if need be,
     // then every following pending stage that the same norms settle.
     auto resolve_oldest = [&]() -> int {
-      LANS_STAT_BEGIN();
       int bad = 0;
       bool waited = false;
       while (pend_count > 0) {
@@ -473,21 +459,20 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
         --pend_count;
         ++resolved_ctr;
       }
-      LANS_STAT_END(st_flag);
       return bad;
     };
 
     auto iteration = [&](uint32_t seq) -> bool {
       uint32_t drawn = 0;
       if (lane == 1) drawn = atomicAdd(&P.hdr->ticket, 1u);  // item seq + 3
-      { LANS_STAT_BEGIN();
+      {
       if (lane == 0) {
         cp_async_wait_all();  // copies of the previous iteration
         fetch_item(seq + 2);  // its ticket was stored at the bottom of the previous iteration
         fetch_desc(seq + 1);
       }
       __syncwarp();
-      LANS_STAT_END(st_x0); }
+        }
       auto finish = [&]() {
         if (lane == 1) chain[(seq + 3u) & 3u].ticket = drawn;
         __syncwarp();
@@ -536,9 +521,7 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
             if (pend_count > 0) {
               failed = resolve_oldest();
             } else {
-              LANS_STAT_BEGIN();
               failed = ring_wait(eb, par, P.hdr, ticket, P.wait_ns) ? 0 : 1;
-              LANS_STAT_END(st_empty);
               break;
             }
           }
@@ -551,7 +534,7 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
         const int n = (len - off) < stage_cap ? (len - off) : stage_cap;
         const int nbulk = bulk_ok ? (n / gran) * gran : 0;
         const uint32_t full = bar_full + 8 * slot;
-        { LANS_STAT_BEGIN();
+        {
         if (lane == 0) {
           StageMeta& mt = s_meta[slot];
           const int64_t e = start + off;
@@ -589,15 +572,13 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
           }
         }
         __syncwarp();
-        LANS_STAT_END(st_x2); }
+        }
         {
-          LANS_STAT_BEGIN();
           if (my_copy && nbulk > 0)
             tma_load_1d(data_base + slot * L::kStageBytes + my_dst_off,
                         my_src + (start + off) * (int64_t)my_esize, (uint32_t)nbulk * my_esize, full,
                         pol);
           __syncwarp();
-          LANS_STAT_END(st_pref);
         }
         ++stage_ctr;
       }
@@ -612,20 +593,6 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
     }
     failed = __shfl_sync(0xffffffffu, failed, 0);
     if (lane == 0) cp_async_wait_all();  // nothing of this thread may still be in flight
-#ifdef RAFB200_LANS_STATS
-    st_total = (unsigned long long)(clock64() - prod_t0);
-    if (P.stats && lane == 0) {
-      atomicAdd(P.stats + 0, st_total);
-      atomicAdd(P.stats + 1, st_empty);
-      atomicAdd(P.stats + 2, st_flag);
-      atomicAdd(P.stats + 3, st_pref);
-      atomicAdd(P.stats + 4, 1ull);
-      atomicAdd(P.stats + 7, st_x0);
-      atomicAdd(P.stats + 8, st_x1);
-      atomicAdd(P.stats + 9, st_x2);
-      atomicAdd(P.stats + 10, st_x3);
-    }
-#endif
     // Terminator.  Every stage published before it is consumed (its copies have
     // landed) before the consumers see it, so nothing is in flight when they leave.
     if (lane == 0) {
@@ -718,17 +685,12 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
     ++red_ctr;
   };
 
-  unsigned long long st_full = 0, st_hand = 0;
-  (void)st_full; (void)st_hand;
-#ifdef RAFB200_LANS_STATS
-  const long long cons_t0 = clock64();
-#endif
   for (uint32_t stage_ctr = 0;; ++stage_ctr) {
     const uint32_t slot = stage_ctr % kStages;
-    { LANS_STAT_BEGIN();
+    {
     if (!ring_wait(bar_full + 8 * slot, (stage_ctr / kStages) & 1u, P.hdr, stage_ctr, P.wait_ns))
       break;
-    LANS_STAT_END(st_full); }
+        }
     const StageMeta& mt = s_meta[slot];
     if (mt.ticket == kTicketEnd) break;
     const uint32_t phase = mt.flags & 3u;
@@ -843,12 +805,6 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
       }
     }
   }
-#ifdef RAFB200_LANS_STATS
-  if (P.stats && tid == 0) {
-    atomicAdd(P.stats + 5, (unsigned long long)(clock64() - cons_t0));
-    atomicAdd(P.stats + 6, st_full);
-  }
-#endif
   // No more stages (or a wait expired): release the publisher.
   hand_over(kRedEnd, 0, 0, 0, 0);
 }
@@ -1011,27 +967,6 @@ int rafb200_lans(rafb200_tensor_list_t list, int step, const float* step_dev, fl
   P.step_dev = step_dev;
   P.bias_correction = bias_correction;
   P.wait_ns = 2000000000ull;  // two seconds: far beyond any legitimate wait
-  P.stats = nullptr;
-#ifdef RAFB200_LANS_STATS
-  {
-    static unsigned long long* dev_stats = nullptr;
-    unsigned long long host[12];
-    if (!dev_stats) {
-      cudaMalloc(&dev_stats, sizeof(host));
-    } else {
-      cudaMemcpy(host, dev_stats, sizeof(host), cudaMemcpyDeviceToHost);
-      const double nb = host[4] ? (double)host[4] : 1.0;
-      fprintf(stderr, "[lans stats] producer: total %.0f cyc/block, empty-wait %.1f%%, flag-wait %.1f%%, "
-              "tma-issue %.1f%%, chain %.1f%%, setup(incl flag-wait) %.1f%%, meta %.1f%%, finish %.1f%%; consumer: total %.0f cyc/block, full-wait %.1f%%\n",
-              host[0] / nb, 100.0 * host[1] / (host[0] + 1.0), 100.0 * host[2] / (host[0] + 1.0),
-              100.0 * host[3] / (host[0] + 1.0), 100.0 * host[7] / (host[0] + 1.0),
-              100.0 * host[8] / (host[0] + 1.0), 100.0 * host[9] / (host[0] + 1.0),
-              100.0 * host[10] / (host[0] + 1.0), host[5] / nb, 100.0 * host[6] / (host[5] + 1.0));
-    }
-    cudaMemset(dev_stats, 0, sizeof(host));
-    P.stats = dev_stats;
-  }
-#endif
 
   RAFB200_CUDA(cudaMemsetAsync(workspace, 0, lans_ctl_bytes(list->k), s));
   if (step_dev) {
