@@ -203,7 +203,7 @@ def run_reference_arm(args, wl):
     line = {
         "impl": "reference", "metric": "ZeRO optimizer-step param-elements/s", "value": val,
         "unit": "param-elements/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * total / val, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": 1e3 * total / val, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": wl["label"], "note": "CPU host cores; ms_per_step extrapolated from the sample to the full parameter count"},
         "cpu_baseline": {**samples, "value": val},
