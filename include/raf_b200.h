@@ -154,6 +154,37 @@ RAFB200_API int rafb200_lans_status(rafb200_tensor_list_t list, const void* work
                                     float* norms_host, void* stream);
 
 /*
+ * LANS update of ONE tensor without any device allocation, by the library or by
+ * the caller.  This entry point has no counterpart in the reference, whose
+ * operator always requests a workspace from the memory pool
+ * (src/op/dialect/cuda/lans.cc:66-78).  It is for callers that cannot allocate
+ * at the point of the call: code running while the memory pool is being torn
+ * down or is exhausted, or inside a region where the allocator must stay
+ * untouched.  The arithmetic, kernel and argument meaning are those of
+ * rafb200_lans on a one-tensor list (p, m, v fp32, updated in place; g of
+ * g_dtype; out NULL or of out_dtype); the header, control words, descriptor row
+ * and work-item table that rafb200_lans keeps in its workspace and list object
+ * live in a fixed device array that is part of the library image instead.
+ *   - Limit: numel <= 4,194,304 (4 Mi elements, the size the 25 KB array is laid
+ *     out for).  Larger tensors are refused with RAFB200_INVALID_ARGUMENT; use
+ *     rafb200_lans for them.  `step` is a host integer.
+ *   - The first call on each device looks up the array's device address (once,
+ *     with that device current).  Make that first call during set-up, before
+ *     any stream capture is begun.
+ *   - All calls on one device share the one array: two calls whose work may
+ *     overlap in time (different streams, different threads) race on it.  Order
+ *     them on one stream, or with events.
+ *   - It reports bounded-wait expiry only through the error word inside the
+ *     array; synchronise the stream and compare results if that matters.
+ */
+RAFB200_API int rafb200_lans_tensor_static(const void* g, int g_dtype, float* p, float* m,
+                                           float* v, void* out, int out_dtype, int64_t numel,
+                                           int step, float learning_rate, float beta1,
+                                           float beta2, float eps, int bias_correction,
+                                           float weight_decay, int grad_averaging, int mode,
+                                           int normalize_grad, float grad_scale, void* stream);
+
+/*
  * Adam / AdamW.  The reference has NO Adam operator; schema modelled on
  * raf.op.lans, arithmetic = LANS stage 1 without gradient normalisation and
  * trust ratios (multi_tensor_lans.cu:281-306):

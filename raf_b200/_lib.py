@@ -54,6 +54,8 @@ SIGNATURES = {
     "rafb200_lans_workspace_bytes": (_sz, [_vp]),
     "rafb200_lans": (_i, [_vp, _i, _vp, _f, _f, _f, _f, _i, _f, _i, _i, _i, _f, _vp, _sz, _vp]),
     "rafb200_lans_status": (_i, [_vp, _vp, _vp, _vp]),
+    "rafb200_lans_tensor_static": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _i64, _i, _f, _f, _f, _f,
+                                        _i, _f, _i, _i, _i, _f, _vp]),
     "rafb200_adam": (_i, [_vp, _i, _vp, _f, _f, _f, _f, _i, _f, _i, _f, _vp]),
     "rafb200_cast": (_i, [_vp, _i, _vp, _i, _i64, _vp]),
     "rafb200_group_cast": (_i, [_i, _vp, _i, _vp, _i, _vp, _vp]),

@@ -915,6 +915,22 @@ static int launch_lans_g(const rafb200_tensor_list_s* l, const LansParams& P, cu
 
 using namespace rafb200;
 
+// ---- scratch of rafb200_lans_tensor_static --------------------------------------
+// Everything rafb200_lans keeps in caller-provided device memory (header, per-tensor
+// control words, descriptor row, work-item table) for ONE tensor of at most
+// kStaticMaxElems elements, as a statically allocated device array: every GPU that
+// loads this library holds these 25 KB until the process exits.
+constexpr int64_t kStaticMaxElems = 4ll << 20;                          // 4,194,304 elements
+constexpr uint32_t kStaticMaxChunks = (uint32_t)(kStaticMaxElems / kChunkElems);  // 1024
+constexpr size_t kStaticCtlOff = 64, kStaticDescOff = 256, kStaticItemsOff = 512;
+constexpr size_t kStaticBytes = kStaticItemsOff + 3 * (size_t)kStaticMaxChunks * sizeof(Item);
+static __device__ __align__(256) unsigned char g_lans_static_scratch[kStaticBytes];
+
+// Device address of the array above, per device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use: the address has
+// to be asked for, once per device, with that device current.
+static void* g_lans_static_ptr[64] = {nullptr};
+
 extern "C" {
 
 size_t rafb200_lans_workspace_bytes(rafb200_tensor_list_t list) {
@@ -977,6 +993,99 @@ int rafb200_lans(rafb200_tensor_list_t list, int step, const float* step_dev, fl
     case RAFB200_F32: return launch_lans_g<float>(list, P, s);
     case RAFB200_F16: return launch_lans_g<__half>(list, P, s);
     default: return launch_lans_g<__nv_bfloat16>(list, P, s);
+  }
+}
+
+int rafb200_lans_tensor_static(const void* g, int g_dtype, float* p, float* m, float* v,
+                               void* out, int out_dtype, int64_t numel, int step,
+                               float learning_rate, float beta1, float beta2, float eps,
+                               int bias_correction, float weight_decay, int grad_averaging,
+                               int mode, int normalize_grad, float grad_scale, void* stream) {
+  RAFB200_REQUIRE(dtype_valid(g_dtype) && dtype_valid(out_dtype),
+                  "rafb200_lans_tensor_static: bad dtype");
+  RAFB200_REQUIRE(numel >= 0, "rafb200_lans_tensor_static: negative numel");
+  RAFB200_REQUIRE(numel <= kStaticMaxElems,
+                  "rafb200_lans_tensor_static: %lld elements exceed the static scratch, which is "
+                  "sized for at most %lld; use rafb200_lans with a caller-provided workspace",
+                  (long long)numel, (long long)kStaticMaxElems);
+  RAFB200_REQUIRE(step >= 1, "rafb200_lans_tensor_static: step counts from 1");
+  RAFB200_REQUIRE(mode == 0 || mode == 1, "rafb200_lans_tensor_static: mode must be 0 or 1");
+  if (numel == 0) return RAFB200_OK;
+  RAFB200_REQUIRE(g && p && m && v, "rafb200_lans_tensor_static: g, p, m and v must not be NULL");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  int device = 0;
+  RAFB200_CUDA(cudaGetDevice(&device));
+  RAFB200_REQUIRE(device >= 0 && device < 64, "rafb200_lans_tensor_static: device %d out of range", device);
+  if (g_lans_static_ptr[device] == nullptr) {
+    // First call on this device (do it before any stream capture): resolve the symbol.
+    void* ptr = nullptr;
+    RAFB200_CUDA(cudaGetSymbolAddress(&ptr, g_lans_static_scratch));
+    g_lans_static_ptr[device] = ptr;
+  }
+  char* ws = static_cast<char*>(g_lans_static_ptr[device]);
+
+  // One-tensor list on the host stack: nothing here touches a device allocator.
+  rafb200_tensor_list_s one;
+  one.k = 1;
+  one.g_dtype = g_dtype;
+  one.out_dtype = out_dtype;
+  one.device = device;
+  RAFB200_CUDA(cudaDeviceGetAttribute(&one.sm_count, cudaDevAttrMultiProcessorCount, device));
+  TensorDesc d{};
+  d.g = g;
+  d.p = p;
+  d.m = m;
+  d.v = v;
+  d.out = out;
+  d.numel = numel;
+  d.first_chunk = 0;
+  d.nchunks = (uint32_t)((numel + kChunkElems - 1) / kChunkElems);
+  auto a16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+  const bool vec_ok = a16(p) && a16(m) && a16(v) &&
+                      (reinterpret_cast<uintptr_t>(g) % (g_dtype == RAFB200_F32 ? 16 : 8) == 0) &&
+                      (!out || reinterpret_cast<uintptr_t>(out) % (out_dtype == RAFB200_F32 ? 16 : 8) == 0);
+  d.flags = vec_ok ? kFlagAligned : 0u;
+  if (vec_ok && a16(g)) d.flags |= kFlagBulk;
+  const std::vector<Item> items =
+      build_lans_schedule(std::vector<uint32_t>{d.nchunks}, normalize_grad != 0,
+                          (int64_t)kStaticMaxChunks, 0);
+
+  LansParams P;
+  P.descs = reinterpret_cast<const TensorDesc*>(ws + kStaticDescOff);
+  P.items = reinterpret_cast<const Item*>(ws + kStaticItemsOff);
+  P.nitems = (uint32_t)items.size();
+  P.hdr = reinterpret_cast<LansHeader*>(ws);
+  P.ctl = reinterpret_cast<LansCtl*>(ws + kStaticCtlOff);
+  P.s1.beta1 = beta1;
+  P.s1.beta2 = beta2;
+  P.s1.beta3 = (grad_averaging == 1) ? 1 - beta1 : 1.0f;
+  P.s1.one_minus_beta2 = 1 - beta2;
+  P.s1.eps = eps;
+  float bc1, bc2;
+  bias_corrections(beta1, beta2, step, bias_correction, &bc1, &bc2);
+  P.s1.inv_bc1 = 1.0f / bc1;
+  P.s1.inv_bc2 = 1.0f / bc2;
+  P.s1.wd = weight_decay;
+  P.s1.gscale = grad_scale;
+  P.s1.mode = mode;
+  P.s1.normalize = normalize_grad ? 1 : 0;
+  P.lr = learning_rate;
+  P.step_dev = nullptr;
+  P.bias_correction = bias_correction;
+  P.wait_ns = 2000000000ull;
+
+  // The array keeps whatever the previous call left in it: ticket counter, error word,
+  // arrival counters, sums and norm words must start at zero; descriptor and item table
+  // are rewritten.  (Pageable sources: the runtime stages them before returning.)
+  RAFB200_CUDA(cudaMemsetAsync(ws, 0, kStaticCtlOff + sizeof(LansCtl), s));
+  RAFB200_CUDA(cudaMemcpyAsync(ws + kStaticDescOff, &d, sizeof(d), cudaMemcpyHostToDevice, s));
+  RAFB200_CUDA(cudaMemcpyAsync(ws + kStaticItemsOff, items.data(), items.size() * sizeof(Item),
+                               cudaMemcpyHostToDevice, s));
+  switch (g_dtype) {
+    case RAFB200_F32: return launch_lans_g<float>(&one, P, s);
+    case RAFB200_F16: return launch_lans_g<__half>(&one, P, s);
+    default: return launch_lans_g<__nv_bfloat16>(&one, P, s);
   }
 }
 
