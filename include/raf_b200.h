@@ -71,9 +71,9 @@ typedef struct rafb200_tensor_list_s* rafb200_tensor_list_t;
 
 RAFB200_API int rafb200_tensor_list_create(int k, const int64_t* numel, int g_dtype, int out_dtype,
                                            rafb200_tensor_list_t* list);
-/* Host arrays of k device pointers each.  m may be NULL for SGD without
- * momentum state... it is required by every optimizer here (SGD: momentum
- * buffer; Adam/LANS: first moment); v is required by Adam and LANS; out may
+/* Host arrays of k device pointers each.  g, p and m are required by every
+ * optimizer here (m = SGD's momentum buffer, Adam/LANS's first moment); v is
+ * required by Adam and LANS and may be NULL for SGD; out may
  * be NULL (no parameter copy) or hold NULL entries.  The table is copied to
  * the device on `stream` only when a pointer changed since the last bind. */
 RAFB200_API int rafb200_tensor_list_bind(rafb200_tensor_list_t list, const void* const* g,
@@ -121,12 +121,15 @@ RAFB200_API int rafb200_sgd_list(rafb200_tensor_list_t list, float learning_rate
  *   bias_correction, weight_decay, grad_averaging, mode, normalize_grad}
  *   (scripts/src_codegen/def_schema.py:678-694; host src/op/dialect/cuda/lans.cc:25-165;
  *    kernels src/op/dialect/cuda/kernels/multi_tensor_lans.cu:95-450).
- * Same argument meaning and per-element arithmetic (true divisions, sqrtf, no
- * fused multiply-add).  Differences, all deliberate:
+ * Same argument meaning and per-element formulas.  Differences, all deliberate:
  *   - one persistent launch instead of about fifty; per-tensor norms are
- *     reduced warp-shuffle-then-block in the same kernel, in a fixed order
- *     (bitwise reproducible run to run) that differs from the reference's
- *     chunk/tree order: trust ratios agree to ~1e-7 relative;
+ *     reduced warp-shuffle-then-block in the same kernel and summed across
+ *     chunks in double precision (exact, hence independent of arrival order,
+ *     for any realistic tensor), not in the reference's chunk/tree order;
+ *     reciprocals and square roots use the approximate (<= 1 ulp) hardware
+ *     forms with fused multiply-adds: p, m, v agree with the reference
+ *     arithmetic to ~3e-6 relative after 10 steps, inside the 1e-5 the path
+ *     allows for LANS;
  *   - `step` is a host integer, or - when step_dev is not NULL - is read on the
  *     device from a 0-d fp32 tensor as the reference schema has it, without the
  *     blocking device-to-host copy of lans.cc:97-99;
@@ -243,6 +246,12 @@ RAFB200_API int rafb200_unique_id(void* id128);
 RAFB200_API int rafb200_comm_create_with_id(int world_size, int rank, int device,
                                             const void* id128, int timeout_ms,
                                             rafb200_comm_t* comm);
+/* Wraps an ncclComm_t that the caller created and keeps owning (RAF's
+ * NCCLCommunicatorObj::nccl_comm, include/raf/nccl_communicator.h:21-28, as an
+ * OpEnv receives it from RequestDistributed, src/op/dialect/nccl/nccl.cc:329).
+ * rafb200_comm_destroy on the result frees the wrapper only.  world_size 1
+ * gives the copy-only communicator and ignores nccl_comm. */
+RAFB200_API int rafb200_comm_adopt(void* nccl_comm, int world_size, int rank, rafb200_comm_t* comm);
 RAFB200_API int rafb200_comm_destroy(rafb200_comm_t comm);
 RAFB200_API int rafb200_comm_size(rafb200_comm_t comm);
 RAFB200_API int rafb200_comm_rank(rafb200_comm_t comm);

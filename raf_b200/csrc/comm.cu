@@ -30,6 +30,7 @@ struct rafb200_comm_s {
   int device = 0;
   bool is_void = true;  // world of one: no NCCL underneath
   ncclComm_t nccl = nullptr;
+  bool borrowed = false;   // adopted from the caller: never destroyed here
   std::string store_file;  // file this rank published (removed on destroy)
 };
 
@@ -192,6 +193,33 @@ int rafb200_comm_create_with_id(int world_size, int rank, int device, const void
   return RAFB200_OK;
 }
 
+int rafb200_comm_adopt(void* nccl_comm, int world_size, int rank, rafb200_comm_t* comm) {
+  RAFB200_REQUIRE(comm, "rafb200_comm_adopt: NULL result pointer");
+  *comm = nullptr;
+  RAFB200_REQUIRE(world_size >= 1 && rank >= 0 && rank < world_size,
+                  "rafb200_comm_adopt: rank %d outside world of %d", rank, world_size);
+  RAFB200_REQUIRE(world_size == 1 || nccl_comm, "rafb200_comm_adopt: NULL ncclComm_t");
+  auto* c = new rafb200_comm_s();
+  c->size = world_size;
+  c->rank = rank;
+  if (cudaGetDevice(&c->device) != cudaSuccess) c->device = 0;
+  if (world_size > 1) {
+    c->is_void = false;
+    c->borrowed = true;
+    c->nccl = static_cast<ncclComm_t>(nccl_comm);
+    int n = 0, r = -1;
+    if (ncclCommCount(c->nccl, &n) != ncclSuccess || ncclCommUserRank(c->nccl, &r) != ncclSuccess ||
+        n != world_size || r != rank) {
+      delete c;
+      return set_error(RAFB200_INVALID_ARGUMENT,
+                       "rafb200_comm_adopt: communicator reports rank %d of %d, caller said %d of %d",
+                       r, n, rank, world_size);
+    }
+  }
+  *comm = c;
+  return RAFB200_OK;
+}
+
 int rafb200_comm_create(int world_size, int rank, int device, const char* store_path,
                         int timeout_ms, rafb200_comm_t* comm) {
   RAFB200_REQUIRE(comm, "rafb200_comm_create: NULL result pointer");
@@ -226,7 +254,7 @@ int rafb200_comm_create(int world_size, int rank, int device, const char* store_
 int rafb200_comm_destroy(rafb200_comm_t c) {
   if (!c) return RAFB200_OK;
   int rc = RAFB200_OK;
-  if (c->nccl) {
+  if (c->nccl && !c->borrowed) {
     ncclResult_t r = ncclCommDestroy(c->nccl);
     if (r != ncclSuccess) rc = nccl_fail(r, "ncclCommDestroy");
   }

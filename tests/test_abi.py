@@ -97,3 +97,14 @@ def test_comm_create_argument_checks(lib):
     h = C.c_void_p()
     assert lib.rafb200_comm_create(2, 2, 0, None, 100, C.byref(h)) == 1
     assert lib.rafb200_comm_create(2, 0, 0, None, 0, C.byref(h)) == 1
+
+
+def test_comm_adopt_world_of_one_and_bad_arguments(lib):
+    """The wrapper around a caller-owned ncclComm_t: a world of one needs no NCCL handle."""
+    h = C.c_void_p()
+    assert lib.rafb200_comm_adopt(None, 1, 0, C.byref(h)) == 0
+    assert lib.rafb200_comm_size(h) == 1 and lib.rafb200_comm_rank(h) == 0
+    assert lib.rafb200_comm_destroy(h) == 0
+    assert lib.rafb200_comm_adopt(None, 2, 0, C.byref(h)) == 1  # world of two without a handle
+    assert b"NULL ncclComm_t" in lib.rafb200_last_error()
+    assert lib.rafb200_comm_adopt(None, 1, 3, C.byref(h)) == 1  # rank outside the world
