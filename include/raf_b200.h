@@ -241,7 +241,15 @@ typedef struct rafb200_comm_s* rafb200_comm_t;
 
 RAFB200_API int rafb200_comm_create(int world_size, int rank, int device, const char* store_path,
                                     int timeout_ms, rafb200_comm_t* comm);
-/* Same, with the id supplied by the caller (e.g. broadcast by its own launcher). */
+/* The id exchange on its own (host only): rank 0 publishes `nbytes` of `data`
+ * as <store_path>/<key> (written to a temporary name and renamed, so readers see
+ * nothing or all of it); every other rank polls every 10 ms until the file
+ * holds nbytes and copies it into `data`, or returns RAFB200_TIMEOUT after
+ * timeout_ms - a root that never arrives is reported, not waited for forever. */
+RAFB200_API int rafb200_store_exchange(int rank, const char* store_path, int key, void* data,
+                                       size_t nbytes, int timeout_ms);
+/* Same as rafb200_comm_create, with the id supplied by the caller (e.g.
+ * broadcast by its own launcher). */
 RAFB200_API int rafb200_unique_id(void* id128);
 RAFB200_API int rafb200_comm_create_with_id(int world_size, int rank, int device,
                                             const void* id128, int timeout_ms,

@@ -64,6 +64,7 @@ SIGNATURES = {
     "rafb200_comm_create": (_i, [_i, _i, _i, C.c_char_p, _i, _P(_vp)]),
     "rafb200_unique_id": (_i, [_vp]),
     "rafb200_comm_create_with_id": (_i, [_i, _i, _i, _vp, _i, _P(_vp)]),
+    "rafb200_store_exchange": (_i, [_i, C.c_char_p, _i, _vp, _sz, _i]),
     "rafb200_comm_adopt": (_i, [_vp, _i, _i, _P(_vp)]),
     "rafb200_comm_destroy": (_i, [_vp]),
     "rafb200_comm_size": (_i, [_vp]),

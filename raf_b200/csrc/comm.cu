@@ -193,6 +193,17 @@ int rafb200_comm_create_with_id(int world_size, int rank, int device, const void
   return RAFB200_OK;
 }
 
+int rafb200_store_exchange(int rank, const char* store_path, int key, void* data, size_t nbytes,
+                           int timeout_ms) {
+  RAFB200_REQUIRE(rank >= 0 && key >= 0 && data && nbytes > 0 && timeout_ms > 0,
+                  "rafb200_store_exchange: bad argument");
+  const std::string dir = store_dir(store_path);
+  ::mkdir(dir.c_str(), 0777);  // nccl_communicator.cc:28-33; fine if it exists
+  const std::string file = dir + "/" + std::to_string(key);
+  if (rank == 0) return store_publish(file, data, nbytes);
+  return store_fetch(file, data, nbytes, timeout_ms);
+}
+
 int rafb200_comm_adopt(void* nccl_comm, int world_size, int rank, rafb200_comm_t* comm) {
   RAFB200_REQUIRE(comm, "rafb200_comm_adopt: NULL result pointer");
   *comm = nullptr;
@@ -229,18 +240,15 @@ int rafb200_comm_create(int world_size, int rank, int device, const char* store_
   RAFB200_REQUIRE(timeout_ms > 0, "rafb200_comm_create: timeout must be positive");
   if (world_size == 1) return rafb200_comm_create_with_id(1, 0, device, nullptr, timeout_ms, comm);
 
-  const std::string dir = store_dir(store_path);
-  ::mkdir(dir.c_str(), 0777);  // nccl_communicator.cc:28-33; fine if it exists
   const int seq = ++g_store_seq;  // every rank creates its communicators in the same order
-  const std::string file = dir + "/" + std::to_string(seq);
+  const std::string file = store_dir(store_path) + "/" + std::to_string(seq);
   ncclUniqueId id;
   if (rank == 0) {
     ncclResult_t r = ncclGetUniqueId(&id);
     if (r != ncclSuccess) return nccl_fail(r, "ncclGetUniqueId");
-    int rc = store_publish(file, &id, sizeof(id));
-    if (rc != RAFB200_OK) return rc;
-  } else {
-    int rc = store_fetch(file, &id, sizeof(id), timeout_ms);
+  }
+  {
+    int rc = rafb200_store_exchange(rank, store_path, seq, &id, sizeof(id), timeout_ms);
     if (rc != RAFB200_OK) return rc;
   }
   int rc = rafb200_comm_create_with_id(world_size, rank, device, &id, timeout_ms, comm);

@@ -1,0 +1,151 @@
+"""One rank of the multi-GPU tests (started by tests/test_dist_gpu.py, one process per GPU).
+
+Environment: RANK, WORLD_SIZE, LOCAL_RANK, RAF_FILE_STORE_PATH (id exchange), OUT_DIR.
+Part 1 checks the collectives against the known answers of the reference's own tests
+(tests/python/distributed/test_collective_communication.py:73-121,230-255,637-754:
+rank-valued inputs whose reductions are exact integers).  Part 2 runs the ZeRO step
+for three steps per optimizer and writes what this rank saw (reduced gradient shard,
+state shards, gathered parameters) to OUT_DIR for the parent to check against the oracle.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from raf_b200 import distributed as dist  # noqa: E402
+from raf_b200.zero import Plan, ZeroStep, make_hyper, numel  # noqa: E402
+
+SHAPES = [(30, 16), (16,), (7, 3, 3), (1,), (129, 65), (4096,), (50, 1024), (2, 8)]
+BUCKET = 5000
+CASES = [("sgd", "float32", "float32"), ("adam", "bfloat16", "bfloat16"), ("lans", "float16", "float16"),
+         ("lans", "float32", "float32")]
+TORCH = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
+STEPS = 3
+
+
+def local_grad(rank, step, i, n, dtype, loss_scale):
+    """Rank-local gradient k * 2^-10 * loss_scale with integer |k| <= 15, a different seed per
+    rank: sums over up to 8 ranks are exact in fp32, fp16 and bf16 whatever order NCCL adds in,
+    so the parent can state the reduced gradient exactly."""
+    rng = np.random.default_rng(1000 * rank + 100 * step + i)
+    k = rng.integers(-15, 16, size=n).astype(np.float32)
+    return torch.from_numpy(k * np.float32(2.0 ** -10 * loss_scale)).to(TORCH[dtype])
+
+
+def check_collectives(comm):
+    n, r = comm.size, comm.rank
+    s = dist.comm_stream()
+    with torch.cuda.stream(s):
+        # _allreduce: every rank contributes ones * (rank + 1)
+        for dtype in (torch.float32, torch.float16):
+            x = torch.full((4, 4), float(r + 1), dtype=dtype, device="cuda")
+            dist.allreduce(x, "sum", stream=s)
+            assert torch.all(x == n * (n + 1) / 2), x
+        x = torch.full((4, 4), float(r + 1), device="cuda")
+        dist.allreduce(x, "avg", stream=s)
+        assert torch.allclose(x, torch.full_like(x, (n + 1) / 2))
+        pair = [torch.full((4, 4), float(r + 1), device="cuda"), torch.full((3,), float(-(r + 1)), device="cuda")]
+        dist.allreduce(pair, "max", stream=s)
+        assert torch.all(pair[0] == n) and torch.all(pair[1] == -1)
+        # _allgather on axis 0 and 1
+        x = torch.full((2, 3), float(r + 1), device="cuda")
+        y = dist.allgather(x, 0, stream=s)
+        assert y.shape == (2 * n, 3)
+        assert torch.equal(y[:, 0].cpu(), torch.arange(1, n + 1).repeat_interleave(2).float())
+        y = dist.allgather(x, 1, stream=s)
+        assert y.shape == (2, 3 * n)
+        assert torch.equal(y[0].cpu(), torch.arange(1, n + 1).repeat_interleave(3).float())
+        # _reduce_scatter: rank j receives row block j of the sum
+        x = (torch.arange(n * 2, device="cuda").float().reshape(n * 2, 1) + 1) * (r + 1)
+        y = dist.reduce_scatter(x.expand(n * 2, 4).contiguous(), "sum", stream=s)
+        want = (torch.arange(2 * r, 2 * r + 2).float() + 1) * (n * (n + 1) / 2)
+        assert y.shape == (2, 4) and torch.equal(y[:, 0].cpu(), want), (y, want)
+        for comp, red in (("min", min), ("max", max), ("prod", None)):
+            x = torch.full((n, 2), float(r + 1), device="cuda")
+            y = dist.reduce_scatter(x, comp, stream=s)
+            if red is not None:
+                assert torch.all(y == red(range(1, n + 1)))
+            else:
+                assert torch.all(y == float(np.prod(np.arange(1, n + 1))))
+        # _group_reduce_scatter / _group_allgather on lists of different sizes, fp16 too
+        for dtype in (torch.float32, torch.float16):
+            xs = [torch.full((n * k, 3), float(r + 1), dtype=dtype, device="cuda") for k in (1, 2, 5)]
+            ys = dist.group_reduce_scatter(xs, "sum", stream=s)
+            for k, y in zip((1, 2, 5), ys):
+                assert y.shape == (k, 3) and torch.all(y == n * (n + 1) / 2)
+            ys = dist.group_reduce_scatter(xs, "avg", stream=s)
+            for y in ys:
+                assert torch.allclose(y.float(), torch.full(y.shape, (n + 1) / 2, device="cuda"))
+            shards = [torch.full((k, 3), float(r + 1), dtype=dtype, device="cuda") for k in (1, 2, 5)]
+            outs = [torch.zeros((n * k, 3), dtype=dtype, device="cuda") for k in (1, 2, 5)]
+            dist.group_allgather(shards, 0, outs, stream=s)
+            for k, o in zip((1, 2, 5), outs):
+                assert torch.equal(o[:, 0].float().cpu(), torch.arange(1, n + 1).repeat_interleave(k).float())
+        try:
+            dist.reduce_scatter(torch.zeros(n + 1, 2, device="cuda"), "sum", stream=s)
+            raise AssertionError("reduce_scatter accepted a dim 0 that does not divide")
+        except ValueError:
+            pass
+    s.synchronize()
+    comm.check()
+
+
+def run_zero(comm, out_dir):
+    n, r = comm.size, comm.rank
+    for case, (optimizer, g_dtype, p_dtype) in enumerate(CASES):
+        plan = Plan(SHAPES, n, r, BUCKET)
+        z = ZeroStep(plan, comm, g_dtype, p_dtype, optimizer)
+        rng = np.random.default_rng(0)
+        full_p = [(rng.standard_normal(numel(s)) * 0.02).astype(np.float32) for s in SHAPES]
+        tp, tm, tv = [], [], []
+        for i, s in enumerate(SHAPES):
+            se = int(plan.shard_elems[i])
+            padded = np.zeros(se * n, np.float32)
+            padded[:numel(s)] = full_p[i]
+            tp.append(torch.from_numpy(padded[r * se:(r + 1) * se].copy()).cuda())
+            tm.append(torch.zeros(se, device="cuda"))
+            tv.append(torch.zeros(se, device="cuda"))
+        params = [torch.zeros(numel(s), dtype=TORCH[p_dtype], device="cuda") for s in SHAPES]
+        scale = 2.0 ** -15 if g_dtype == "float16" else 1.0
+        hyper = make_hyper(optimizer, learning_rate=0.1 if optimizer == "sgd" else 1e-3, mu=0.9,
+                           beta1=0.9, beta2=0.999, eps=1e-6, weight_decay=0.01, grad_scale=scale,
+                           average=1)
+        saved = {}
+        for step in range(1, STEPS + 1):
+            grads = [local_grad(r, step, i, numel(s), g_dtype, 1 / scale).cuda() for i, s in enumerate(SHAPES)]
+            z.bind(grads, params, tp, tm, tv)
+            z.step(hyper, step)
+            torch.cuda.synchronize()
+            for i, s in enumerate(SHAPES):
+                se = int(plan.shard_elems[i])
+                if int(plan.padded_elems[i]) == numel(s):
+                    # the reduce-scatter ran in place: this rank's row block holds the reduced shard
+                    red = grads[i].view(-1)[r * se:(r + 1) * se]
+                    saved[f"red_{step}_{i}"] = red.float().cpu().numpy()
+        for i in range(len(SHAPES)):
+            saved[f"p_{i}"] = tp[i].cpu().numpy()
+            saved[f"m_{i}"] = tm[i].cpu().numpy()
+            saved[f"v_{i}"] = tv[i].cpu().numpy()
+            saved[f"param_{i}"] = params[i].float().cpu().numpy()
+        kernels, collectives = z.launch_counts()
+        saved["counts"] = np.array([kernels, collectives, plan.num_buckets])
+        np.savez(os.path.join(out_dir, f"case{case}_rank{r}.npz"), **saved)
+        z.close()
+        plan.close()
+
+
+def main():
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    comm = dist.init_from_env(timeout_ms=120000)
+    check_collectives(comm)
+    run_zero(comm, os.environ["OUT_DIR"])
+    torch.cuda.synchronize()
+    comm.close()
+    print(f"rank {comm.rank}: ok", flush=True)
+
+
+if __name__ == "__main__":
+    main()
