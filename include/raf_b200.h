@@ -342,14 +342,20 @@ RAFB200_API int rafb200_plan_totals(rafb200_plan_t plan, int64_t* elems, int64_t
  * src/pass/enforce_sync.cc:45-68: compute stream 1, communication stream 4).
  *
  * Buffers (all device memory owned by the caller, k entries each):
- *   grads[i]   local gradient of tensor i, dim0 x row_elems, g_dtype.  It is
- *              reduced IN PLACE: after the step rank r's row block holds the
- *              reduced shard, the rest is unspecified.
- *   params[i]  full model parameter, dim0 x row_elems, param_dtype: the
- *              all-gather destination.
+ *   grads[i]   local gradient of tensor i, dim0 x row_elems, g_dtype; read only.
+ *   params[i]  full model parameter, dim0 x row_elems, param_dtype: receives
+ *              the all-gathered update.
  *   p/m/v[i]   fp32 master shard and optimizer state, shard_elems[i] each.
- * Tensors whose dim0 does not divide by n are staged through padded buffers
- * the state object owns (raf.op.pad before, strided_slice after).
+ * With more than one rank the state object owns two rank-major flat buffers per
+ * bucket (gradients, parameter copies; padded elements x dtype size each in
+ * total).  A step is, per bucket: one pack kernel (row block r of every gradient
+ * into slot r; the zero rows of raf.op.pad are never written and stay zero),
+ * ONE in-place ncclReduceScatter, the update kernel on slot `rank` (it writes
+ * the parameter copy into the gather buffer), ONE in-place ncclAllGather, one
+ * unpack kernel into params[i] (the strided_slice that drops the padding).  The
+ * reference issues one collective per tensor inside a group
+ * (src/op/dialect/nccl/nccl.cc:231-242,382-390).  Buckets are software-pipelined:
+ * bucket b+1 is on the wire while bucket b is updated.
  */
 typedef enum { RAFB200_OPT_SGD = 0, RAFB200_OPT_ADAM = 1, RAFB200_OPT_LANS = 2 } rafb200_optimizer;
 

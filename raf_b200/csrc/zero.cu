@@ -1,11 +1,14 @@
-// ZeRO plan (shard geometry, buckets) and the step driver:
-// grouped reduce-scatter -> shard-local update -> grouped all-gather per bucket,
-// collectives on the communication stream, updates on the compute stream.
+// ZeRO plan (shard geometry, buckets) and the step driver.  Per bucket:
+//   pack (gradient row blocks -> rank-major flat buffer)  ->  ONE reduce-scatter
+//   -> shard-local update (writes the parameter copy into the flat gather buffer)
+//   -> ONE all-gather  ->  unpack (row blocks -> the caller's parameter tensors).
+// Collectives run on the communication stream, kernels on the compute stream.
 #include <algorithm>
 #include <cstring>
 #include <memory>
 
 #include "common.h"
+#include "vec_io.cuh"
 
 struct rafb200_plan_s {
   int k = 0, n = 1, rank = 0;
@@ -18,19 +21,104 @@ struct rafb200_plan_s {
 
 namespace rafb200 {
 
+// One contiguous run of bytes moved by the pack / unpack kernel.
+struct Seg {
+  const char* src;
+  char* dst;
+  int64_t bytes;
+  int64_t pad_;
+};
+constexpr int kSegChunkBytes = 32768;  // bytes per work item of the copy kernel
+
 struct Bucket {
   std::vector<int> tensors;
   rafb200_tensor_list_t list = nullptr;
   void* lans_ws = nullptr;
   size_t lans_ws_bytes = 0;
-  cudaEvent_t rs_done = nullptr, upd_done = nullptr;
-  // arguments of the grouped collectives, rebuilt on bind
-  std::vector<const void*> rs_send;
-  std::vector<void*> rs_recv;
-  std::vector<int64_t> counts;
-  std::vector<const void*> ag_send;
-  std::vector<void*> ag_recv;
+  cudaEvent_t packed = nullptr, rs_done = nullptr, upd_done = nullptr, ag_done = nullptr;
+  // n > 1: rank-major flat buffers.  Slot r of a buffer holds, for every tensor of the
+  // bucket in order, row block r of that tensor at element offset `off[j]` (each offset a
+  // multiple of 8 elements, so every block starts 16-byte aligned in either dtype).
+  int64_t slot_elems = 0;          // elements per rank slot (sum of aligned shard sizes)
+  std::vector<int64_t> off;        // element offset of tensor j inside a slot
+  char* g_flat = nullptr;          // n * slot_elems gradients (reduce-scatter in place)
+  char* p_flat = nullptr;          // n * slot_elems parameter copies (all-gather in place)
+  Seg* dev_pack = nullptr;         // n * tensors segments each
+  Seg* dev_unpack = nullptr;
+  Item* dev_pack_items = nullptr;  // (segment, chunk) work items
+  Item* dev_unpack_items = nullptr;
+  uint32_t n_pack_items = 0, n_unpack_items = 0;
 };
+
+// Copies every segment; 16-byte accesses when both ends of a segment are aligned,
+// element-sized (2 or 4 byte) accesses otherwise.
+__global__ void __launch_bounds__(kBlockThreads)
+    seg_copy_kernel(const Seg* __restrict__ segs, const Item* __restrict__ items, uint32_t nitems,
+                    int elem_size) {
+  Policies pol;
+  pol.init();
+  for (uint32_t it = blockIdx.x; it < nitems; it += gridDim.x) {
+    const Item item = items[it];
+    const Seg sg = segs[item.tensor_phase];
+    const int64_t begin = (int64_t)item.chunk * kSegChunkBytes;
+    int64_t n = sg.bytes - begin;
+    if (n > kSegChunkBytes) n = kSegChunkBytes;
+    const char* src = sg.src + begin;
+    char* dst = sg.dst + begin;
+    if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0) {
+      const int nv = (int)(n >> 4);
+      constexpr int kU = kSegChunkBytes / 16 / kBlockThreads;  // 8 vectors per thread
+      uint4 r[kU];
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int i = threadIdx.x + u * kBlockThreads;
+        if (i < nv) r[u] = ld16<kStream>(src + (size_t)i * 16, pol);
+      }
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int i = threadIdx.x + u * kBlockThreads;
+        if (i < nv) st16<kDefault>(dst + (size_t)i * 16, r[u], pol);
+      }
+      for (int64_t e = ((int64_t)nv << 4) + threadIdx.x; e < n; e += kBlockThreads) dst[e] = src[e];
+    } else if (elem_size == 4) {
+      for (int64_t e = threadIdx.x; e < (n >> 2); e += kBlockThreads)
+        reinterpret_cast<uint32_t*>(dst)[e] = reinterpret_cast<const uint32_t*>(src)[e];
+    } else {
+      for (int64_t e = threadIdx.x; e < (n >> 1); e += kBlockThreads)
+        reinterpret_cast<uint16_t*>(dst)[e] = reinterpret_cast<const uint16_t*>(src)[e];
+    }
+  }
+}
+
+static int launch_seg_copy(const Seg* segs, const Item* items, uint32_t nitems, int elem_size,
+                           int sm_count, cudaStream_t s) {
+  if (nitems == 0) return RAFB200_OK;
+  int64_t grid = (int64_t)sm_count * 8;
+  if (grid > (int64_t)nitems) grid = nitems;
+  seg_copy_kernel<<<(unsigned)grid, kBlockThreads, 0, s>>>(segs, items, nitems, elem_size);
+  RAFB200_CUDA(cudaGetLastError());
+  return RAFB200_OK;
+}
+
+static int upload(const void* host, size_t bytes, void** dev) {
+  if (*dev) {
+    cudaFree(*dev);
+    *dev = nullptr;
+  }
+  if (bytes == 0) return RAFB200_OK;
+  RAFB200_CUDA(cudaMalloc(dev, bytes));
+  RAFB200_CUDA(cudaMemcpy(*dev, host, bytes, cudaMemcpyHostToDevice));
+  return RAFB200_OK;
+}
+
+static std::vector<Item> seg_items(const std::vector<Seg>& segs) {
+  std::vector<Item> items;
+  for (size_t i = 0; i < segs.size(); ++i) {
+    const int64_t chunks = (segs[i].bytes + kSegChunkBytes - 1) / kSegChunkBytes;
+    for (int64_t c = 0; c < chunks; ++c) items.push_back(Item{(uint32_t)i, (uint32_t)c});
+  }
+  return items;
+}
 
 }  // namespace rafb200
 
@@ -40,8 +128,9 @@ struct rafb200_zero_s {
   int n = 1, rank = 0;
   int g_dtype = 0, param_dtype = 0, optimizer = 0;
   std::vector<rafb200::Bucket> buckets;
-  // staging for tensors whose dim 0 does not divide by n (raf.op.pad / strided_slice)
-  std::vector<void*> stage_g, stage_p;
+  char* g_flat = nullptr;  // all buckets' gradient buffers, one allocation (n > 1)
+  char* p_flat = nullptr;  // all buckets' parameter-copy buffers
+  int sm_count = 148;
   std::vector<void*> grads, params;
   std::vector<float*> p, m, v;
   bool bound = false;
@@ -137,13 +226,14 @@ int rafb200_zero_destroy(rafb200_zero_t z) {
   for (auto& b : z->buckets) {
     if (b.list) rafb200_tensor_list_destroy(b.list);
     if (b.lans_ws) cudaFree(b.lans_ws);
-    if (b.rs_done) cudaEventDestroy(b.rs_done);
-    if (b.upd_done) cudaEventDestroy(b.upd_done);
+    for (cudaEvent_t e : {b.packed, b.rs_done, b.upd_done, b.ag_done})
+      if (e) cudaEventDestroy(e);
+    for (void* ptr : {(void*)b.dev_pack, (void*)b.dev_unpack, (void*)b.dev_pack_items,
+                      (void*)b.dev_unpack_items})
+      if (ptr) cudaFree(ptr);
   }
-  for (void* ptr : z->stage_g)
-    if (ptr) cudaFree(ptr);
-  for (void* ptr : z->stage_p)
-    if (ptr) cudaFree(ptr);
+  if (z->g_flat) cudaFree(z->g_flat);
+  if (z->p_flat) cudaFree(z->p_flat);
   if (z->ev_start) cudaEventDestroy(z->ev_start);
   if (z->ev_done) cudaEventDestroy(z->ev_done);
   delete z;
@@ -170,17 +260,27 @@ int rafb200_zero_create(rafb200_plan_t plan, rafb200_comm_t comm, int g_dtype, i
   z->param_dtype = param_dtype;
   z->optimizer = optimizer;
   const int k = plan->k;
-  z->stage_g.assign(k, nullptr);
-  z->stage_p.assign(k, nullptr);
   int rc = RAFB200_OK;
   do {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&z->sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+      rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: no usable CUDA device");
+      break;
+    }
     // With a single rank there is nothing to overlap: one bucket, one launch.
     const int nb = (z->n == 1) ? (k > 0 ? 1 : 0) : plan->nbuckets;
     z->buckets.resize(nb);
     for (int i = 0; i < k; ++i) z->buckets[z->n == 1 ? 0 : plan->bucket_of[i]].tensors.push_back(i);
+    int64_t flat_elems = 0;
     for (auto& b : z->buckets) {
       std::vector<int64_t> numel;
-      for (int i : b.tensors) numel.push_back(plan->shard_elems[i]);
+      for (int i : b.tensors) {
+        numel.push_back(plan->shard_elems[i]);
+        b.off.push_back(b.slot_elems);
+        b.slot_elems += (plan->shard_elems[i] + 7) & ~(int64_t)7;
+      }
+      flat_elems += b.slot_elems * z->n;
       rc = rafb200_tensor_list_create((int)numel.size(), numel.data(), g_dtype, param_dtype, &b.list);
       if (rc != RAFB200_OK) break;
       if (optimizer == RAFB200_OPT_LANS) {
@@ -190,11 +290,10 @@ int rafb200_zero_create(rafb200_plan_t plan, rafb200_comm_t comm, int g_dtype, i
           break;
         }
       }
-      if (cudaEventCreateWithFlags(&b.rs_done, cudaEventDisableTiming) != cudaSuccess ||
-          cudaEventCreateWithFlags(&b.upd_done, cudaEventDisableTiming) != cudaSuccess) {
-        rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: cannot create events");
-        break;
-      }
+      for (cudaEvent_t* e : {&b.packed, &b.rs_done, &b.upd_done, &b.ag_done})
+        if (cudaEventCreateWithFlags(e, cudaEventDisableTiming) != cudaSuccess)
+          rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: cannot create events");
+      if (rc != RAFB200_OK) break;
     }
     if (rc != RAFB200_OK) break;
     if (cudaEventCreateWithFlags(&z->ev_start, cudaEventDisableTiming) != cudaSuccess ||
@@ -202,15 +301,27 @@ int rafb200_zero_create(rafb200_plan_t plan, rafb200_comm_t comm, int g_dtype, i
       rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: cannot create events");
       break;
     }
-    for (int i = 0; i < k && z->n > 1; ++i) {
-      if (plan->padded_elems[i] == plan->numel[i]) continue;
-      if (cudaMalloc(&z->stage_g[i], (size_t)plan->padded_elems[i] * dtype_size(g_dtype)) != cudaSuccess ||
-          cudaMalloc(&z->stage_p[i], (size_t)plan->padded_elems[i] * dtype_size(param_dtype)) != cudaSuccess) {
-        rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: cannot allocate padding buffers");
+    if (z->n > 1 && flat_elems > 0) {
+      const size_t gbytes = (size_t)flat_elems * dtype_size(g_dtype);
+      const size_t pbytes = (size_t)flat_elems * dtype_size(param_dtype);
+      if (cudaMalloc(reinterpret_cast<void**>(&z->g_flat), gbytes) != cudaSuccess ||
+          cudaMalloc(reinterpret_cast<void**>(&z->p_flat), pbytes) != cudaSuccess) {
+        rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: cannot allocate %zu bytes of bucket buffers",
+                       gbytes + pbytes);
         break;
       }
-      // The zero tail is written once: reduce-scatter only ever adds zeros to it.
-      cudaMemset(z->stage_g[i], 0, (size_t)plan->padded_elems[i] * dtype_size(g_dtype));
+      // Zeroed once: the pack kernel never writes the padding rows or the alignment
+      // gaps, and a reduce-scatter only ever adds zeros to them.
+      if (cudaMemset(z->g_flat, 0, gbytes) != cudaSuccess || cudaMemset(z->p_flat, 0, pbytes) != cudaSuccess) {
+        rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: cannot clear the bucket buffers");
+        break;
+      }
+      int64_t at = 0;
+      for (auto& b : z->buckets) {
+        b.g_flat = z->g_flat + (size_t)at * dtype_size(g_dtype);
+        b.p_flat = z->p_flat + (size_t)at * dtype_size(param_dtype);
+        at += b.slot_elems * z->n;
+      }
     }
   } while (false);
   if (rc != RAFB200_OK) {
@@ -227,6 +338,11 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
   const int k = z->plan.k;
   RAFB200_REQUIRE(k == 0 || (grads && params && p && m), "rafb200_zero_bind: NULL pointer table");
   RAFB200_REQUIRE(z->optimizer == RAFB200_OPT_SGD || v, "rafb200_zero_bind: v is required");
+  const bool same = z->bound && std::equal(grads, grads + k, z->grads.begin()) &&
+                    std::equal(params, params + k, z->params.begin()) &&
+                    std::equal(p, p + k, z->p.begin()) && std::equal(m, m + k, z->m.begin()) &&
+                    (v ? (z->v.size() == (size_t)k && std::equal(v, v + k, z->v.begin())) : z->v.empty());
+  if (same) return RAFB200_OK;
   z->grads.assign(grads, grads + k);
   z->params.assign(params, params + k);
   z->p.assign(p, p + k);
@@ -236,42 +352,58 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
   const int gs = dtype_size(z->g_dtype), ps = dtype_size(z->param_dtype);
   z->kernels_per_step = 0;
   z->collectives_per_step = 0;
+  // Tables that a kernel of an earlier step may still be reading are replaced below.
+  RAFB200_CUDA(cudaDeviceSynchronize());
   for (auto& b : z->buckets) {
     const size_t nt = b.tensors.size();
     std::vector<const void*> lg(nt);
     std::vector<float*> lp(nt), lm(nt), lv(nt);
     std::vector<void*> lo(nt);
-    b.rs_send.resize(nt);
-    b.rs_recv.resize(nt);
-    b.ag_send.resize(nt);
-    b.ag_recv.resize(nt);
-    b.counts.resize(nt);
+    std::vector<Seg> pack, unpack;
     for (size_t j = 0; j < nt; ++j) {
       const int i = b.tensors[j];
       const int64_t se = z->plan.shard_elems[i];
-      // Tensors that need padding live in staging buffers for the collectives.
-      char* gbase = static_cast<char*>(z->stage_g[i] ? z->stage_g[i] : grads[i]);
-      char* pbase = static_cast<char*>(z->stage_p[i] ? z->stage_p[i] : params[i]);
-      RAFB200_REQUIRE(se == 0 || (gbase && pbase && p[i] && m[i]),
+      RAFB200_REQUIRE(se == 0 || (grads[i] && params[i] && p[i] && m[i]),
                       "rafb200_zero_bind: NULL buffer for tensor %d", i);
-      char* gshard = gbase + (size_t)z->rank * se * gs;  // in-place reduce-scatter target
-      char* pshard = pbase + (size_t)z->rank * se * ps;  // in-place all-gather source
-      b.rs_send[j] = gbase;
-      b.rs_recv[j] = gshard;
-      b.ag_send[j] = pshard;
-      b.ag_recv[j] = pbase;
-      b.counts[j] = se;
-      lg[j] = gshard;
       lp[j] = p[i];
       lm[j] = m[i];
       lv[j] = v ? v[i] : nullptr;
-      lo[j] = pshard;
+      if (z->n == 1) {
+        lg[j] = grads[i];
+        lo[j] = params[i];
+        continue;
+      }
+      // This rank updates slot `rank` of the flat buffers in place.
+      lg[j] = b.g_flat + (size_t)(z->rank * b.slot_elems + b.off[j]) * gs;
+      lo[j] = b.p_flat + (size_t)(z->rank * b.slot_elems + b.off[j]) * ps;
+      for (int r = 0; r < z->n; ++r) {
+        // rows of block r that exist in the unpadded tensor (raf.op.pad / strided_slice)
+        int64_t cnt = z->plan.numel[i] - (int64_t)r * se;
+        cnt = cnt < 0 ? 0 : (cnt > se ? se : cnt);
+        if (cnt == 0) continue;
+        const size_t slot = (size_t)(r * b.slot_elems + b.off[j]);
+        pack.push_back(Seg{static_cast<const char*>(grads[i]) + (size_t)r * se * gs,
+                           b.g_flat + slot * gs, cnt * gs, 0});
+        unpack.push_back(Seg{b.p_flat + slot * ps, static_cast<char*>(params[i]) + (size_t)r * se * ps,
+                             cnt * ps, 0});
+      }
     }
     int rc = rafb200_tensor_list_bind(b.list, lg.data(), lp.data(), lm.data(), v ? lv.data() : nullptr,
                                       lo.data(), nullptr);
     if (rc != RAFB200_OK) return rc;
     if (rafb200_tensor_list_total_elems(b.list) > 0) z->kernels_per_step += 1;
-    if (z->n > 1) z->collectives_per_step += 2 * (int)nt;
+    if (z->n > 1) {
+      const std::vector<Item> pi = seg_items(pack), ui = seg_items(unpack);
+      b.n_pack_items = (uint32_t)pi.size();
+      b.n_unpack_items = (uint32_t)ui.size();
+      if ((rc = upload(pack.data(), pack.size() * sizeof(Seg), reinterpret_cast<void**>(&b.dev_pack))) ||
+          (rc = upload(unpack.data(), unpack.size() * sizeof(Seg), reinterpret_cast<void**>(&b.dev_unpack))) ||
+          (rc = upload(pi.data(), pi.size() * sizeof(Item), reinterpret_cast<void**>(&b.dev_pack_items))) ||
+          (rc = upload(ui.data(), ui.size() * sizeof(Item), reinterpret_cast<void**>(&b.dev_unpack_items))))
+        return rc;
+      z->kernels_per_step += (b.n_pack_items > 0) + (b.n_unpack_items > 0);
+      if (b.slot_elems > 0) z->collectives_per_step += 2;
+    }
   }
   RAFB200_CUDA(cudaStreamSynchronize(nullptr));  // descriptor tables are in place
   z->bound = true;
@@ -329,43 +461,45 @@ int rafb200_zero_step(rafb200_zero_t z, const rafb200_hyper* h, int step, void* 
     return RAFB200_OK;
   }
   const int gs = dtype_size(z->g_dtype), ps = dtype_size(z->param_dtype);
-  // Gradients were produced on the compute stream.
+  // The communication stream must not run ahead of work already queued on the compute
+  // stream that still uses the flat buffers (the previous step's unpack).
   RAFB200_CUDA(cudaEventRecord(z->ev_start, cs));
   RAFB200_CUDA(cudaStreamWaitEvent(ms, z->ev_start, 0));
-  auto reduce_scatter = [&](Bucket& b) -> int {
-    for (int i : b.tensors)  // raf.op.pad: copy the unpadded rows in front of the zero tail
-      if (z->stage_g[i])
-        RAFB200_CUDA(cudaMemcpyAsync(z->stage_g[i], z->grads[i], (size_t)z->plan.numel[i] * gs,
-                                     cudaMemcpyDeviceToDevice, ms));
-    int rc = rafb200_group_reduce_scatter(z->comm, (int)b.tensors.size(), b.rs_send.data(),
-                                          b.rs_recv.data(), b.counts.data(), z->g_dtype, "sum", ms);
-    if (rc != RAFB200_OK) return rc;
-    RAFB200_CUDA(cudaEventRecord(b.rs_done, ms));
-    return RAFB200_OK;
-  };
-  int rc = nb > 0 ? reduce_scatter(z->buckets[0]) : RAFB200_OK;
-  if (rc != RAFB200_OK) return rc;
-  for (int bi = 0; bi < nb; ++bi) {
-    Bucket& b = z->buckets[bi];
-    if (bi + 1 < nb) {
-      rc = reduce_scatter(z->buckets[bi + 1]);
+  // Software pipeline over buckets; stage s of bucket b is issued in iteration b + s:
+  //   0 pack (compute)  1 reduce-scatter (comm)  2 update (compute)  3 all-gather (comm)
+  //   4 unpack (compute)
+  // so bucket b+1 is on the wire while bucket b is being updated.
+  for (int it = 0; it < nb + 2; ++it) {
+    if (it < nb) {
+      Bucket& b = z->buckets[it];
+      int rc = launch_seg_copy(b.dev_pack, b.dev_pack_items, b.n_pack_items, gs, z->sm_count, cs);
+      if (rc != RAFB200_OK) return rc;
+      RAFB200_CUDA(cudaEventRecord(b.packed, cs));
+      RAFB200_CUDA(cudaStreamWaitEvent(ms, b.packed, 0));
+      rc = rafb200_reduce_scatter(z->comm, b.g_flat, b.g_flat + (size_t)z->rank * b.slot_elems * gs,
+                                  b.slot_elems, z->g_dtype, "sum", ms);
+      if (rc != RAFB200_OK) return rc;
+      RAFB200_CUDA(cudaEventRecord(b.rs_done, ms));
+    }
+    if (it >= 1 && it - 1 < nb) {
+      Bucket& b = z->buckets[it - 1];
+      RAFB200_CUDA(cudaStreamWaitEvent(cs, b.rs_done, 0));
+      int rc = run_update(z, b, h, step, gscale, cs);
+      if (rc != RAFB200_OK) return rc;
+      RAFB200_CUDA(cudaEventRecord(b.upd_done, cs));
+      RAFB200_CUDA(cudaStreamWaitEvent(ms, b.upd_done, 0));
+      rc = rafb200_allgather(z->comm, b.p_flat + (size_t)z->rank * b.slot_elems * ps, b.p_flat,
+                             b.slot_elems, z->param_dtype, ms);
+      if (rc != RAFB200_OK) return rc;
+      RAFB200_CUDA(cudaEventRecord(b.ag_done, ms));
+    }
+    if (it >= 2) {
+      Bucket& b = z->buckets[it - 2];
+      RAFB200_CUDA(cudaStreamWaitEvent(cs, b.ag_done, 0));
+      int rc = launch_seg_copy(b.dev_unpack, b.dev_unpack_items, b.n_unpack_items, ps, z->sm_count, cs);
       if (rc != RAFB200_OK) return rc;
     }
-    RAFB200_CUDA(cudaStreamWaitEvent(cs, b.rs_done, 0));
-    rc = run_update(z, b, h, step, gscale, cs);
-    if (rc != RAFB200_OK) return rc;
-    RAFB200_CUDA(cudaEventRecord(b.upd_done, cs));
-    RAFB200_CUDA(cudaStreamWaitEvent(ms, b.upd_done, 0));
-    rc = rafb200_group_allgather(z->comm, (int)b.tensors.size(), b.ag_send.data(), b.ag_recv.data(),
-                                 b.counts.data(), z->param_dtype, ms);
-    if (rc != RAFB200_OK) return rc;
-    for (int i : b.tensors)  // strided_slice [0:dim0] + add(out=param): drop the padding rows
-      if (z->stage_p[i])
-        RAFB200_CUDA(cudaMemcpyAsync(z->params[i], z->stage_p[i], (size_t)z->plan.numel[i] * ps,
-                                     cudaMemcpyDeviceToDevice, ms));
   }
-  RAFB200_CUDA(cudaEventRecord(z->ev_done, ms));
-  RAFB200_CUDA(cudaStreamWaitEvent(cs, z->ev_done, 0));
   return RAFB200_OK;
 }
 

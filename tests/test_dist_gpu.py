@@ -83,9 +83,6 @@ def test_collectives_and_zero_step_multi_gpu(world):
                         for q in range(world):
                             total[:numel(s)] += W.local_grad(q, step, i, numel(s), "float32", 1 / scale).numpy()
                         shard = total[r * ses[i]:(r + 1) * ses[i]].copy()
-                        key = f"red_{step}_{i}"
-                        if key in ranks[r].files:  # unpadded tensors: reduced in place, visible to the caller
-                            assert bits_equal(ranks[r][key], shard), (case, r, step, i)
                         g.append(O.cast(shard, CODES[g_dtype]) if g_dtype != "float32" else shard)
                     if optimizer == "sgd":
                         outs = [O.sgd(p[i], g[i], m[i], 0.1, 0.9, 0.01, gscale, out_code=CODES[p_dtype])
@@ -121,4 +118,5 @@ def test_collectives_and_zero_step_multi_gpu(world):
                             else:
                                 assert bits_equal(got, want), (case, r, q, i)
                 kernels, collectives, nb = ranks[r]["counts"]
-                assert kernels == nb and collectives == 2 * len(W.SHAPES)
+                # per bucket: pack, update, unpack kernels and ONE reduce-scatter + ONE all-gather
+                assert kernels == 3 * nb and collectives == 2 * nb
