@@ -226,10 +226,16 @@ def main():
     ap.add_argument("--window-elems", type=int, default=None)
     ap.add_argument("--slack-items", type=int, default=None)
     ap.add_argument("--update-blocks", type=int, default=0)
+    ap.add_argument("--bucket-elems", type=int, default=None,
+                    help="bucket size in elements (default: the workload's)")
+    ap.add_argument("--stages", action="store_true",
+                    help="N > 1: also time each stage of the step alone (pack, reduce-scatter, ...)")
     ap.add_argument("--existing-kernel", action="store_true",
                     help="also time the reference's own LANS kernel (oracle/_ref) on the same shards")
     args = ap.parse_args()
     wl = workload(args.workload)
+    if args.bucket_elems:
+        wl["bucket_elems"] = args.bucket_elems
     if args.impl == "reference":
         run_reference_arm(args, wl)
         return
@@ -386,6 +392,26 @@ def main():
                "h2d_bytes_per_step": total * gsz * world, "d2h_bytes_per_step": total * psz * world,
                "steps": args.e2e_steps}
 
+    stage_ms = None
+    if args.stages and world > 1:
+        stage_ms = {}
+        for name, mask in (("pack", 1), ("reduce_scatter", 2), ("update", 4), ("all_gather", 8),
+                           ("unpack", 16), ("collectives", 10), ("kernels", 21)):
+            zs[0].set_stage_mask(mask)
+            for _ in range(2):
+                step_no += 1
+                zs[0].step(hyper, step_no, compute, comm_stream)
+            barrier()
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record(compute)
+            for _ in range(5):
+                step_no += 1
+                zs[0].step(hyper, step_no, compute, comm_stream)
+            s1.record(compute)
+            barrier()
+            stage_ms[name] = max_over_ranks(s0.elapsed_time(s1)) / 5
+        zs[0].set_stage_mask(31)
+
     existing = None
     if args.existing_kernel and wl["optimizer"] == "lans":
         from oracle import ref_lans
@@ -426,6 +452,8 @@ def main():
         }
         if existing:
             line["existing_kernel"] = existing
+        if stage_ms:
+            line["stage_ms"] = stage_ms
         print(json.dumps(line), flush=True)
     barrier()
     for z in zs:

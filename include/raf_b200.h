@@ -261,6 +261,16 @@ RAFB200_API int rafb200_comm_create_with_id(int world_size, int rank, int device
  * gives the copy-only communicator and ignores nccl_comm. */
 RAFB200_API int rafb200_comm_adopt(void* nccl_comm, int world_size, int rank, rafb200_comm_t* comm);
 RAFB200_API int rafb200_comm_destroy(rafb200_comm_t comm);
+/* Device memory for collective buffers, registered with the communicator
+ * (ncclMemAlloc + ncclCommRegister) so that in-place collectives on it can take
+ * NCCL's zero-copy and in-switch (NVLS) paths; plain cudaMalloc for a world of
+ * one, when registration is unavailable, or when RAFB200_NCCL_REGISTER=0.  The
+ * reference allocates every collective buffer from its memory pool without
+ * registration (src/op/dialect/nccl/nccl.cc:119-146).  Free with
+ * rafb200_comm_free before rafb200_comm_destroy; allocation is a collective-
+ * free, set-up-time operation. */
+RAFB200_API int rafb200_comm_alloc(rafb200_comm_t comm, size_t bytes, void** ptr);
+RAFB200_API int rafb200_comm_free(rafb200_comm_t comm, void* ptr);
 RAFB200_API int rafb200_comm_size(rafb200_comm_t comm);
 RAFB200_API int rafb200_comm_rank(rafb200_comm_t comm);
 /* Polls NCCL's asynchronous error state (the reference never does). */
@@ -385,6 +395,11 @@ RAFB200_API int rafb200_zero_bind(rafb200_zero_t zero, void* const* grads, void*
 RAFB200_API int rafb200_zero_step(rafb200_zero_t zero, const rafb200_hyper* hyper, int step,
                                   void* compute_stream, void* comm_stream);
 /* Kernel launches and NCCL calls one step enqueues (for accounting). */
+/* Measurement aid: issue only the selected stages of a multi-rank step
+ * (bit 0 pack, 1 reduce-scatter, 2 update, 3 all-gather, 4 unpack; default 31).
+ * With a stage missing the results are meaningless; every rank must use the
+ * same mask.  bench.py uses it to time the stages separately. */
+RAFB200_API int rafb200_zero_set_stage_mask(rafb200_zero_t zero, int mask);
 RAFB200_API int rafb200_zero_launch_counts(rafb200_zero_t zero, int* kernels, int* collectives);
 /* Cap on the persistent update grids while collectives are in flight (0 = no cap). */
 RAFB200_API int rafb200_zero_set_update_blocks(rafb200_zero_t zero, int max_blocks);

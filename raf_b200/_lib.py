@@ -67,6 +67,8 @@ SIGNATURES = {
     "rafb200_store_exchange": (_i, [_i, C.c_char_p, _i, _vp, _sz, _i]),
     "rafb200_comm_adopt": (_i, [_vp, _i, _i, _P(_vp)]),
     "rafb200_comm_destroy": (_i, [_vp]),
+    "rafb200_comm_alloc": (_i, [_vp, _sz, _P(_vp)]),
+    "rafb200_comm_free": (_i, [_vp, _vp]),
     "rafb200_comm_size": (_i, [_vp]),
     "rafb200_comm_rank": (_i, [_vp]),
     "rafb200_comm_check": (_i, [_vp]),
@@ -84,6 +86,7 @@ SIGNATURES = {
     "rafb200_zero_destroy": (_i, [_vp]),
     "rafb200_zero_bind": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "rafb200_zero_step": (_i, [_vp, _P(Hyper), _i, _vp, _vp]),
+    "rafb200_zero_set_stage_mask": (_i, [_vp, _i]),
     "rafb200_zero_launch_counts": (_i, [_vp, _P(_i), _P(_i)]),
     "rafb200_zero_set_update_blocks": (_i, [_vp, _i]),
     "rafb200_zero_step_host": (_i, [_vp, _P(Hyper), _i, _vp, _vp, _vp, _vp]),

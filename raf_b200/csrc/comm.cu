@@ -18,6 +18,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <condition_variable>
+#include <map>
 #include <memory>
 #include <mutex>
 #include <thread>
@@ -31,6 +32,12 @@ struct rafb200_comm_s {
   bool is_void = true;  // world of one: no NCCL underneath
   ncclComm_t nccl = nullptr;
   bool borrowed = false;   // adopted from the caller: never destroyed here
+  // buffers from rafb200_comm_alloc: pointer -> (registration handle or NULL, from ncclMemAlloc?)
+  struct Reg {
+    void* handle;
+    bool nccl_mem;
+  };
+  std::map<void*, Reg> regs;
   std::string store_file;  // file this rank published (removed on destroy)
 };
 
@@ -268,6 +275,41 @@ int rafb200_comm_destroy(rafb200_comm_t c) {
   }
   if (!c->store_file.empty()) ::unlink(c->store_file.c_str());
   delete c;
+  return rc;
+}
+
+int rafb200_comm_alloc(rafb200_comm_t c, size_t bytes, void** ptr) {
+  RAFB200_REQUIRE(c && ptr && bytes > 0, "rafb200_comm_alloc: bad arguments");
+  *ptr = nullptr;
+  const char* off = getenv("RAFB200_NCCL_REGISTER");
+  const bool want = !c->is_void && !(off && off[0] == '0');
+  rafb200_comm_s::Reg reg{nullptr, false};
+  void* p = nullptr;
+  if (want && ncclMemAlloc(&p, bytes) == ncclSuccess && p) {
+    reg.nccl_mem = true;
+    if (ncclCommRegister(c->nccl, p, bytes, &reg.handle) != ncclSuccess) reg.handle = nullptr;
+  } else {
+    p = nullptr;
+    RAFB200_CUDA(cudaMalloc(&p, bytes));
+  }
+  c->regs[p] = reg;
+  *ptr = p;
+  return RAFB200_OK;
+}
+
+int rafb200_comm_free(rafb200_comm_t c, void* ptr) {
+  if (!c || !ptr) return RAFB200_OK;
+  auto it = c->regs.find(ptr);
+  RAFB200_REQUIRE(it != c->regs.end(), "rafb200_comm_free: pointer was not allocated by rafb200_comm_alloc");
+  int rc = RAFB200_OK;
+  if (it->second.handle && ncclCommDeregister(c->nccl, it->second.handle) != ncclSuccess)
+    rc = set_error(RAFB200_NCCL_ERROR, "ncclCommDeregister failed");
+  if (it->second.nccl_mem) {
+    if (ncclMemFree(ptr) != ncclSuccess) rc = set_error(RAFB200_NCCL_ERROR, "ncclMemFree failed");
+  } else {
+    cudaFree(ptr);
+  }
+  c->regs.erase(it);
   return rc;
 }
 

@@ -136,6 +136,7 @@ struct rafb200_zero_s {
   bool bound = false;
   cudaEvent_t ev_start = nullptr, ev_done = nullptr;
   int max_update_blocks = 0;
+  int stage_mask = 31;  // measurement aid: which of the five stages a step issues
   int kernels_per_step = 0, collectives_per_step = 0;
 };
 
@@ -232,8 +233,8 @@ int rafb200_zero_destroy(rafb200_zero_t z) {
                       (void*)b.dev_unpack_items})
       if (ptr) cudaFree(ptr);
   }
-  if (z->g_flat) cudaFree(z->g_flat);
-  if (z->p_flat) cudaFree(z->p_flat);
+  if (z->g_flat) rafb200_comm_free(z->comm, z->g_flat);
+  if (z->p_flat) rafb200_comm_free(z->comm, z->p_flat);
   if (z->ev_start) cudaEventDestroy(z->ev_start);
   if (z->ev_done) cudaEventDestroy(z->ev_done);
   delete z;
@@ -304,12 +305,9 @@ int rafb200_zero_create(rafb200_plan_t plan, rafb200_comm_t comm, int g_dtype, i
     if (z->n > 1 && flat_elems > 0) {
       const size_t gbytes = (size_t)flat_elems * dtype_size(g_dtype);
       const size_t pbytes = (size_t)flat_elems * dtype_size(param_dtype);
-      if (cudaMalloc(reinterpret_cast<void**>(&z->g_flat), gbytes) != cudaSuccess ||
-          cudaMalloc(reinterpret_cast<void**>(&z->p_flat), pbytes) != cudaSuccess) {
-        rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: cannot allocate %zu bytes of bucket buffers",
-                       gbytes + pbytes);
+      if ((rc = rafb200_comm_alloc(comm, gbytes, reinterpret_cast<void**>(&z->g_flat))) != RAFB200_OK ||
+          (rc = rafb200_comm_alloc(comm, pbytes, reinterpret_cast<void**>(&z->p_flat))) != RAFB200_OK)
         break;
-      }
       // Zeroed once: the pack kernel never writes the padding rows or the alignment
       // gaps, and a reduce-scatter only ever adds zeros to them.
       if (cudaMemset(z->g_flat, 0, gbytes) != cudaSuccess || cudaMemset(z->p_flat, 0, pbytes) != cudaSuccess) {
@@ -420,6 +418,12 @@ int rafb200_zero_set_update_blocks(rafb200_zero_t z, int max_blocks) {
   return RAFB200_OK;
 }
 
+int rafb200_zero_set_stage_mask(rafb200_zero_t z, int mask) {
+  RAFB200_REQUIRE(z && mask >= 0 && mask < 32, "rafb200_zero_set_stage_mask: bad arguments");
+  z->stage_mask = mask;
+  return RAFB200_OK;
+}
+
 int rafb200_zero_launch_counts(rafb200_zero_t z, int* kernels, int* collectives) {
   RAFB200_REQUIRE(z, "rafb200_zero_launch_counts: NULL state");
   if (kernels) *kernels = z->kernels_per_step;
@@ -472,31 +476,37 @@ int rafb200_zero_step(rafb200_zero_t z, const rafb200_hyper* h, int step, void* 
   for (int it = 0; it < nb + 2; ++it) {
     if (it < nb) {
       Bucket& b = z->buckets[it];
-      int rc = launch_seg_copy(b.dev_pack, b.dev_pack_items, b.n_pack_items, gs, z->sm_count, cs);
+      int rc = RAFB200_OK;
+      if (z->stage_mask & 1)
+        rc = launch_seg_copy(b.dev_pack, b.dev_pack_items, b.n_pack_items, gs, z->sm_count, cs);
       if (rc != RAFB200_OK) return rc;
       RAFB200_CUDA(cudaEventRecord(b.packed, cs));
       RAFB200_CUDA(cudaStreamWaitEvent(ms, b.packed, 0));
-      rc = rafb200_reduce_scatter(z->comm, b.g_flat, b.g_flat + (size_t)z->rank * b.slot_elems * gs,
-                                  b.slot_elems, z->g_dtype, "sum", ms);
+      if (z->stage_mask & 2)
+        rc = rafb200_reduce_scatter(z->comm, b.g_flat, b.g_flat + (size_t)z->rank * b.slot_elems * gs,
+                                    b.slot_elems, z->g_dtype, "sum", ms);
       if (rc != RAFB200_OK) return rc;
       RAFB200_CUDA(cudaEventRecord(b.rs_done, ms));
     }
     if (it >= 1 && it - 1 < nb) {
       Bucket& b = z->buckets[it - 1];
       RAFB200_CUDA(cudaStreamWaitEvent(cs, b.rs_done, 0));
-      int rc = run_update(z, b, h, step, gscale, cs);
+      int rc = (z->stage_mask & 4) ? run_update(z, b, h, step, gscale, cs) : (int)RAFB200_OK;
       if (rc != RAFB200_OK) return rc;
       RAFB200_CUDA(cudaEventRecord(b.upd_done, cs));
       RAFB200_CUDA(cudaStreamWaitEvent(ms, b.upd_done, 0));
-      rc = rafb200_allgather(z->comm, b.p_flat + (size_t)z->rank * b.slot_elems * ps, b.p_flat,
-                             b.slot_elems, z->param_dtype, ms);
+      if (z->stage_mask & 8)
+        rc = rafb200_allgather(z->comm, b.p_flat + (size_t)z->rank * b.slot_elems * ps, b.p_flat,
+                               b.slot_elems, z->param_dtype, ms);
       if (rc != RAFB200_OK) return rc;
       RAFB200_CUDA(cudaEventRecord(b.ag_done, ms));
     }
     if (it >= 2) {
       Bucket& b = z->buckets[it - 2];
       RAFB200_CUDA(cudaStreamWaitEvent(cs, b.ag_done, 0));
-      int rc = launch_seg_copy(b.dev_unpack, b.dev_unpack_items, b.n_unpack_items, ps, z->sm_count, cs);
+      int rc = RAFB200_OK;
+      if (z->stage_mask & 16)
+        rc = launch_seg_copy(b.dev_unpack, b.dev_unpack_items, b.n_unpack_items, ps, z->sm_count, cs);
       if (rc != RAFB200_OK) return rc;
     }
   }

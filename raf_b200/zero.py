@@ -143,6 +143,10 @@ class ZeroStep:
         check(_lib.load().rafb200_zero_launch_counts(self.handle, C.byref(a), C.byref(b)))
         return a.value, b.value
 
+    def set_stage_mask(self, mask: int):
+        """Measurement aid: bit 0 pack, 1 reduce-scatter, 2 update, 3 all-gather, 4 unpack."""
+        check(_lib.load().rafb200_zero_set_stage_mask(self.handle, int(mask)))
+
     def set_update_blocks(self, max_blocks: int):
         check(_lib.load().rafb200_zero_set_update_blocks(self.handle, int(max_blocks)))
 
