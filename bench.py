@@ -228,6 +228,10 @@ def main():
     ap.add_argument("--update-blocks", type=int, default=0)
     ap.add_argument("--bucket-elems", type=int, default=None,
                     help="bucket size in elements (default: the workload's)")
+    ap.add_argument("--collectives", default="multimem", choices=["multimem", "peer", "nccl"],
+                    help="N > 1: own kernels over symmetric memory (NVSwitch multicast / peer "
+                         "pointers) or NCCL")
+    ap.add_argument("--comm-blocks", type=int, default=0, help="thread blocks per collective kernel")
     ap.add_argument("--stages", action="store_true",
                     help="N > 1: also time each stage of the step alone (pack, reduce-scatter, ...)")
     ap.add_argument("--existing-kernel", action="store_true",
@@ -288,10 +292,15 @@ def main():
     # Gradient sets: the step leaves the caller's gradients untouched (they are packed into
     # the bucket buffers first), so a set can be reused; two sets alternate.
     nsets = 1 if world == 1 else 2
+    collectives_used = args.collectives if world > 1 else "none"
     gsets = [[randn(numel(s), 1e-3 * wl["loss_scale"], gdt) for s in shapes] for _ in range(nsets)]
     zs = []
     for gs in gsets:
         z = ZeroStep(plan, comm, gdt, pdt, wl["optimizer"])
+        if world > 1 and args.collectives != "nccl":
+            z.attach_symmetric(comm_blocks=args.comm_blocks, multicast=(args.collectives == "multimem"))
+            if args.collectives == "multimem" and not z.multicast:
+                collectives_used = "peer (no multicast address available)"
         z.bind(gs, params, p, m, v if wl["optimizer"] != "sgd" else None)
         if args.update_blocks:
             z.set_update_blocks(args.update_blocks)
@@ -328,6 +337,8 @@ def main():
         zs[step_no % nsets].step(hyper, step_no, compute, comm_stream)
     e1.record(compute)
     barrier()
+    for z in zs:
+        z.status()  # raises if a bounded cross-GPU wait ran out
     clocks = sampler.stop() if rank == 0 else None
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     ms_step = ms_total / args.steps
@@ -442,7 +453,7 @@ def main():
             "config": {"workload": wl["label"], "optimizer": wl["optimizer"], "n_tensors": k,
                        "elements": total, "shard_elements_per_rank": shard_elems,
                        "bucket_elems": wl["bucket_elems"], "buckets": plan.num_buckets if world > 1 else 1,
-                       "gradient_sets": nsets,
+                       "gradient_sets": nsets, "collectives": collectives_used,
                        "l2": f"inputs larger than L2 ({wl['bytes_per_elem'] * shard_elems >> 20} MiB touched per step per rank)"},
             "roofline": roofline,
             "step_roofline": {"bound_ms": bound_ms, "frac": bound_ms / ms_step,

@@ -395,6 +395,34 @@ RAFB200_API int rafb200_zero_bind(rafb200_zero_t zero, void* const* grads, void*
 RAFB200_API int rafb200_zero_step(rafb200_zero_t zero, const rafb200_hyper* hyper, int step,
                                   void* compute_stream, void* comm_stream);
 /* Kernel launches and NCCL calls one step enqueues (for accounting). */
+/*
+ * Symmetric-memory mode (no counterpart in the reference, which always goes
+ * through NCCL).  The caller provides, for the two flat bucket buffers and a
+ * small signal pad, memory that EVERY rank has mapped: peer[q] is rank q's
+ * buffer as addressable from this process (peer[rank] is the local one), and
+ * mc is the NVSwitch multicast address bound to all of them, or NULL.  Sizes
+ * come from rafb200_zero_flat_bytes; all three must be zero-filled, on every
+ * rank, before the first step (the caller synchronises the ranks once after
+ * clearing them).  After attaching, a step runs this library's own kernels for
+ * the collectives instead of NCCL: reduce-scatter = multimem.ld_reduce of this
+ * rank's slot (sum accumulated in fp32, rounded once), all-gather =
+ * multimem.st of this rank's slot, on two streams so that they use the links
+ * in opposite directions at the same time; without a multicast address the
+ * same kernels read / write the peers one by one.  Ranks meet at two flag
+ * barriers per bucket whose waits are bounded (10 s); rafb200_zero_status
+ * synchronises the device and returns RAFB200_DEVICE_WAIT_EXPIRED if one ran
+ * out.  comm_blocks = thread blocks per collective kernel (0 = default 128).
+ * How the memory is obtained is the caller's business (cuMemCreate +
+ * cuMulticastBindMem, or torch.distributed._symmetric_memory as the Python
+ * layer of this package does).  Call between rafb200_zero_create and
+ * rafb200_zero_bind, on every rank or on none.
+ */
+RAFB200_API int rafb200_zero_flat_bytes(rafb200_zero_t zero, size_t* g_bytes, size_t* p_bytes,
+                                        size_t* signal_bytes);
+RAFB200_API int rafb200_zero_attach_symmetric(rafb200_zero_t zero, void* const* g_peer, void* g_mc,
+                                              void* const* p_peer, void* p_mc,
+                                              void* const* signal_peer, int comm_blocks);
+RAFB200_API int rafb200_zero_status(rafb200_zero_t zero);
 /* Measurement aid: issue only the selected stages of a multi-rank step
  * (bit 0 pack, 1 reduce-scatter, 2 update, 3 all-gather, 4 unpack; default 31).
  * With a stage missing the results are meaningless; every rank must use the

@@ -1,0 +1,240 @@
+// Collectives of the ZeRO step over symmetric memory: every rank's bucket buffer is mapped
+// into every process (peer pointers) and, where the NVSwitch offers it, bound to one
+// multicast address.  Reduce-scatter is then a `multimem.ld_reduce` of this rank's slot
+// (the switch fetches the slot from every GPU and returns the sum, accumulated in fp32),
+// all-gather a `multimem.st` of this rank's slot (the switch stores it into every GPU).
+// Per direction a rank moves (n-1)/n of a bucket for the pair instead of twice that with a
+// ring, and the two run in opposite directions, so they overlap.  Without a multicast
+// address the same kernels read / write the peers one by one.
+//
+// No kernel here waits on another kernel of the same GPU.  The only cross-GPU wait is the
+// flag barrier below; it is bounded by a clock and reports expiry instead of hanging.
+#include "symm.h"
+
+#include "vec_io.cuh"
+
+namespace rafb200 {
+
+__device__ __forceinline__ uint64_t symm_now_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// ---- flag barrier across GPUs ----------------------------------------------------
+// Rank r stores `epoch` into word [lane][r] of every rank's signal pad, then waits until
+// every word [lane][q] of its own pad has reached `epoch`.  Epochs only grow, so a peer
+// that is already one barrier ahead does no harm.  Work issued before the barrier in
+// stream order is complete, hence published by the release stores; work issued after it
+// starts only when every peer has arrived.
+__global__ void xbarrier_kernel(SymmPeers sig, int world, int rank, int lane, uint32_t epoch,
+                                uint64_t timeout_ns, unsigned int* err) {
+  const int t = threadIdx.x;
+  if (t >= world) return;
+  __threadfence_system();
+  uint32_t* remote = static_cast<uint32_t*>(sig.ptr[t]) + lane * kSymmMaxWorld + rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  const uint32_t* mine = static_cast<const uint32_t*>(sig.ptr[rank]) + lane * kSymmMaxWorld + t;
+  const uint64_t t0 = symm_now_ns();
+  // After a first expiry the step is lost anyway: later barriers do not wait again.
+  if (*reinterpret_cast<volatile unsigned int*>(err) != 0) return;
+  while (true) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if ((int32_t)(v - epoch) >= 0) break;
+    if (symm_now_ns() - t0 > timeout_ns) {  // a peer never arrived: report, do not hang
+      atomicCAS(err, 0u, 0x100u | (unsigned)(lane << 4) | (unsigned)t);
+      break;
+    }
+    __nanosleep(200);
+  }
+}
+
+// ---- multimem helpers (16 bytes per call) -------------------------------------------
+template <int DT>
+__device__ __forceinline__ uint4 mc_ld_reduce(const void* mc) {
+  uint4 r;
+  if (DT == RAFB200_F16) {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc) : "memory");
+  } else if (DT == RAFB200_BF16) {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc) : "memory");
+  } else {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc) : "memory");
+  }
+  return r;
+}
+
+__device__ __forceinline__ void mc_st(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ uint4 peer_ld(const void* p) {
+  uint4 r;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+  return r;
+}
+
+template <int DT>
+__device__ __forceinline__ void accumulate(float (&acc)[8], uint4 v) {
+  if (DT == RAFB200_F32) {
+    acc[0] += __uint_as_float(v.x);
+    acc[1] += __uint_as_float(v.y);
+    acc[2] += __uint_as_float(v.z);
+    acc[3] += __uint_as_float(v.w);
+  } else {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f;
+      if (DT == RAFB200_F16) f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      else f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+      acc[2 * i] += f.x;
+      acc[2 * i + 1] += f.y;
+    }
+  }
+}
+
+template <int DT>
+__device__ __forceinline__ uint4 round_once(const float (&acc)[8]) {
+  uint4 r;
+  if (DT == RAFB200_F32) {
+    r.x = __float_as_uint(acc[0]);
+    r.y = __float_as_uint(acc[1]);
+    r.z = __float_as_uint(acc[2]);
+    r.w = __float_as_uint(acc[3]);
+  } else {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (DT == RAFB200_F16) {
+        __half2 h = __floats2half2_rn(acc[2 * i], acc[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    r = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  return r;
+}
+
+constexpr int kSymmThreads = 256;
+constexpr int kSymmUnroll = 8;  // 16-byte accesses in flight per thread
+
+// dst (local, this rank's slot) = sum over ranks of the slot at byte offset `off`.
+template <int DT, bool MC>
+__global__ void __launch_bounds__(kSymmThreads)
+    symm_reduce_scatter_kernel(SymmPeers peers, const char* mc, size_t off, char* dst, int64_t nvec,
+                               int world) {
+  const int64_t stride = (int64_t)gridDim.x * kSymmThreads;
+  for (int64_t i0 = (int64_t)blockIdx.x * kSymmThreads + threadIdx.x; i0 < nvec; i0 += stride * kSymmUnroll) {
+    uint4 out[kSymmUnroll];
+#pragma unroll
+    for (int u = 0; u < kSymmUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i >= nvec) continue;
+      if (MC) {
+        out[u] = mc_ld_reduce<DT>(mc + off + (size_t)i * 16);
+      } else {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int q = 0; q < world; ++q)  // fixed order: the same bits on every run
+          accumulate<DT>(acc, peer_ld(static_cast<const char*>(peers.ptr[q]) + off + (size_t)i * 16));
+        out[u] = round_once<DT>(acc);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kSymmUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < nvec) *reinterpret_cast<uint4*>(dst + (size_t)i * 16) = out[u];
+    }
+  }
+}
+
+// Every rank's copy of the slot at byte offset `off` = src (local).
+template <bool MC>
+__global__ void __launch_bounds__(kSymmThreads)
+    symm_allgather_kernel(SymmPeers peers, char* mc, size_t off, const char* src, int64_t nvec, int world,
+                          int rank) {
+  const int64_t stride = (int64_t)gridDim.x * kSymmThreads;
+  for (int64_t i0 = (int64_t)blockIdx.x * kSymmThreads + threadIdx.x; i0 < nvec; i0 += stride * kSymmUnroll) {
+    uint4 v[kSymmUnroll];
+#pragma unroll
+    for (int u = 0; u < kSymmUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i < nvec) v[u] = *reinterpret_cast<const uint4*>(src + (size_t)i * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < kSymmUnroll; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i >= nvec) continue;
+      if (MC) {
+        mc_st(mc + off + (size_t)i * 16, v[u]);
+      } else {
+        for (int q = 0; q < world; ++q)
+          if (q != rank)
+            *reinterpret_cast<uint4*>(static_cast<char*>(peers.ptr[q]) + off + (size_t)i * 16) = v[u];
+      }
+    }
+  }
+}
+
+static unsigned symm_grid(int64_t nvec, int blocks) {
+  int64_t g = (nvec + (int64_t)kSymmThreads * kSymmUnroll - 1) / ((int64_t)kSymmThreads * kSymmUnroll);
+  if (g > blocks) g = blocks;
+  return (unsigned)(g < 1 ? 1 : g);
+}
+
+int symm_barrier(const SymmPeers& sig, int world, int rank, int lane, uint32_t epoch,
+                 unsigned int* err, cudaStream_t s) {
+  xbarrier_kernel<<<1, 32, 0, s>>>(sig, world, rank, lane, epoch, 10000000000ull, err);
+  RAFB200_CUDA(cudaGetLastError());
+  return RAFB200_OK;
+}
+
+template <int DT>
+static int launch_rs(const SymmPeers& peers, const void* mc, size_t off, void* dst, int64_t nvec, int world,
+                     int blocks, cudaStream_t s) {
+  const unsigned g = symm_grid(nvec, blocks);
+  if (mc)
+    symm_reduce_scatter_kernel<DT, true><<<g, kSymmThreads, 0, s>>>(peers, static_cast<const char*>(mc), off,
+                                                                    static_cast<char*>(dst), nvec, world);
+  else
+    symm_reduce_scatter_kernel<DT, false><<<g, kSymmThreads, 0, s>>>(peers, nullptr, off,
+                                                                     static_cast<char*>(dst), nvec, world);
+  RAFB200_CUDA(cudaGetLastError());
+  return RAFB200_OK;
+}
+
+int symm_reduce_scatter(const SymmPeers& peers, const void* mc, size_t off, void* dst, int64_t bytes,
+                        int dtype, int world, int blocks, cudaStream_t s) {
+  RAFB200_REQUIRE(bytes % 16 == 0 && off % 16 == 0, "symm_reduce_scatter: slot is not 16-byte aligned");
+  if (bytes == 0) return RAFB200_OK;
+  switch (dtype) {
+    case RAFB200_F32: return launch_rs<RAFB200_F32>(peers, mc, off, dst, bytes / 16, world, blocks, s);
+    case RAFB200_F16: return launch_rs<RAFB200_F16>(peers, mc, off, dst, bytes / 16, world, blocks, s);
+    default: return launch_rs<RAFB200_BF16>(peers, mc, off, dst, bytes / 16, world, blocks, s);
+  }
+}
+
+int symm_allgather(const SymmPeers& peers, void* mc, size_t off, const void* src, int64_t bytes, int world,
+                   int rank, int blocks, cudaStream_t s) {
+  RAFB200_REQUIRE(bytes % 16 == 0 && off % 16 == 0, "symm_allgather: slot is not 16-byte aligned");
+  if (bytes == 0) return RAFB200_OK;
+  const unsigned g = symm_grid(bytes / 16, blocks);
+  if (mc)
+    symm_allgather_kernel<true><<<g, kSymmThreads, 0, s>>>(peers, static_cast<char*>(mc), off,
+                                                          static_cast<const char*>(src), bytes / 16, world, rank);
+  else
+    symm_allgather_kernel<false><<<g, kSymmThreads, 0, s>>>(peers, nullptr, off, static_cast<const char*>(src),
+                                                           bytes / 16, world, rank);
+  RAFB200_CUDA(cudaGetLastError());
+  return RAFB200_OK;
+}
+
+}  // namespace rafb200

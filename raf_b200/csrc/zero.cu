@@ -8,6 +8,7 @@
 #include <memory>
 
 #include "common.h"
+#include "symm.h"
 #include "vec_io.cuh"
 
 struct rafb200_plan_s {
@@ -131,12 +132,24 @@ struct rafb200_zero_s {
   char* g_flat = nullptr;  // all buckets' gradient buffers, one allocation (n > 1)
   char* p_flat = nullptr;  // all buckets' parameter-copy buffers
   int sm_count = 148;
+  int64_t flat_elems = 0;  // elements of each flat buffer (all buckets, all slots)
   std::vector<void*> grads, params;
   std::vector<float*> p, m, v;
   bool bound = false;
   cudaEvent_t ev_start = nullptr, ev_done = nullptr;
   int max_update_blocks = 0;
   int stage_mask = 31;  // measurement aid: which of the five stages a step issues
+  // symmetric-memory mode (rafb200_zero_attach_symmetric): the flat buffers live in memory
+  // every rank has mapped; the collectives are this library's own kernels, not NCCL's
+  bool symmetric = false;
+  rafb200::SymmPeers g_peers{}, p_peers{}, sig_peers{};
+  void* g_mc = nullptr;
+  void* p_mc = nullptr;
+  unsigned int* dev_err = nullptr;   // first expired cross-GPU wait, 0 if none
+  uint32_t epoch[2] = {0, 0};        // barrier lanes: 0 before reduce-scatter, 1 after all-gather
+  cudaStream_t gather_stream = nullptr;
+  cudaEvent_t ev_gather = nullptr;
+  int comm_blocks = 128;
   int kernels_per_step = 0, collectives_per_step = 0;
 };
 
@@ -233,8 +246,11 @@ int rafb200_zero_destroy(rafb200_zero_t z) {
                       (void*)b.dev_unpack_items})
       if (ptr) cudaFree(ptr);
   }
-  if (z->g_flat) rafb200_comm_free(z->comm, z->g_flat);
-  if (z->p_flat) rafb200_comm_free(z->comm, z->p_flat);
+  if (z->g_flat && !z->symmetric) rafb200_comm_free(z->comm, z->g_flat);
+  if (z->p_flat && !z->symmetric) rafb200_comm_free(z->comm, z->p_flat);
+  if (z->dev_err) cudaFree(z->dev_err);
+  if (z->gather_stream) cudaStreamDestroy(z->gather_stream);
+  if (z->ev_gather) cudaEventDestroy(z->ev_gather);
   if (z->ev_start) cudaEventDestroy(z->ev_start);
   if (z->ev_done) cudaEventDestroy(z->ev_done);
   delete z;
@@ -302,6 +318,7 @@ int rafb200_zero_create(rafb200_plan_t plan, rafb200_comm_t comm, int g_dtype, i
       rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: cannot create events");
       break;
     }
+    z->flat_elems = flat_elems;
     if (z->n > 1 && flat_elems > 0) {
       const size_t gbytes = (size_t)flat_elems * dtype_size(g_dtype);
       const size_t pbytes = (size_t)flat_elems * dtype_size(param_dtype);
@@ -408,6 +425,68 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
   return RAFB200_OK;
 }
 
+int rafb200_zero_flat_bytes(rafb200_zero_t z, size_t* g_bytes, size_t* p_bytes, size_t* signal_bytes) {
+  RAFB200_REQUIRE(z, "rafb200_zero_flat_bytes: NULL state");
+  const int64_t e = z->n > 1 ? z->flat_elems : 0;
+  if (g_bytes) *g_bytes = (size_t)e * dtype_size(z->g_dtype);
+  if (p_bytes) *p_bytes = (size_t)e * dtype_size(z->param_dtype);
+  if (signal_bytes) *signal_bytes = kSymmSignalBytes;
+  return RAFB200_OK;
+}
+
+int rafb200_zero_attach_symmetric(rafb200_zero_t z, void* const* g_peer, void* g_mc, void* const* p_peer,
+                                  void* p_mc, void* const* signal_peer, int comm_blocks) {
+  RAFB200_REQUIRE(z && g_peer && p_peer && signal_peer, "rafb200_zero_attach_symmetric: NULL argument");
+  RAFB200_REQUIRE(z->n > 1, "rafb200_zero_attach_symmetric: a world of one has no collectives");
+  RAFB200_REQUIRE(z->n <= kSymmMaxWorld, "rafb200_zero_attach_symmetric: at most %d ranks", kSymmMaxWorld);
+  RAFB200_REQUIRE(!z->bound, "rafb200_zero_attach_symmetric: attach before rafb200_zero_bind");
+  RAFB200_REQUIRE(!z->symmetric, "rafb200_zero_attach_symmetric: already attached");
+  RAFB200_REQUIRE((g_mc == nullptr) == (p_mc == nullptr),
+                  "rafb200_zero_attach_symmetric: give both multicast addresses or neither");
+  for (int q = 0; q < z->n; ++q) {
+    RAFB200_REQUIRE(g_peer[q] && p_peer[q] && signal_peer[q],
+                    "rafb200_zero_attach_symmetric: NULL mapping of rank %d", q);
+    RAFB200_REQUIRE(((reinterpret_cast<uintptr_t>(g_peer[q]) | reinterpret_cast<uintptr_t>(p_peer[q])) & 15u) == 0,
+                    "rafb200_zero_attach_symmetric: buffers must be 16-byte aligned");
+    z->g_peers.ptr[q] = g_peer[q];
+    z->p_peers.ptr[q] = p_peer[q];
+    z->sig_peers.ptr[q] = signal_peer[q];
+  }
+  RAFB200_CUDA(cudaMalloc(reinterpret_cast<void**>(&z->dev_err), 16));
+  RAFB200_CUDA(cudaMemset(z->dev_err, 0, 16));
+  RAFB200_CUDA(cudaStreamCreateWithFlags(&z->gather_stream, cudaStreamNonBlocking));
+  RAFB200_CUDA(cudaEventCreateWithFlags(&z->ev_gather, cudaEventDisableTiming));
+  // The NCCL-registered buffers of rafb200_zero_create are not needed in this mode.
+  if (z->g_flat) rafb200_comm_free(z->comm, z->g_flat);
+  if (z->p_flat) rafb200_comm_free(z->comm, z->p_flat);
+  z->g_flat = static_cast<char*>(g_peer[z->rank]);
+  z->p_flat = static_cast<char*>(p_peer[z->rank]);
+  z->g_mc = g_mc;
+  z->p_mc = p_mc;
+  z->symmetric = true;
+  if (comm_blocks > 0) z->comm_blocks = comm_blocks;
+  int64_t at = 0;
+  for (auto& b : z->buckets) {
+    b.g_flat = z->g_flat + (size_t)at * dtype_size(z->g_dtype);
+    b.p_flat = z->p_flat + (size_t)at * dtype_size(z->param_dtype);
+    at += b.slot_elems * z->n;
+  }
+  return RAFB200_OK;
+}
+
+int rafb200_zero_status(rafb200_zero_t z) {
+  RAFB200_REQUIRE(z, "rafb200_zero_status: NULL state");
+  RAFB200_CUDA(cudaDeviceSynchronize());
+  if (!z->dev_err) return RAFB200_OK;
+  unsigned int e = 0;
+  RAFB200_CUDA(cudaMemcpy(&e, z->dev_err, sizeof(e), cudaMemcpyDeviceToHost));
+  if (e != 0)
+    return set_error(RAFB200_DEVICE_WAIT_EXPIRED,
+                     "rafb200_zero_step: rank %u did not reach barrier lane %u within the limit",
+                     e & 15u, (e >> 4) & 15u);
+  return RAFB200_OK;
+}
+
 int rafb200_zero_set_update_blocks(rafb200_zero_t z, int max_blocks) {
   RAFB200_REQUIRE(z && max_blocks >= 0, "rafb200_zero_set_update_blocks: bad arguments");
   z->max_update_blocks = max_blocks;
@@ -469,6 +548,7 @@ int rafb200_zero_step(rafb200_zero_t z, const rafb200_hyper* h, int step, void* 
   // stream that still uses the flat buffers (the previous step's unpack).
   RAFB200_CUDA(cudaEventRecord(z->ev_start, cs));
   RAFB200_CUDA(cudaStreamWaitEvent(ms, z->ev_start, 0));
+  if (z->symmetric) RAFB200_CUDA(cudaStreamWaitEvent(z->gather_stream, z->ev_start, 0));
   // Software pipeline over buckets; stage s of bucket b is issued in iteration b + s:
   //   0 pack (compute)  1 reduce-scatter (comm)  2 update (compute)  3 all-gather (comm)
   //   4 unpack (compute)
@@ -482,9 +562,17 @@ int rafb200_zero_step(rafb200_zero_t z, const rafb200_hyper* h, int step, void* 
       if (rc != RAFB200_OK) return rc;
       RAFB200_CUDA(cudaEventRecord(b.packed, cs));
       RAFB200_CUDA(cudaStreamWaitEvent(ms, b.packed, 0));
-      if (z->stage_mask & 2)
+      if ((z->stage_mask & 2) && !z->symmetric)
         rc = rafb200_reduce_scatter(z->comm, b.g_flat, b.g_flat + (size_t)z->rank * b.slot_elems * gs,
                                     b.slot_elems, z->g_dtype, "sum", ms);
+      if ((z->stage_mask & 2) && z->symmetric) {
+        // every rank has packed this bucket -> sum this rank's slot over all ranks, in place
+        rc = symm_barrier(z->sig_peers, z->n, z->rank, 0, ++z->epoch[0], z->dev_err, ms);
+        if (rc != RAFB200_OK) return rc;
+        const size_t off = (size_t)(b.g_flat - z->g_flat) + (size_t)z->rank * b.slot_elems * gs;
+        rc = symm_reduce_scatter(z->g_peers, z->g_mc, off, z->g_flat + off, b.slot_elems * gs, z->g_dtype,
+                                 z->n, z->comm_blocks, ms);
+      }
       if (rc != RAFB200_OK) return rc;
       RAFB200_CUDA(cudaEventRecord(b.rs_done, ms));
     }
@@ -494,12 +582,23 @@ int rafb200_zero_step(rafb200_zero_t z, const rafb200_hyper* h, int step, void* 
       int rc = (z->stage_mask & 4) ? run_update(z, b, h, step, gscale, cs) : (int)RAFB200_OK;
       if (rc != RAFB200_OK) return rc;
       RAFB200_CUDA(cudaEventRecord(b.upd_done, cs));
-      RAFB200_CUDA(cudaStreamWaitEvent(ms, b.upd_done, 0));
-      if (z->stage_mask & 8)
+      // In symmetric mode the all-gather has a stream of its own: it loads the links in the
+      // direction the reduce-scatter leaves idle, so the two overlap.
+      cudaStream_t as = z->symmetric ? z->gather_stream : ms;
+      RAFB200_CUDA(cudaStreamWaitEvent(as, b.upd_done, 0));
+      if ((z->stage_mask & 8) && !z->symmetric)
         rc = rafb200_allgather(z->comm, b.p_flat + (size_t)z->rank * b.slot_elems * ps, b.p_flat,
                                b.slot_elems, z->param_dtype, ms);
+      if ((z->stage_mask & 8) && z->symmetric) {
+        const size_t off = (size_t)(b.p_flat - z->p_flat) + (size_t)z->rank * b.slot_elems * ps;
+        rc = symm_allgather(z->p_peers, z->p_mc, off, z->p_flat + off, b.slot_elems * ps, z->n, z->rank,
+                            z->comm_blocks, as);
+        if (rc != RAFB200_OK) return rc;
+        // every rank's slot has landed here before the unpack reads the buffer
+        rc = symm_barrier(z->sig_peers, z->n, z->rank, 1, ++z->epoch[1], z->dev_err, as);
+      }
       if (rc != RAFB200_OK) return rc;
-      RAFB200_CUDA(cudaEventRecord(b.ag_done, ms));
+      RAFB200_CUDA(cudaEventRecord(b.ag_done, as));
     }
     if (it >= 2) {
       Bucket& b = z->buckets[it - 2];

@@ -143,6 +143,45 @@ class ZeroStep:
         check(_lib.load().rafb200_zero_launch_counts(self.handle, C.byref(a), C.byref(b)))
         return a.value, b.value
 
+    def attach_symmetric(self, group=None, comm_blocks: int = 0, multicast: bool = True):
+        """Switch the collectives of this step from NCCL to the library's own kernels over
+        symmetric memory.  torch.distributed._symmetric_memory provides the plumbing only:
+        one allocation mapped into every rank of ``group`` (default: the world group, which
+        must be initialised) plus its NVSwitch multicast address.  Call on every rank,
+        before :meth:`bind`."""
+        import torch.distributed as td
+        import torch.distributed._symmetric_memory as symm
+
+        lib = _lib.load()
+        gb, pb, sb = C.c_size_t(), C.c_size_t(), C.c_size_t()
+        check(lib.rafb200_zero_flat_bytes(self.handle, C.byref(gb), C.byref(pb), C.byref(sb)))
+
+        def up(x):
+            return (x + 4095) & ~4095
+
+        sig_off, g_off = 0, up(sb.value)
+        p_off = g_off + up(gb.value)
+        total = p_off + up(pb.value)
+        buf = symm.empty(total, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+        handle = symm.rendezvous(buf, group if group is not None else td.group.WORLD)
+        buf.zero_()  # padding rows, alignment gaps and barrier words all start at zero
+        torch.cuda.synchronize()
+        handle.barrier()
+        torch.cuda.synchronize()
+        bases = [int(x) for x in handle.buffer_ptrs]
+        mc = int(handle.multicast_ptr) if multicast else 0
+        pa = _lib.ptr_array
+        check(lib.rafb200_zero_attach_symmetric(
+            self.handle, pa([b + g_off for b in bases]), (mc + g_off) if mc else None,
+            pa([b + p_off for b in bases]), (mc + p_off) if mc else None,
+            pa([b + sig_off for b in bases]), int(comm_blocks)))
+        self._symm = (buf, handle)  # keeps the mapping alive
+        self.multicast = bool(mc)
+
+    def status(self):
+        """Synchronise the device; raise if a bounded cross-GPU wait of a step ran out."""
+        check(_lib.load().rafb200_zero_status(self.handle))
+
     def set_stage_mask(self, mask: int):
         """Measurement aid: bit 0 pack, 1 reduce-scatter, 2 update, 3 all-gather, 4 unpack."""
         check(_lib.load().rafb200_zero_set_stage_mask(self.handle, int(mask)))

@@ -1,6 +1,7 @@
 """One rank of the multi-GPU tests (started by tests/test_dist_gpu.py, one process per GPU).
 
-Environment: RANK, WORLD_SIZE, LOCAL_RANK, RAF_FILE_STORE_PATH (id exchange), OUT_DIR.
+Environment: RANK, WORLD_SIZE, LOCAL_RANK, MASTER_ADDR, MASTER_PORT, RAF_FILE_STORE_PATH (id
+exchange), OUT_DIR.
 Part 1 checks the collectives against the known answers of the reference's own tests
 (tests/python/distributed/test_collective_communication.py:73-121,230-255,637-754:
 rank-valued inputs whose reductions are exact integers).  Part 2 runs the ZeRO step
@@ -93,11 +94,18 @@ def check_collectives(comm):
     comm.check()
 
 
-def run_zero(comm, out_dir):
+MODES = ["nccl", "multimem", "peer"]  # collectives by NCCL / own kernels with / without multicast
+
+
+def run_zero(comm, out_dir, mode):
     n, r = comm.size, comm.rank
     for case, (optimizer, g_dtype, p_dtype) in enumerate(CASES):
         plan = Plan(SHAPES, n, r, BUCKET)
         z = ZeroStep(plan, comm, g_dtype, p_dtype, optimizer)
+        if mode != "nccl":
+            z.attach_symmetric(multicast=(mode == "multimem"))
+            if mode == "multimem":
+                assert z.multicast, "no multicast address on this box"
         rng = np.random.default_rng(0)
         full_p = [(rng.standard_normal(numel(s)) * 0.02).astype(np.float32) for s in SHAPES]
         tp, tm, tv = [], [], []
@@ -118,7 +126,7 @@ def run_zero(comm, out_dir):
             grads = [local_grad(r, step, i, numel(s), g_dtype, 1 / scale).cuda() for i, s in enumerate(SHAPES)]
             z.bind(grads, params, tp, tm, tv)
             z.step(hyper, step)
-            torch.cuda.synchronize()
+            z.status()
             if step == 1:  # the caller's gradients are inputs only: the step must not modify them
                 for i, s in enumerate(SHAPES):
                     again = local_grad(r, step, i, numel(s), g_dtype, 1 / scale)
@@ -130,18 +138,26 @@ def run_zero(comm, out_dir):
             saved[f"param_{i}"] = params[i].float().cpu().numpy()
         kernels, collectives = z.launch_counts()
         saved["counts"] = np.array([kernels, collectives, plan.num_buckets])
-        np.savez(os.path.join(out_dir, f"case{case}_rank{r}.npz"), **saved)
+        np.savez(os.path.join(out_dir, f"case{case}_{mode}_rank{r}.npz"), **saved)
         z.close()
         plan.close()
 
 
 def main():
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    import torch.distributed as td
+
     comm = dist.init_from_env(timeout_ms=120000)
     check_collectives(comm)
-    run_zero(comm, os.environ["OUT_DIR"])
+    # torch.distributed only carries the symmetric-memory rendezvous of the two non-NCCL modes
+    td.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    for mode in MODES:
+        run_zero(comm, os.environ["OUT_DIR"], mode)
+    torch.cuda.synchronize()
+    td.barrier()
     torch.cuda.synchronize()
     comm.close()
+    td.destroy_process_group()
     print(f"rank {comm.rank}: ok", flush=True)
 
 

@@ -6,8 +6,11 @@ collectives themselves, and write what each rank ended with; this process then r
 same three steps per rank shard on the oracle.  Rank-local gradients are small integers
 times a power of two, so their sum over ranks is exact in every dtype and in any order:
 the reduced gradient is known exactly and SGD / Adam must match the oracle bit for bit at
-any world size; LANS within 1e-5.
+any world size; LANS within 1e-5.  Each case runs three times: collectives by NCCL, by the
+library's own kernels over symmetric memory with the NVSwitch multicast address
+(multimem.ld_reduce / multimem.st), and by the same kernels over plain peer pointers.
 """
+import itertools
 import os
 import subprocess
 import sys
@@ -26,11 +29,16 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _spawn(world, out_dir, store):
+    import socket
+
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
     procs = []
     for r in range(world):
         env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r),
                    RAF_FILE_STORE_PATH=store, OUT_DIR=out_dir, NCCL_NVLS_ENABLE="0",
-                   MASTER_ADDR="127.0.0.1")
+                   MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
         procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "dist_worker.py")],
                                       env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
                                       text=True))
@@ -59,8 +67,8 @@ def test_collectives_and_zero_step_multi_gpu(world):
         store = os.path.join(tmp, "store")
         os.makedirs(store)
         _spawn(world, tmp, store)
-        for case, (optimizer, g_dtype, p_dtype) in enumerate(W.CASES):
-            ranks = [np.load(os.path.join(tmp, f"case{case}_rank{r}.npz")) for r in range(world)]
+        for mode, (case, (optimizer, g_dtype, p_dtype)) in itertools.product(W.MODES, enumerate(W.CASES)):
+            ranks = [np.load(os.path.join(tmp, f"case{case}_{mode}_rank{r}.npz")) for r in range(world)]
             scale = 2.0 ** -15 if g_dtype == "float16" else 1.0
             gscale = scale / world  # the mean over ranks folded into the gradient scale
             rng = np.random.default_rng(0)
@@ -99,7 +107,7 @@ def test_collectives_and_zero_step_multi_gpu(world):
                         assert rel_err(got_p, p[i]) < 1e-5 and rel_err(got_m, m[i]) < 1e-5
                         assert rel_err(got_v, v[i]) < 1e-5
                     else:
-                        assert bits_equal(got_p, p[i]) and bits_equal(got_m, m[i]), (case, r, i)
+                        assert bits_equal(got_p, p[i]) and bits_equal(got_m, m[i]), (mode, case, r, i)
                         if optimizer == "adam":
                             assert bits_equal(got_v, v[i])
                     # every rank's gathered parameter holds this rank's block (padding rows dropped)
@@ -116,7 +124,7 @@ def test_collectives_and_zero_step_multi_gpu(world):
                             if optimizer == "lans":
                                 assert rel_err(got, want) < (1e-5 if p_dtype == "float32" else 2e-3)
                             else:
-                                assert bits_equal(got, want), (case, r, q, i)
+                                assert bits_equal(got, want), (mode, case, r, q, i)
                 kernels, collectives, nb = ranks[r]["counts"]
                 # per bucket: pack, update, unpack kernels and ONE reduce-scatter + ONE all-gather
                 assert kernels == 3 * nb and collectives == 2 * nb
