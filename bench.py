@@ -36,6 +36,17 @@ if ROOT not in sys.path:
 L2_BYTES = 126 << 20
 
 
+NVLINK_MEASURED_GBS = 770.0  # peer copy, per direction per GPU, measured on this pool
+# DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu captures
+# summarised under profiles/ (workload, n_gpus, shard_of) -> bytes
+MEASURED_TRAFFIC = {
+    ("bert_lans", 1, 1): 14312909824,   # profiles/lans_kernel_bert_large_n1.md
+    ("bert_lans", 1, 8): 1689914872,    # profiles/lans_kernel_bert_large_shard8_full.md
+    ("rn50_sgd", 1, 1): 556562432,      # profiles/update_list_kernel_sgd_rn50.md
+    ("gpt2_adam", 1, 8): 1184124416,    # profiles/update_list_kernel_adam_gpt2_shard8.md
+}
+
+
 # --------------------------------------------------------------------------- workloads
 def workload(name: str):
     """-> dict(shapes, optimizer, g_dtype, p_dtype, hyper kwargs, bucket_elems, bytes_per_elem, label)"""
@@ -228,6 +239,9 @@ def main():
     ap.add_argument("--update-blocks", type=int, default=0)
     ap.add_argument("--bucket-elems", type=int, default=None,
                     help="bucket size in elements (default: the workload's)")
+    ap.add_argument("--shard-of", type=int, default=0,
+                    help="N = 1 only: run on the shard list that rank 0 of an N-way partition owns "
+                         "(a small case of the same kernel, e.g. for profiler captures)")
     ap.add_argument("--collectives", default="multimem", choices=["multimem", "peer", "nccl"],
                     help="N > 1: own kernels over symmetric memory (NVSwitch multicast / peer "
                          "pointers) or NCCL")
@@ -274,6 +288,13 @@ def main():
     dist.set_communicator(comm)
 
     shapes = wl["shapes"]
+    if args.shard_of > 1:
+        if world != 1:
+            raise SystemExit("--shard-of needs --gpus 1")
+        part = Plan(shapes, args.shard_of, 0, wl["bucket_elems"])
+        shapes = [part.shard_shape(i) for i in range(len(shapes))]
+        wl["label"] += f" -- rank 0's shards of a {args.shard_of}-way partition, no collectives"
+        part.close()
     k = len(shapes)
     total = sum(numel(s) for s in shapes)
     plan = Plan(shapes, world, rank, wl["bucket_elems"])
@@ -371,7 +392,9 @@ def main():
     peak, peak_src = measured_hbm_peak()
     achieved = wl["bytes_per_elem"] * shard_elems / (kern_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                "frac": achieved / peak,
+                "traffic": MEASURED_TRAFFIC.get((args.workload, world, args.shard_of if args.shard_of > 1 else 1)),
+                "peak_source": peak_src,
                 "kernel": {"sgd": "update_list_kernel<SgdOp>", "adam": "update_list_kernel<AdamOp>",
                            "lans": "lans_kernel"}[wl["optimizer"]],
                 "kernel_ms": kern_ms, "algorithmic_bytes_per_launch": wl["bytes_per_elem"] * shard_elems}
@@ -379,7 +402,9 @@ def main():
     # ---- step roofline: slower of update bytes at HBM peak and collective bytes at 900 GB/s ----
     gsz, psz = gsets[0][0].element_size(), params[0].element_size()
     coll_bytes = (world - 1) / world * int(plan.total_padded) * (gsz + psz)
-    bound_ms = max(wl["bytes_per_elem"] * shard_elems / (peak * 1e9), coll_bytes / 900e9) * 1e3
+    # measured peer-copy bandwidth of this pool (770 GB/s per direction per GPU); 900 nominal
+    bound_ms = max(wl["bytes_per_elem"] * shard_elems / (peak * 1e9), coll_bytes / NVLINK_MEASURED_GBS / 1e9) * 1e3
+    bound_nominal_ms = max(wl["bytes_per_elem"] * shard_elems / (peak * 1e9), coll_bytes / 900e9) * 1e3
 
     # ---- end to end: host gradients in, host parameters out ----
     e2e = None
@@ -457,7 +482,10 @@ def main():
                        "l2": f"inputs larger than L2 ({wl['bytes_per_elem'] * shard_elems >> 20} MiB touched per step per rank)"},
             "roofline": roofline,
             "step_roofline": {"bound_ms": bound_ms, "frac": bound_ms / ms_step,
-                              "collective_bytes_per_direction": coll_bytes, "nvlink_gbs": 900},
+                              "collective_bytes_per_direction": coll_bytes,
+                              "nvlink_gbs": NVLINK_MEASURED_GBS, "nvlink_source": "measured peer copy on this pool",
+                              "bound_ms_at_nominal_900": bound_nominal_ms,
+                              "frac_at_nominal_900": bound_nominal_ms / ms_step},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": kernels * args.steps,
             "nccl_calls": collectives * args.steps, "clocks": clocks,
         }
