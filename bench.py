@@ -148,76 +148,104 @@ def measured_hbm_peak():
 
 
 # --------------------------------------------------------------------------- CPU baseline
-def cpu_baseline(wl, budget_s=12.0):
-    """The oracle on the host cores over a growing prefix of the workload's tensors until
-    about `budget_s` seconds of CPU work have been spent.  Returns elements/s of one rank's
-    full-size (unsharded) update, i.e. the reference math without collectives."""
-    import numpy as np
+class CpuArm:
+    """The oracle (C/OpenMP restatement of the reference math) on the host cores: one rank's
+    full-size, unsharded update of a prefix of the workload's tensors, no collectives.
+    Inputs are generated once (untimed); every `step()` is one optimizer step over them."""
 
-    from oracle import oracle as O
-    from raf_b200.zero import numel
+    def __init__(self, wl, max_elems=None):
+        import numpy as np
 
-    code = {"float32": O.F32, "float16": O.F16, "bfloat16": O.BF16}
-    rng = np.random.default_rng(0)
-    done_elems, spent, used = 0, 0.0, 0
-    hy = wl["hyper"]
-    order = sorted(range(len(wl["shapes"])), key=lambda i: -numel(wl["shapes"][i]))
-    # largest tensors first would bias the sample; walk in model order instead
-    order = list(range(len(wl["shapes"])))
-    for i in order:
-        n = numel(wl["shapes"][i])
-        if n == 0:
-            continue
-        p = (rng.standard_normal(n, dtype=np.float32) * 0.02)
-        m = np.zeros(n, np.float32)
-        v = np.zeros(n, np.float32)
-        g32 = rng.standard_normal(n, dtype=np.float32) * (1e-3 * wl["loss_scale"])
-        g = O.cast(g32, code[wl["g_dtype"]]) if wl["g_dtype"] != "float32" else g32
-        oc = code[wl["p_dtype"]]
+        from oracle import oracle as O
+        from raf_b200.zero import numel
+
+        self.O, self.wl = O, wl
+        code = {"float32": O.F32, "float16": O.F16, "bfloat16": O.BF16}
+        self.out_code = code[wl["p_dtype"]]
+        rng = np.random.default_rng(0)
+        self.p, self.m, self.v, self.g = [], [], [], []
+        self.elems = 0
+        for s in wl["shapes"]:
+            n = numel(s)
+            if n == 0:
+                continue
+            if max_elems is not None and self.elems + n > max_elems and self.elems > 0:
+                break
+            self.p.append(rng.standard_normal(n, dtype=np.float32) * np.float32(0.02))
+            self.m.append(np.zeros(n, np.float32))
+            self.v.append(np.zeros(n, np.float32))
+            g32 = rng.standard_normal(n, dtype=np.float32) * np.float32(1e-3 * wl["loss_scale"])
+            self.g.append(O.cast(g32, code[wl["g_dtype"]]) if wl["g_dtype"] != "float32" else g32)
+            self.elems += n
+        self.tensors = len(self.p)
+        self.step_no = 0
+
+    def step(self) -> float:
+        """One optimizer step; returns its wall time in seconds."""
+        O, wl, hy = self.O, self.wl, self.wl["hyper"]
+        self.step_no += 1
+        scale = 1.0 / wl["loss_scale"]
         t0 = time.perf_counter()
         if wl["optimizer"] == "sgd":
-            O.sgd(p, g, m, hy["learning_rate"], hy["mu"], hy["weight_decay"], 1.0 / wl["loss_scale"], out_code=oc)
+            for p, g, m in zip(self.p, self.g, self.m):
+                O.sgd(p, g, m, hy["learning_rate"], hy["mu"], hy["weight_decay"], scale, out_code=self.out_code)
         elif wl["optimizer"] == "adam":
-            O.adam(g, p, m, v, 1, hy["learning_rate"], hy["beta1"], hy["beta2"], hy["eps"], 1,
-                   hy["weight_decay"], hy["mode"], 1.0 / wl["loss_scale"], out_code=oc)
+            for p, g, m, v in zip(self.p, self.g, self.m, self.v):
+                O.adam(g, p, m, v, self.step_no, hy["learning_rate"], hy["beta1"], hy["beta2"], hy["eps"], 1,
+                       hy["weight_decay"], hy["mode"], scale, out_code=self.out_code)
         else:
-            O.lans([g], [p], [m], [v], 1, hy["learning_rate"], hy["beta1"], hy["beta2"], hy["eps"], 1,
-                   hy["weight_decay"], 1, 1, 1, 1.0 / wl["loss_scale"], norm_mode=0, out_code=oc)
-        spent += time.perf_counter() - t0
-        done_elems += n
-        used += 1
-        if spent >= budget_s:
-            break
-    return {"value": done_elems / spent if spent > 0 else None, "unit": "param-elements/s",
-            "cores": O.num_threads(), "kind": "port",
-            "sample": f"first {used} of {len(wl['shapes'])} tensors ({done_elems} elements), one update, "
-                      f"{spent:.2f} s of host time; C/OpenMP restatement of the reference math "
-                      f"(RAF's TVM CPU path cannot be built here; LANS and Adam have no CPU path in RAF)"}
+            O.lans(self.g, self.p, self.m, self.v, self.step_no, hy["learning_rate"], hy["beta1"], hy["beta2"],
+                   hy["eps"], 1, hy["weight_decay"], 1, 1, 1, scale, norm_mode=0, out_code=self.out_code)
+        return time.perf_counter() - t0
+
+    def describe(self, steps, spent):
+        return (f"first {self.tensors} of {len(self.wl['shapes'])} tensors ({self.elems} elements), "
+                f"{steps} optimizer steps, {spent:.2f} s of host time; C/OpenMP restatement of the "
+                f"reference math (RAF's TVM CPU path cannot be built here; LANS and Adam have no CPU path in RAF)")
+
+
+def cpu_baseline(wl, budget_s=10.0):
+    """Steps of the CPU arm until about `budget_s` seconds of CPU work have been spent."""
+    arm = CpuArm(wl)
+    arm.step()  # page in, warm the thread pool
+    spent, steps = 0.0, 0
+    while spent < budget_s and steps < 200:
+        spent += arm.step()
+        steps += 1
+    return {"value": arm.elems * steps / spent, "unit": "param-elements/s", "cores": arm.O.num_threads(),
+            "kind": "port", "sample": arm.describe(steps, spent)}
 
 
 def run_reference_arm(args, wl):
-    """--impl reference: the CPU restatement of the reference's path on all host threads."""
+    """--impl reference: the CPU restatement of the reference's path on all host threads.
+    A step is one optimizer step over a bounded prefix of the workload, sized from a probe so
+    that warm-up plus timed steps stay within a few minutes."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from raf_b200.zero import numel
 
     total = sum(numel(s) for s in wl["shapes"])
-    vals, samples = [], None
-    budget = max(2.0, min(20.0, 90.0 / max(1, args.steps + args.warmup)))
-    for i in range(args.warmup + args.steps):
-        r = cpu_baseline(wl, budget_s=budget)
-        samples = r
-        if i >= args.warmup:
-            vals.append(r["value"])
-    val = statistics.mean(vals)
+    probe = CpuArm(wl, max_elems=32 << 20)
+    probe.step()
+    rate = probe.elems / probe.step()  # elements/s on this box
+    nsteps = max(1, args.steps + args.warmup)
+    max_elems = int(min(total, max(8 << 20, rate * 120.0 / nsteps)))
+    arm = CpuArm(wl, max_elems=max_elems) if max_elems < total else CpuArm(wl)
+    for _ in range(args.warmup):
+        arm.step()
+    times = [arm.step() for _ in range(args.steps)]
+    spent = sum(times)
+    val = arm.elems * len(times) / spent
+    cpu = {"value": val, "unit": "param-elements/s", "cores": arm.O.num_threads(), "kind": "port",
+           "sample": arm.describe(len(times), spent)}
     line = {
         "impl": "reference", "metric": "ZeRO optimizer-step param-elements/s", "value": val,
         "unit": "param-elements/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * total / val, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": wl["label"], "note": "CPU host cores; ms_per_step extrapolated from the sample to the full parameter count"},
-        "cpu_baseline": {**samples, "value": val},
+        "cpu_baseline": cpu,
         "e2e": {"value": val, "unit": "param-elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -227,8 +255,8 @@ def run_reference_arm(args, wl):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="bert_lans")
     ap.add_argument("--e2e-steps", type=int, default=3)

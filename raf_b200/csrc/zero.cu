@@ -37,6 +37,7 @@ struct Bucket {
   void* lans_ws = nullptr;
   size_t lans_ws_bytes = 0;
   cudaEvent_t packed = nullptr, rs_done = nullptr, upd_done = nullptr, ag_done = nullptr;
+  cudaEvent_t h2d_done = nullptr, out_ready = nullptr;  // host-buffer form of the step
   // n > 1: rank-major flat buffers.  Slot r of a buffer holds, for every tensor of the
   // bucket in order, row block r of that tensor at element offset `off[j]` (each offset a
   // multiple of 8 elements, so every block starts 16-byte aligned in either dtype).
@@ -129,6 +130,11 @@ struct rafb200_zero_s {
   int n = 1, rank = 0;
   int g_dtype = 0, param_dtype = 0, optimizer = 0;
   std::vector<rafb200::Bucket> buckets;
+  // world of one, host-buffer form: one list per plan bucket so that the copy of bucket b+1
+  // from the host, the update of bucket b and the copy of bucket b-1 to the host overlap
+  std::vector<rafb200::Bucket> hbuckets;
+  cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
+  cudaEvent_t ev_d2h_done = nullptr;
   char* g_flat = nullptr;  // all buckets' gradient buffers, one allocation (n > 1)
   char* p_flat = nullptr;  // all buckets' parameter-copy buffers
   int sm_count = 148;
@@ -237,10 +243,11 @@ int rafb200_plan_totals(rafb200_plan_t plan, int64_t* elems, int64_t* padded_ele
 
 int rafb200_zero_destroy(rafb200_zero_t z) {
   if (!z) return RAFB200_OK;
-  for (auto& b : z->buckets) {
+  for (auto* set : {&z->buckets, &z->hbuckets})
+   for (auto& b : *set) {
     if (b.list) rafb200_tensor_list_destroy(b.list);
     if (b.lans_ws) cudaFree(b.lans_ws);
-    for (cudaEvent_t e : {b.packed, b.rs_done, b.upd_done, b.ag_done})
+    for (cudaEvent_t e : {b.packed, b.rs_done, b.upd_done, b.ag_done, b.h2d_done, b.out_ready})
       if (e) cudaEventDestroy(e);
     for (void* ptr : {(void*)b.dev_pack, (void*)b.dev_unpack, (void*)b.dev_pack_items,
                       (void*)b.dev_unpack_items})
@@ -253,6 +260,9 @@ int rafb200_zero_destroy(rafb200_zero_t z) {
   if (z->ev_gather) cudaEventDestroy(z->ev_gather);
   if (z->ev_start) cudaEventDestroy(z->ev_start);
   if (z->ev_done) cudaEventDestroy(z->ev_done);
+  if (z->ev_d2h_done) cudaEventDestroy(z->ev_d2h_done);
+  if (z->h2d_stream) cudaStreamDestroy(z->h2d_stream);
+  if (z->d2h_stream) cudaStreamDestroy(z->d2h_stream);
   delete z;
   return RAFB200_OK;
 }
@@ -289,28 +299,42 @@ int rafb200_zero_create(rafb200_plan_t plan, rafb200_comm_t comm, int g_dtype, i
     const int nb = (z->n == 1) ? (k > 0 ? 1 : 0) : plan->nbuckets;
     z->buckets.resize(nb);
     for (int i = 0; i < k; ++i) z->buckets[z->n == 1 ? 0 : plan->bucket_of[i]].tensors.push_back(i);
+    if (z->n == 1 && plan->nbuckets > 1) {
+      z->hbuckets.resize(plan->nbuckets);
+      for (int i = 0; i < k; ++i) z->hbuckets[plan->bucket_of[i]].tensors.push_back(i);
+    }
     int64_t flat_elems = 0;
-    for (auto& b : z->buckets) {
-      std::vector<int64_t> numel;
-      for (int i : b.tensors) {
-        numel.push_back(plan->shard_elems[i]);
-        b.off.push_back(b.slot_elems);
-        b.slot_elems += (plan->shard_elems[i] + 7) & ~(int64_t)7;
-      }
-      flat_elems += b.slot_elems * z->n;
-      rc = rafb200_tensor_list_create((int)numel.size(), numel.data(), g_dtype, param_dtype, &b.list);
-      if (rc != RAFB200_OK) break;
-      if (optimizer == RAFB200_OPT_LANS) {
-        b.lans_ws_bytes = rafb200_lans_workspace_bytes(b.list);
-        if (cudaMalloc(&b.lans_ws, b.lans_ws_bytes) != cudaSuccess) {
-          rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: cannot allocate LANS workspace");
-          break;
+    for (auto* set : {&z->buckets, &z->hbuckets}) {
+      for (auto& b : *set) {
+        std::vector<int64_t> numel;
+        for (int i : b.tensors) {
+          numel.push_back(plan->shard_elems[i]);
+          b.off.push_back(b.slot_elems);
+          b.slot_elems += (plan->shard_elems[i] + 7) & ~(int64_t)7;
         }
+        if (set == &z->buckets) flat_elems += b.slot_elems * z->n;
+        rc = rafb200_tensor_list_create((int)numel.size(), numel.data(), g_dtype, param_dtype, &b.list);
+        if (rc != RAFB200_OK) break;
+        if (optimizer == RAFB200_OPT_LANS) {
+          b.lans_ws_bytes = rafb200_lans_workspace_bytes(b.list);
+          if (cudaMalloc(&b.lans_ws, b.lans_ws_bytes) != cudaSuccess) {
+            rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: cannot allocate LANS workspace");
+            break;
+          }
+        }
+        for (cudaEvent_t* e : {&b.packed, &b.rs_done, &b.upd_done, &b.ag_done, &b.h2d_done, &b.out_ready})
+          if (cudaEventCreateWithFlags(e, cudaEventDisableTiming) != cudaSuccess)
+            rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: cannot create events");
+        if (rc != RAFB200_OK) break;
       }
-      for (cudaEvent_t* e : {&b.packed, &b.rs_done, &b.upd_done, &b.ag_done})
-        if (cudaEventCreateWithFlags(e, cudaEventDisableTiming) != cudaSuccess)
-          rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: cannot create events");
       if (rc != RAFB200_OK) break;
+    }
+    if (rc != RAFB200_OK) break;
+    if (cudaStreamCreateWithFlags(&z->h2d_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&z->d2h_stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&z->ev_d2h_done, cudaEventDisableTiming) != cudaSuccess) {
+      rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: cannot create copy streams");
+      break;
     }
     if (rc != RAFB200_OK) break;
     if (cudaEventCreateWithFlags(&z->ev_start, cudaEventDisableTiming) != cudaSuccess ||
@@ -369,7 +393,9 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
   z->collectives_per_step = 0;
   // Tables that a kernel of an earlier step may still be reading are replaced below.
   RAFB200_CUDA(cudaDeviceSynchronize());
-  for (auto& b : z->buckets) {
+  for (auto* set : {&z->buckets, &z->hbuckets})
+   for (auto& b : *set) {
+    const bool counted = (set == &z->buckets);
     const size_t nt = b.tensors.size();
     std::vector<const void*> lg(nt);
     std::vector<float*> lp(nt), lm(nt), lv(nt);
@@ -406,7 +432,7 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
     int rc = rafb200_tensor_list_bind(b.list, lg.data(), lp.data(), lm.data(), v ? lv.data() : nullptr,
                                       lo.data(), nullptr);
     if (rc != RAFB200_OK) return rc;
-    if (rafb200_tensor_list_total_elems(b.list) > 0) z->kernels_per_step += 1;
+    if (counted && rafb200_tensor_list_total_elems(b.list) > 0) z->kernels_per_step += 1;
     if (z->n > 1) {
       const std::vector<Item> pi = seg_items(pack), ui = seg_items(unpack);
       b.n_pack_items = (uint32_t)pi.size();
@@ -525,8 +551,11 @@ static int run_update(rafb200_zero_s* z, Bucket& b, const rafb200_hyper* h, int 
   }
 }
 
-int rafb200_zero_step(rafb200_zero_t z, const rafb200_hyper* h, int step, void* compute_stream,
-                      void* comm_stream) {
+// One step.  grads_host / params_host are NULL for the device-buffer form; otherwise the
+// gradients of bucket b arrive on the copy-in stream while earlier buckets are in flight and
+// its parameters leave on the copy-out stream as soon as they are complete.
+static int step_impl(rafb200_zero_t z, const rafb200_hyper* h, int step, void* compute_stream,
+                     void* comm_stream, const void* const* grads_host, void* const* params_host) {
   RAFB200_REQUIRE(z && h, "rafb200_zero_step: NULL argument");
   RAFB200_REQUIRE(z->bound, "rafb200_zero_step: bind buffers first");
   RAFB200_REQUIRE(h->optimizer == z->optimizer, "rafb200_zero_step: optimizer differs from the one created");
@@ -535,18 +564,52 @@ int rafb200_zero_step(rafb200_zero_t z, const rafb200_hyper* h, int step, void* 
   // A mean over ranks is a sum on the wire and a 1/n folded into the update's
   // gradient scale (the `divide` of partition_gradient.cc:274-279, fused).
   const float gscale = h->grad_scale * ((h->average && z->n > 1) ? 1.0f / (float)z->n : 1.0f);
-  const int nb = (int)z->buckets.size();
+  const int gs = dtype_size(z->g_dtype), ps = dtype_size(z->param_dtype);
+  const bool host = grads_host != nullptr;
+  std::vector<Bucket>& bl = (z->n == 1 && host && !z->hbuckets.empty()) ? z->hbuckets : z->buckets;
+  const int nb = (int)bl.size();
+  if (host) {
+    // Every copy from the host is queued up front, bucket by bucket, behind whatever the
+    // compute stream still does with the gradient buffers.
+    RAFB200_CUDA(cudaEventRecord(z->ev_start, cs));
+    RAFB200_CUDA(cudaStreamWaitEvent(z->h2d_stream, z->ev_start, 0));
+    RAFB200_CUDA(cudaStreamWaitEvent(z->d2h_stream, z->ev_start, 0));
+    for (auto& b : bl) {
+      for (int i : b.tensors)
+        if (z->plan.numel[i])
+          RAFB200_CUDA(cudaMemcpyAsync(z->grads[i], grads_host[i], (size_t)z->plan.numel[i] * gs,
+                                       cudaMemcpyHostToDevice, z->h2d_stream));
+      RAFB200_CUDA(cudaEventRecord(b.h2d_done, z->h2d_stream));
+    }
+  }
+  auto copy_out = [&](Bucket& b) -> int {  // after the last kernel of bucket b on the compute stream
+    if (!host) return RAFB200_OK;
+    RAFB200_CUDA(cudaEventRecord(b.out_ready, cs));
+    RAFB200_CUDA(cudaStreamWaitEvent(z->d2h_stream, b.out_ready, 0));
+    for (int i : b.tensors)
+      if (z->plan.numel[i])
+        RAFB200_CUDA(cudaMemcpyAsync(params_host[i], z->params[i], (size_t)z->plan.numel[i] * ps,
+                                     cudaMemcpyDeviceToHost, z->d2h_stream));
+    return RAFB200_OK;
+  };
+  auto finish = [&]() -> int {  // the compute stream ends the step for the caller
+    if (!host) return RAFB200_OK;
+    RAFB200_CUDA(cudaEventRecord(z->ev_d2h_done, z->d2h_stream));
+    RAFB200_CUDA(cudaStreamWaitEvent(cs, z->ev_d2h_done, 0));
+    return RAFB200_OK;
+  };
   if (z->n == 1) {
-    for (auto& b : z->buckets) {
+    for (auto& b : bl) {
+      if (host) RAFB200_CUDA(cudaStreamWaitEvent(cs, b.h2d_done, 0));
       int rc = run_update(z, b, h, step, gscale, cs);
       if (rc != RAFB200_OK) return rc;
+      if ((rc = copy_out(b)) != RAFB200_OK) return rc;
     }
-    return RAFB200_OK;
+    return finish();
   }
-  const int gs = dtype_size(z->g_dtype), ps = dtype_size(z->param_dtype);
   // The communication stream must not run ahead of work already queued on the compute
   // stream that still uses the flat buffers (the previous step's unpack).
-  RAFB200_CUDA(cudaEventRecord(z->ev_start, cs));
+  if (!host) RAFB200_CUDA(cudaEventRecord(z->ev_start, cs));
   RAFB200_CUDA(cudaStreamWaitEvent(ms, z->ev_start, 0));
   if (z->symmetric) RAFB200_CUDA(cudaStreamWaitEvent(z->gather_stream, z->ev_start, 0));
   // Software pipeline over buckets; stage s of bucket b is issued in iteration b + s:
@@ -557,6 +620,7 @@ int rafb200_zero_step(rafb200_zero_t z, const rafb200_hyper* h, int step, void* 
     if (it < nb) {
       Bucket& b = z->buckets[it];
       int rc = RAFB200_OK;
+      if (host) RAFB200_CUDA(cudaStreamWaitEvent(cs, b.h2d_done, 0));
       if (z->stage_mask & 1)
         rc = launch_seg_copy(b.dev_pack, b.dev_pack_items, b.n_pack_items, gs, z->sm_count, cs);
       if (rc != RAFB200_OK) return rc;
@@ -607,9 +671,15 @@ int rafb200_zero_step(rafb200_zero_t z, const rafb200_hyper* h, int step, void* 
       if (z->stage_mask & 16)
         rc = launch_seg_copy(b.dev_unpack, b.dev_unpack_items, b.n_unpack_items, ps, z->sm_count, cs);
       if (rc != RAFB200_OK) return rc;
+      if ((rc = copy_out(b)) != RAFB200_OK) return rc;
     }
   }
-  return RAFB200_OK;
+  return finish();
+}
+
+int rafb200_zero_step(rafb200_zero_t z, const rafb200_hyper* h, int step, void* compute_stream,
+                      void* comm_stream) {
+  return step_impl(z, h, step, compute_stream, comm_stream, nullptr, nullptr);
 }
 
 int rafb200_zero_step_host(rafb200_zero_t z, const rafb200_hyper* h, int step,
@@ -617,19 +687,7 @@ int rafb200_zero_step_host(rafb200_zero_t z, const rafb200_hyper* h, int step,
                            void* compute_stream, void* comm_stream) {
   RAFB200_REQUIRE(z && h && grads_host && params_host, "rafb200_zero_step_host: NULL argument");
   RAFB200_REQUIRE(z->bound, "rafb200_zero_step_host: bind device buffers first");
-  cudaStream_t cs = static_cast<cudaStream_t>(compute_stream);
-  const int gs = dtype_size(z->g_dtype), ps = dtype_size(z->param_dtype);
-  for (int i = 0; i < z->plan.k; ++i)
-    if (z->plan.numel[i])
-      RAFB200_CUDA(cudaMemcpyAsync(z->grads[i], grads_host[i], (size_t)z->plan.numel[i] * gs,
-                                   cudaMemcpyHostToDevice, cs));
-  int rc = rafb200_zero_step(z, h, step, compute_stream, comm_stream);
-  if (rc != RAFB200_OK) return rc;
-  for (int i = 0; i < z->plan.k; ++i)
-    if (z->plan.numel[i])
-      RAFB200_CUDA(cudaMemcpyAsync(params_host[i], z->params[i], (size_t)z->plan.numel[i] * ps,
-                                   cudaMemcpyDeviceToHost, cs));
-  return RAFB200_OK;
+  return step_impl(z, h, step, compute_stream, comm_stream, grads_host, params_host);
 }
 
 }  // extern "C"
