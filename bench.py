@@ -270,9 +270,9 @@ def main():
     ap.add_argument("--shard-of", type=int, default=0,
                     help="N = 1 only: run on the shard list that rank 0 of an N-way partition owns "
                          "(a small case of the same kernel, e.g. for profiler captures)")
-    ap.add_argument("--collectives", default="multimem", choices=["multimem", "peer", "nccl"],
+    ap.add_argument("--collectives", default="auto", choices=["auto", "multimem", "peer", "nccl"],
                     help="N > 1: own kernels over symmetric memory (NVSwitch multicast / peer "
-                         "pointers) or NCCL")
+                         "pointers) or NCCL; auto = NCCL at N = 2, multicast from N = 4 (measured best)")
     ap.add_argument("--comm-blocks", type=int, default=0, help="thread blocks per collective kernel")
     ap.add_argument("--stages", action="store_true",
                     help="N > 1: also time each stage of the step alone (pack, reduce-scatter, ...)")
@@ -341,15 +341,24 @@ def main():
     # Gradient sets: the step leaves the caller's gradients untouched (they are packed into
     # the bucket buffers first), so a set can be reused; two sets alternate.
     nsets = 1 if world == 1 else 2
+    if args.collectives == "auto":
+        args.collectives = "nccl" if world <= 2 else "multimem"
+    if world > 1 and not args.update_blocks and wl["optimizer"] == "lans":
+        # leave 16 SMs' worth of block slots to the collective kernels running beside the update
+        args.update_blocks = 2 * (torch.cuda.get_device_properties(dev).multi_processor_count - 16)
     collectives_used = args.collectives if world > 1 else "none"
     gsets = [[randn(numel(s), 1e-3 * wl["loss_scale"], gdt) for s in shapes] for _ in range(nsets)]
     zs = []
     for gs in gsets:
         z = ZeroStep(plan, comm, gdt, pdt, wl["optimizer"])
         if world > 1 and args.collectives != "nccl":
-            z.attach_symmetric(comm_blocks=args.comm_blocks, multicast=(args.collectives == "multimem"))
-            if args.collectives == "multimem" and not z.multicast:
-                collectives_used = "peer (no multicast address available)"
+            try:
+                z.attach_symmetric(comm_blocks=args.comm_blocks, multicast=(args.collectives == "multimem"))
+                if args.collectives == "multimem" and not z.multicast:
+                    collectives_used = "peer (no multicast address available)"
+            except Exception as exc:  # symmetric memory is plumbing: without it NCCL still works
+                collectives_used = f"nccl (symmetric memory unavailable: {type(exc).__name__})"
+                args.collectives = "nccl"
         z.bind(gs, params, p, m, v if wl["optimizer"] != "sgd" else None)
         if args.update_blocks:
             z.set_update_blocks(args.update_blocks)
