@@ -40,8 +40,8 @@ NVLINK_MEASURED_GBS = 770.0  # peer copy, per direction per GPU, measured on thi
 # DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (workload, n_gpus, shard_of) -> bytes
 MEASURED_TRAFFIC = {
-    ("bert_lans", 1, 1): 14312909824,   # profiles/lans_kernel_bert_large_n1.md
-    ("bert_lans", 1, 8): 1689914872,    # profiles/lans_kernel_bert_large_shard8_full.md
+    ("bert_lans", 1, 1): 14644926464,   # profiles/lans_kernel_bert_large_n1.md
+    ("bert_lans", 1, 8): 1705129480,    # profiles/lans_kernel_bert_large_shard8_full.md
     ("rn50_sgd", 1, 1): 556562432,      # profiles/update_list_kernel_sgd_rn50.md
     ("gpt2_adam", 1, 8): 1184124416,    # profiles/update_list_kernel_adam_gpt2_shard8.md
 }
@@ -262,8 +262,6 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--window-elems", type=int, default=None)
-    ap.add_argument("--slack-items", type=int, default=None)
     ap.add_argument("--update-blocks", type=int, default=0)
     ap.add_argument("--bucket-elems", type=int, default=None,
                     help="bucket size in elements (default: the workload's)")

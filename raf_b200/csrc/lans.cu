@@ -836,12 +836,8 @@ std::vector<Item> build_lans_schedule(const std::vector<uint32_t>& nchunks, bool
   skip_empty(B);
   skip_empty(Cc);
   std::vector<int64_t> done_a(k, -1), done_b(k, -1);
-  // Phase B walks a tensor front to back, phases A and C back to front: the chunks a
-  // pass touches first are the ones the previous pass over the same tensor touched
-  // last, i.e. the ones most likely to still be in L2 when the tensor is larger than
-  // what L2 holds.
   auto emit = [&](Cursor& cur, int phase, std::vector<int64_t>* done) {
-    const uint32_t chunk = (phase == kPhaseB) ? cur.c : nchunks[cur.t] - 1u - cur.c;
+    const uint32_t chunk = cur.c;
     out.push_back(Item{((uint32_t)phase << kPhaseShift) | (uint32_t)cur.t, chunk});
     cur.emitted++;
     if (++cur.c == nchunks[cur.t]) {
@@ -852,22 +848,42 @@ std::vector<Item> build_lans_schedule(const std::vector<uint32_t>& nchunks, bool
     }
   };
   if (!with_a) A.t = k;
+  // Round-robin: in every round each phase that may run emits one item.  The three passes
+  // then advance at the same rate, reads and writes reach DRAM in a steady 2:1 mix, and a
+  // block that holds an item whose norm is not final yet is one of few, not one of all:
+  // measured 2.21 ms against 2.45 ms for "phase C first, in bursts" on the 335 M-element list.
+  // Phase C trails phase B by the largest tensor seen so far, so on lists with tensors
+  // beyond a few MB its reads come from DRAM, not from L2; schedules that kept it closer
+  // (bursts, 2:1 to 8:1 catch-up) re-read less but stalled more and measured slower.
   while (Cc.t < k) {
-    const int64_t n = (int64_t)out.size();
-    const bool a_ready = with_a && A.t < k;
-    const bool b_ready = B.t < k && (!with_a || A.t > B.t);
-    const bool c_ready = B.t > Cc.t;
-    const bool b_slack_ok = b_ready && (B.c > 0 || !with_a || n - done_a[B.t] >= slack);
-    const bool c_slack_ok = c_ready && (Cc.c > 0 || n - done_b[Cc.t] >= slack);
-    const bool b_window_ok = (int64_t)(B.emitted - Cc.emitted) < window_chunks;
-    const bool a_window_ok = (int64_t)(A.emitted - B.emitted) < window_chunks;
-    if (c_slack_ok) emit(Cc, kPhaseC, nullptr);
-    else if (b_slack_ok && b_window_ok) emit(B, kPhaseB, &done_b);
-    else if (a_ready && a_window_ok) emit(A, kPhaseA, &done_a);
-    else if (b_slack_ok) emit(B, kPhaseB, &done_b);
-    else if (a_ready) emit(A, kPhaseA, &done_a);
-    else if (b_ready) emit(B, kPhaseB, &done_b);
-    else emit(Cc, kPhaseC, nullptr);  // c_ready must hold here
+    bool progressed = false;
+    {
+      const int64_t n = (int64_t)out.size();
+      const bool c_ready = Cc.t < k && B.t > Cc.t;
+      if (c_ready && (Cc.c > 0 || n - done_b[Cc.t] >= slack)) {
+        emit(Cc, kPhaseC, nullptr);
+        progressed = true;
+      }
+    }
+    {
+      const int64_t n = (int64_t)out.size();
+      const bool b_ready = B.t < k && (!with_a || A.t > B.t);
+      if (b_ready && (B.c > 0 || !with_a || n - done_a[B.t] >= slack) &&
+          (int64_t)(B.emitted - Cc.emitted) < window_chunks) {
+        emit(B, kPhaseB, &done_b);
+        progressed = true;
+      }
+    }
+    if (with_a && A.t < k && (int64_t)(A.emitted - B.emitted) < window_chunks + 2048) {
+      emit(A, kPhaseA, &done_a);
+      progressed = true;
+    }
+    if (!progressed) {  // slack or window not met anywhere: advance what the dependencies allow
+      const bool b_ready = B.t < k && (!with_a || A.t > B.t);
+      if (with_a && A.t < k) emit(A, kPhaseA, &done_a);
+      else if (b_ready) emit(B, kPhaseB, &done_b);
+      else emit(Cc, kPhaseC, nullptr);
+    }
   }
   return out;
 }

@@ -1,4 +1,5 @@
 // Tensor-list objects, error reporting and library identity.
+#include <cstdlib>
 #include <cstring>
 
 #include "common.h"
@@ -111,11 +112,11 @@ int rafb200_tensor_list_create(int k, const int64_t* numel, int g_dtype, int out
     rc = upload_items(items, &l->dev_items, &l->n_items);
     if (rc != RAFB200_OK) break;
     // Defaults.  A block holds up to four tickets and two blocks run per SM, so about
-    // eight items per SM are in flight; four times that many items are placed between
-    // the last item of a phase of a tensor and the first item that depends on it
-    // (measured best on B200 for both 335 M-element and 42 M-element lists).  The B
-    // pass may lead the C pass by 32 Mi elements where the order leaves a choice.
-    l->slack_items = 32 * l->sm_count;
+    // eight items per SM are in flight; that many items are placed between the last item
+    // of a phase of a tensor and the first item that depends on it.  With the round-robin
+    // order of the three passes the step time is flat in this value (0 to 32 per SM
+    // measured within 1 %).  The B pass may lead the C pass by 32 Mi elements at most.
+    l->slack_items = 8 * l->sm_count;
     l->window_elems = 32ll << 20;
     rc = rebuild_lans_schedule(l);
   } while (false);

@@ -90,7 +90,7 @@ class TensorList:
             window_elems = 32 << 20
         if slack_items is None:
             props = torch.cuda.get_device_properties(torch.cuda.current_device())
-            slack_items = 32 * props.multi_processor_count
+            slack_items = 8 * props.multi_processor_count
         check(lib.rafb200_tensor_list_tune(self.handle, int(window_elems), int(slack_items),
                                            int(max_blocks)))
 
