@@ -854,7 +854,9 @@ std::vector<Item> build_lans_schedule(const std::vector<uint32_t>& nchunks, bool
   // measured 2.21 ms against 2.45 ms for "phase C first, in bursts" on the 335 M-element list.
   // Phase C trails phase B by the largest tensor seen so far, so on lists with tensors
   // beyond a few MB its reads come from DRAM, not from L2; schedules that kept it closer
-  // (bursts, 2:1 to 8:1 catch-up) re-read less but stalled more and measured slower.
+  // (bursts, 2:1 to 8:1 catch-up) re-read less but stalled more and measured slower, and
+  // visiting the tensors smallest first cut the DRAM reads by 12 % but left the huge ones
+  // as an unoverlapped tail (2.33 ms).
   while (Cc.t < k) {
     bool progressed = false;
     {
