@@ -270,8 +270,11 @@ def main():
                          "(a small case of the same kernel, e.g. for profiler captures)")
     ap.add_argument("--collectives", default="auto", choices=["auto", "multimem", "peer", "nccl"],
                     help="N > 1: own kernels over symmetric memory (NVSwitch multicast / peer "
-                         "pointers) or NCCL; auto = NCCL at N = 2, multicast from N = 4 (measured best)")
+                         "pointers) or NCCL; auto = multicast, NCCL if symmetric memory cannot be set up")
     ap.add_argument("--comm-blocks", type=int, default=0, help="thread blocks per collective kernel")
+    ap.add_argument("--no-views", action="store_true",
+                    help="symmetric modes: keep gradients and parameters in separate tensors "
+                         "(pack / unpack copies) instead of inside the symmetric buffer")
     ap.add_argument("--stages", action="store_true",
                     help="N > 1: also time each stage of the step alone (pack, reduce-scatter, ...)")
     ap.add_argument("--existing-kernel", action="store_true",
@@ -340,11 +343,12 @@ def main():
     # the bucket buffers first), so a set can be reused; two sets alternate.
     nsets = 1 if world == 1 else 2
     if args.collectives == "auto":
-        args.collectives = "nccl" if world <= 2 else "multimem"
+        args.collectives = "multimem"
     if world > 1 and not args.update_blocks and wl["optimizer"] == "lans":
         # leave 16 SMs' worth of block slots to the collective kernels running beside the update
         args.update_blocks = 2 * (torch.cuda.get_device_properties(dev).multi_processor_count - 16)
     collectives_used = args.collectives if world > 1 else "none"
+    views_used = 0
     gsets = [[randn(numel(s), 1e-3 * wl["loss_scale"], gdt) for s in shapes] for _ in range(nsets)]
     zs = []
     for gs in gsets:
@@ -357,7 +361,18 @@ def main():
             except Exception as exc:  # symmetric memory is plumbing: without it NCCL still works
                 collectives_used = f"nccl (symmetric memory unavailable: {type(exc).__name__})"
                 args.collectives = "nccl"
-        z.bind(gs, params, p, m, v if wl["optimizer"] != "sgd" else None)
+        zg, zp = gs, params
+        if world > 1 and args.collectives != "nccl" and not args.no_views:
+            # gradients and model parameters live inside the symmetric buffer where their
+            # shard size allows (all tensors of the benchmark shapes): no pack / unpack
+            gv, pv = z.arena_views()
+            zg = [x.reshape(-1) if x is not None else own for x, own in zip(gv, gs)]
+            zp = [x.reshape(-1) if x is not None else own for x, own in zip(pv, params)]
+            for dst, src in zip(zg, gs):
+                if dst is not src:
+                    dst.copy_(src)
+            views_used = sum(x is not None for x in gv)
+        z.bind(zg, zp, p, m, v if wl["optimizer"] != "sgd" else None)
         if args.update_blocks:
             z.set_update_blocks(args.update_blocks)
         zs.append(z)
@@ -514,6 +529,7 @@ def main():
                        "elements": total, "shard_elements_per_rank": shard_elems,
                        "bucket_elems": wl["bucket_elems"], "buckets": plan.num_buckets if world > 1 else 1,
                        "gradient_sets": nsets, "collectives": collectives_used,
+                       "tensors_inside_symmetric_buffer": views_used,
                        "l2": f"inputs larger than L2 ({wl['bytes_per_elem'] * shard_elems >> 20} MiB touched per step per rank)"},
             "roofline": roofline,
             "step_roofline": {"bound_ms": bound_ms, "frac": bound_ms / ms_step,

@@ -411,7 +411,8 @@ RAFB200_API int rafb200_zero_step(rafb200_zero_t zero, const rafb200_hyper* hype
  * same kernels read / write the peers one by one.  Ranks meet at two flag
  * barriers per bucket whose waits are bounded (10 s); rafb200_zero_status
  * synchronises the device and returns RAFB200_DEVICE_WAIT_EXPIRED if one ran
- * out.  comm_blocks = thread blocks per collective kernel (0 = default 128).
+ * out.  comm_blocks = thread blocks per collective kernel (0 = default: 128 with a
+ * multicast address, two per SM without).
  * How the memory is obtained is the caller's business (cuMemCreate +
  * cuMulticastBindMem, or torch.distributed._symmetric_memory as the Python
  * layer of this package does).  Call between rafb200_zero_create and
@@ -422,12 +423,26 @@ RAFB200_API int rafb200_zero_flat_bytes(rafb200_zero_t zero, size_t* g_bytes, si
 RAFB200_API int rafb200_zero_attach_symmetric(rafb200_zero_t zero, void* const* g_peer, void* g_mc,
                                               void* const* p_peer, void* p_mc,
                                               void* const* signal_peer, int comm_blocks);
+/* Symmetric mode lays each flat buffer out tensor by tensor: tensor i owns n
+ * row blocks of align8(shard_elems[i]) elements, starting elem_offset[i]
+ * elements into the buffer (the same offset in the gradient and in the
+ * parameter buffer).  Where natural[i] is 1 (shard size a multiple of 8
+ * elements) that region IS the zero-padded tensor in its ordinary row-major
+ * layout, so the caller may keep its gradient and / or model parameter there:
+ * rafb200_zero_bind recognises grads[i] == g_peer[rank] + elem_offset[i] *
+ * sizeof(g dtype) (params[i] likewise) and then skips the pack (unpack) copy of
+ * that tensor - gradients are reduced from where backward wrote them and the
+ * gathered parameters land where the model reads them.  The gradients are not
+ * modified (sums go to a shard-sized buffer of the step object). */
+RAFB200_API int rafb200_zero_arena_offsets(rafb200_zero_t zero, int64_t* elem_offset, int* natural);
 RAFB200_API int rafb200_zero_status(rafb200_zero_t zero);
 /* Measurement aid: issue only the selected stages of a multi-rank step
  * (bit 0 pack, 1 reduce-scatter, 2 update, 3 all-gather, 4 unpack; default 31).
  * With a stage missing the results are meaningless; every rank must use the
  * same mask.  bench.py uses it to time the stages separately. */
 RAFB200_API int rafb200_zero_set_stage_mask(rafb200_zero_t zero, int mask);
+/* Per step: kernels of this library (update, pack, unpack and, in symmetric mode,
+ * the collective and barrier kernels) and NCCL calls (0 in symmetric mode). */
 RAFB200_API int rafb200_zero_launch_counts(rafb200_zero_t zero, int* kernels, int* collectives);
 /* Cap on the persistent update grids while collectives are in flight (0 = no cap). */
 RAFB200_API int rafb200_zero_set_update_blocks(rafb200_zero_t zero, int max_blocks);

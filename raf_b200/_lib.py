@@ -88,6 +88,7 @@ SIGNATURES = {
     "rafb200_zero_step": (_i, [_vp, _P(Hyper), _i, _vp, _vp]),
     "rafb200_zero_flat_bytes": (_i, [_vp, _P(_sz), _P(_sz), _P(_sz)]),
     "rafb200_zero_attach_symmetric": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i]),
+    "rafb200_zero_arena_offsets": (_i, [_vp, _vp, _vp]),
     "rafb200_zero_status": (_i, [_vp]),
     "rafb200_zero_set_stage_mask": (_i, [_vp, _i]),
     "rafb200_zero_launch_counts": (_i, [_vp, _P(_i), _P(_i)]),

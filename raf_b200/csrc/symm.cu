@@ -126,67 +126,77 @@ __device__ __forceinline__ uint4 round_once(const float (&acc)[8]) {
 
 constexpr int kSymmThreads = 256;
 constexpr int kSymmUnroll = 8;  // 16-byte accesses in flight per thread
+static_assert(kSymmThreads * kSymmUnroll * 16 == kSymmChunkBytes, "one work item = one pass of a block");
 
-// dst (local, this rank's slot) = sum over ranks of the slot at byte offset `off`.
+// A work item = one 32 KB chunk of one segment; a segment = this rank's row block of one
+// tensor, `off` bytes into the (symmetric) buffer, a multiple of 16 bytes long.
+// Reduce-scatter: out[dst_off..] = sum over ranks of buffer[off..].
 template <int DT, bool MC>
 __global__ void __launch_bounds__(kSymmThreads)
-    symm_reduce_scatter_kernel(SymmPeers peers, const char* mc, size_t off, char* dst, int64_t nvec,
-                               int world) {
-  const int64_t stride = (int64_t)gridDim.x * kSymmThreads;
-  for (int64_t i0 = (int64_t)blockIdx.x * kSymmThreads + threadIdx.x; i0 < nvec; i0 += stride * kSymmUnroll) {
+    symm_reduce_scatter_kernel(SymmPeers peers, const char* mc, char* local, const SymmSeg* __restrict__ segs,
+                               const Item* __restrict__ items, uint32_t nitems, int world) {
+  for (uint32_t it = blockIdx.x; it < nitems; it += gridDim.x) {
+    const Item item = items[it];
+    const SymmSeg sg = segs[item.tensor_phase];
+    const size_t base = sg.off + (size_t)item.chunk * kSymmChunkBytes;
+    const size_t dst = sg.dst_off + (size_t)item.chunk * kSymmChunkBytes;
+    int64_t left = sg.bytes - (int64_t)item.chunk * kSymmChunkBytes;
+    const int nvec = (int)((left > kSymmChunkBytes ? kSymmChunkBytes : left) >> 4);
     uint4 out[kSymmUnroll];
 #pragma unroll
     for (int u = 0; u < kSymmUnroll; ++u) {
-      const int64_t i = i0 + u * stride;
+      const int i = threadIdx.x + u * kSymmThreads;
       if (i >= nvec) continue;
       if (MC) {
-        out[u] = mc_ld_reduce<DT>(mc + off + (size_t)i * 16);
+        out[u] = mc_ld_reduce<DT>(mc + base + (size_t)i * 16);
       } else {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (int q = 0; q < world; ++q)  // fixed order: the same bits on every run
-          accumulate<DT>(acc, peer_ld(static_cast<const char*>(peers.ptr[q]) + off + (size_t)i * 16));
+          accumulate<DT>(acc, peer_ld(static_cast<const char*>(peers.ptr[q]) + base + (size_t)i * 16));
         out[u] = round_once<DT>(acc);
       }
     }
 #pragma unroll
     for (int u = 0; u < kSymmUnroll; ++u) {
-      const int64_t i = i0 + u * stride;
-      if (i < nvec) *reinterpret_cast<uint4*>(dst + (size_t)i * 16) = out[u];
+      const int i = threadIdx.x + u * kSymmThreads;
+      if (i < nvec) *reinterpret_cast<uint4*>(local + dst + (size_t)i * 16) = out[u];
     }
   }
 }
 
-// Every rank's copy of the slot at byte offset `off` = src (local).
+// All-gather: buffer[off..] on every rank = local[off..].
 template <bool MC>
 __global__ void __launch_bounds__(kSymmThreads)
-    symm_allgather_kernel(SymmPeers peers, char* mc, size_t off, const char* src, int64_t nvec, int world,
-                          int rank) {
-  const int64_t stride = (int64_t)gridDim.x * kSymmThreads;
-  for (int64_t i0 = (int64_t)blockIdx.x * kSymmThreads + threadIdx.x; i0 < nvec; i0 += stride * kSymmUnroll) {
+    symm_allgather_kernel(SymmPeers peers, char* mc, const char* local, const SymmSeg* __restrict__ segs,
+                          const Item* __restrict__ items, uint32_t nitems, int world, int rank) {
+  for (uint32_t it = blockIdx.x; it < nitems; it += gridDim.x) {
+    const Item item = items[it];
+    const SymmSeg sg = segs[item.tensor_phase];
+    const size_t base = sg.off + (size_t)item.chunk * kSymmChunkBytes;
+    int64_t left = sg.bytes - (int64_t)item.chunk * kSymmChunkBytes;
+    const int nvec = (int)((left > kSymmChunkBytes ? kSymmChunkBytes : left) >> 4);
     uint4 v[kSymmUnroll];
 #pragma unroll
     for (int u = 0; u < kSymmUnroll; ++u) {
-      const int64_t i = i0 + u * stride;
-      if (i < nvec) v[u] = *reinterpret_cast<const uint4*>(src + (size_t)i * 16);
+      const int i = threadIdx.x + u * kSymmThreads;
+      if (i < nvec) v[u] = *reinterpret_cast<const uint4*>(local + base + (size_t)i * 16);
     }
 #pragma unroll
     for (int u = 0; u < kSymmUnroll; ++u) {
-      const int64_t i = i0 + u * stride;
+      const int i = threadIdx.x + u * kSymmThreads;
       if (i >= nvec) continue;
       if (MC) {
-        mc_st(mc + off + (size_t)i * 16, v[u]);
+        mc_st(mc + base + (size_t)i * 16, v[u]);
       } else {
         for (int q = 0; q < world; ++q)
-          if (q != rank)
-            *reinterpret_cast<uint4*>(static_cast<char*>(peers.ptr[q]) + off + (size_t)i * 16) = v[u];
+          if (q != rank) *reinterpret_cast<uint4*>(static_cast<char*>(peers.ptr[q]) + base + (size_t)i * 16) = v[u];
       }
     }
   }
 }
 
-static unsigned symm_grid(int64_t nvec, int blocks) {
-  int64_t g = (nvec + (int64_t)kSymmThreads * kSymmUnroll - 1) / ((int64_t)kSymmThreads * kSymmUnroll);
-  if (g > blocks) g = blocks;
+static unsigned symm_grid(uint32_t nitems, int blocks) {
+  int64_t g = nitems < (uint32_t)blocks ? nitems : blocks;
   return (unsigned)(g < 1 ? 1 : g);
 }
 
@@ -198,41 +208,39 @@ int symm_barrier(const SymmPeers& sig, int world, int rank, int lane, uint32_t e
 }
 
 template <int DT>
-static int launch_rs(const SymmPeers& peers, const void* mc, size_t off, void* dst, int64_t nvec, int world,
-                     int blocks, cudaStream_t s) {
-  const unsigned g = symm_grid(nvec, blocks);
+static int launch_rs(const SymmPeers& peers, const void* mc, void* local, const SymmSeg* segs, const Item* items,
+                     uint32_t nitems, int world, int blocks, cudaStream_t s) {
+  const unsigned g = symm_grid(nitems, blocks);
   if (mc)
-    symm_reduce_scatter_kernel<DT, true><<<g, kSymmThreads, 0, s>>>(peers, static_cast<const char*>(mc), off,
-                                                                    static_cast<char*>(dst), nvec, world);
+    symm_reduce_scatter_kernel<DT, true><<<g, kSymmThreads, 0, s>>>(peers, static_cast<const char*>(mc),
+                                                                    static_cast<char*>(local), segs, items, nitems, world);
   else
-    symm_reduce_scatter_kernel<DT, false><<<g, kSymmThreads, 0, s>>>(peers, nullptr, off,
-                                                                     static_cast<char*>(dst), nvec, world);
+    symm_reduce_scatter_kernel<DT, false><<<g, kSymmThreads, 0, s>>>(peers, nullptr, static_cast<char*>(local),
+                                                                     segs, items, nitems, world);
   RAFB200_CUDA(cudaGetLastError());
   return RAFB200_OK;
 }
 
-int symm_reduce_scatter(const SymmPeers& peers, const void* mc, size_t off, void* dst, int64_t bytes,
-                        int dtype, int world, int blocks, cudaStream_t s) {
-  RAFB200_REQUIRE(bytes % 16 == 0 && off % 16 == 0, "symm_reduce_scatter: slot is not 16-byte aligned");
-  if (bytes == 0) return RAFB200_OK;
+int symm_reduce_scatter(const SymmPeers& peers, const void* mc, void* local, const SymmSeg* segs,
+                        const Item* items, uint32_t nitems, int dtype, int world, int blocks, cudaStream_t s) {
+  if (nitems == 0) return RAFB200_OK;
   switch (dtype) {
-    case RAFB200_F32: return launch_rs<RAFB200_F32>(peers, mc, off, dst, bytes / 16, world, blocks, s);
-    case RAFB200_F16: return launch_rs<RAFB200_F16>(peers, mc, off, dst, bytes / 16, world, blocks, s);
-    default: return launch_rs<RAFB200_BF16>(peers, mc, off, dst, bytes / 16, world, blocks, s);
+    case RAFB200_F32: return launch_rs<RAFB200_F32>(peers, mc, local, segs, items, nitems, world, blocks, s);
+    case RAFB200_F16: return launch_rs<RAFB200_F16>(peers, mc, local, segs, items, nitems, world, blocks, s);
+    default: return launch_rs<RAFB200_BF16>(peers, mc, local, segs, items, nitems, world, blocks, s);
   }
 }
 
-int symm_allgather(const SymmPeers& peers, void* mc, size_t off, const void* src, int64_t bytes, int world,
-                   int rank, int blocks, cudaStream_t s) {
-  RAFB200_REQUIRE(bytes % 16 == 0 && off % 16 == 0, "symm_allgather: slot is not 16-byte aligned");
-  if (bytes == 0) return RAFB200_OK;
-  const unsigned g = symm_grid(bytes / 16, blocks);
+int symm_allgather(const SymmPeers& peers, void* mc, const void* local, const SymmSeg* segs, const Item* items,
+                   uint32_t nitems, int world, int rank, int blocks, cudaStream_t s) {
+  if (nitems == 0) return RAFB200_OK;
+  const unsigned g = symm_grid(nitems, blocks);
   if (mc)
-    symm_allgather_kernel<true><<<g, kSymmThreads, 0, s>>>(peers, static_cast<char*>(mc), off,
-                                                          static_cast<const char*>(src), bytes / 16, world, rank);
+    symm_allgather_kernel<true><<<g, kSymmThreads, 0, s>>>(peers, static_cast<char*>(mc),
+                                                          static_cast<const char*>(local), segs, items, nitems, world, rank);
   else
-    symm_allgather_kernel<false><<<g, kSymmThreads, 0, s>>>(peers, nullptr, off, static_cast<const char*>(src),
-                                                           bytes / 16, world, rank);
+    symm_allgather_kernel<false><<<g, kSymmThreads, 0, s>>>(peers, nullptr, static_cast<const char*>(local), segs,
+                                                           items, nitems, world, rank);
   RAFB200_CUDA(cudaGetLastError());
   return RAFB200_OK;
 }

@@ -16,11 +16,23 @@ struct SymmPeers {
 // Cross-GPU flag barrier on `lane` (epochs grow by one per call, in the same order on every rank).
 int symm_barrier(const SymmPeers& sig, int world, int rank, int lane, uint32_t epoch,
                  unsigned int* err, cudaStream_t s);
-// dst[0..bytes) = sum over ranks of (buffer + off)[0..bytes); mc = multicast address or NULL.
-int symm_reduce_scatter(const SymmPeers& peers, const void* mc, size_t off, void* dst, int64_t bytes,
-                        int dtype, int world, int blocks, cudaStream_t s);
-// (buffer + off)[0..bytes) on every rank = src[0..bytes).
-int symm_allgather(const SymmPeers& peers, void* mc, size_t off, const void* src, int64_t bytes, int world,
-                   int rank, int blocks, cudaStream_t s);
+constexpr int kSymmChunkBytes = 32768;  // bytes per work item of the collective kernels
+
+// This rank's row block of one tensor inside the symmetric buffer.
+struct SymmSeg {
+  size_t off;      // byte offset from the start of the symmetric buffer, a multiple of 16
+  size_t dst_off;  // reduce-scatter only: byte offset of the result in the local output buffer
+  int64_t bytes;   // a multiple of 16
+};
+
+// out[seg.dst_off ..] = sum over ranks of buffer[seg.off ..] for every segment; `out` is a plain
+// local buffer, so the callers' data in the symmetric buffer stays as it was; mc = multicast
+// address or NULL.
+// `items` lists (segment, 32 KB chunk) pairs; segs and items are device arrays.
+int symm_reduce_scatter(const SymmPeers& peers, const void* mc, void* out, const SymmSeg* segs,
+                        const Item* items, uint32_t nitems, int dtype, int world, int blocks, cudaStream_t s);
+// buffer[seg] on every rank = local[seg] for every segment.
+int symm_allgather(const SymmPeers& peers, void* mc, const void* local, const SymmSeg* segs, const Item* items,
+                   uint32_t nitems, int world, int rank, int blocks, cudaStream_t s);
 
 }  // namespace rafb200

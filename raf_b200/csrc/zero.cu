@@ -50,6 +50,16 @@ struct Bucket {
   Item* dev_pack_items = nullptr;  // (segment, chunk) work items
   Item* dev_unpack_items = nullptr;
   uint32_t n_pack_items = 0, n_unpack_items = 0;
+  // Symmetric mode lays a bucket out tensor-major instead: tensor j owns n row blocks of
+  // align8(shard elements) each, starting n * off[j] elements into the bucket, i.e. the
+  // padded tensor in its natural layout whenever its shard size is a multiple of 8
+  // elements.  The collectives then work on one segment per tensor (this rank's block).
+  int64_t base_elems = 0;          // first element of the bucket inside the flat buffers
+  SymmSeg* dev_rs_segs = nullptr;
+  SymmSeg* dev_ag_segs = nullptr;
+  Item* dev_rs_items = nullptr;
+  Item* dev_ag_items = nullptr;
+  uint32_t n_rs_items = 0, n_ag_items = 0;
 };
 
 // Copies every segment; 16-byte accesses when both ends of a segment are aligned,
@@ -151,6 +161,7 @@ struct rafb200_zero_s {
   rafb200::SymmPeers g_peers{}, p_peers{}, sig_peers{};
   void* g_mc = nullptr;
   void* p_mc = nullptr;
+  char* g_red = nullptr;             // this rank's reduced gradient blocks (plain local memory)
   unsigned int* dev_err = nullptr;   // first expired cross-GPU wait, 0 if none
   uint32_t epoch[2] = {0, 0};        // barrier lanes: 0 before reduce-scatter, 1 after all-gather
   cudaStream_t gather_stream = nullptr;
@@ -250,12 +261,14 @@ int rafb200_zero_destroy(rafb200_zero_t z) {
     for (cudaEvent_t e : {b.packed, b.rs_done, b.upd_done, b.ag_done, b.h2d_done, b.out_ready})
       if (e) cudaEventDestroy(e);
     for (void* ptr : {(void*)b.dev_pack, (void*)b.dev_unpack, (void*)b.dev_pack_items,
-                      (void*)b.dev_unpack_items})
+                      (void*)b.dev_unpack_items, (void*)b.dev_rs_segs, (void*)b.dev_ag_segs,
+                      (void*)b.dev_rs_items, (void*)b.dev_ag_items})
       if (ptr) cudaFree(ptr);
   }
   if (z->g_flat && !z->symmetric) rafb200_comm_free(z->comm, z->g_flat);
   if (z->p_flat && !z->symmetric) rafb200_comm_free(z->comm, z->p_flat);
   if (z->dev_err) cudaFree(z->dev_err);
+  if (z->g_red) cudaFree(z->g_red);
   if (z->gather_stream) cudaStreamDestroy(z->gather_stream);
   if (z->ev_gather) cudaEventDestroy(z->ev_gather);
   if (z->ev_start) cudaEventDestroy(z->ev_start);
@@ -357,6 +370,7 @@ int rafb200_zero_create(rafb200_plan_t plan, rafb200_comm_t comm, int g_dtype, i
       }
       int64_t at = 0;
       for (auto& b : z->buckets) {
+        b.base_elems = at;
         b.g_flat = z->g_flat + (size_t)at * dtype_size(g_dtype);
         b.p_flat = z->p_flat + (size_t)at * dtype_size(param_dtype);
         at += b.slot_elems * z->n;
@@ -401,6 +415,7 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
     std::vector<float*> lp(nt), lm(nt), lv(nt);
     std::vector<void*> lo(nt);
     std::vector<Seg> pack, unpack;
+    std::vector<SymmSeg> rs_segs, ag_segs;
     for (size_t j = 0; j < nt; ++j) {
       const int i = b.tensors[j];
       const int64_t se = z->plan.shard_elems[i];
@@ -414,18 +429,42 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
         lo[j] = params[i];
         continue;
       }
-      // This rank updates slot `rank` of the flat buffers in place.
-      lg[j] = b.g_flat + (size_t)(z->rank * b.slot_elems + b.off[j]) * gs;
-      lo[j] = b.p_flat + (size_t)(z->rank * b.slot_elems + b.off[j]) * ps;
+      // This rank updates its own row block inside the flat buffers, in place.
+      const int64_t bs = (se + 7) & ~(int64_t)7;  // block stride of the tensor-major layout
+      const bool tm = z->symmetric;
+      auto block = [&](int r) -> size_t {          // element offset of row block r of tensor j
+        return tm ? (size_t)(z->n * b.off[j] + r * bs) : (size_t)(r * b.slot_elems + b.off[j]);
+      };
+      lg[j] = b.g_flat + block(z->rank) * gs;
+      lo[j] = b.p_flat + block(z->rank) * ps;
+      if (tm) {
+        // The sum goes to a buffer of its own: the gradients in the symmetric buffer (which
+        // may be the caller's tensors themselves) are inputs only.
+        const size_t red = (size_t)(b.base_elems / z->n + b.off[j]) * gs;
+        lg[j] = z->g_red + red;
+        rs_segs.push_back(SymmSeg{(size_t)(b.g_flat - z->g_flat) + block(z->rank) * gs, red, bs * gs});
+        ag_segs.push_back(SymmSeg{(size_t)(b.p_flat - z->p_flat) + block(z->rank) * ps, 0, bs * ps});
+      }
+      // A caller tensor that IS the tensor's region of the flat buffer needs no copy.
+      const bool g_view = tm && bs == se && grads[i] == b.g_flat + block(0) * gs;
+      const bool p_view = tm && bs == se && params[i] == b.p_flat + block(0) * ps;
+      if (tm && bs == se) {  // natural layout: one contiguous copy per tensor
+        if (!g_view && z->plan.numel[i] > 0)
+          pack.push_back(Seg{static_cast<const char*>(grads[i]), b.g_flat + block(0) * gs,
+                             z->plan.numel[i] * gs, 0});
+        if (!p_view && z->plan.numel[i] > 0)
+          unpack.push_back(Seg{b.p_flat + block(0) * ps, static_cast<char*>(params[i]),
+                               z->plan.numel[i] * ps, 0});
+        continue;
+      }
       for (int r = 0; r < z->n; ++r) {
         // rows of block r that exist in the unpadded tensor (raf.op.pad / strided_slice)
         int64_t cnt = z->plan.numel[i] - (int64_t)r * se;
         cnt = cnt < 0 ? 0 : (cnt > se ? se : cnt);
         if (cnt == 0) continue;
-        const size_t slot = (size_t)(r * b.slot_elems + b.off[j]);
         pack.push_back(Seg{static_cast<const char*>(grads[i]) + (size_t)r * se * gs,
-                           b.g_flat + slot * gs, cnt * gs, 0});
-        unpack.push_back(Seg{b.p_flat + slot * ps, static_cast<char*>(params[i]) + (size_t)r * se * ps,
+                           b.g_flat + block(r) * gs, cnt * gs, 0});
+        unpack.push_back(Seg{b.p_flat + block(r) * ps, static_cast<char*>(params[i]) + (size_t)r * se * ps,
                              cnt * ps, 0});
       }
     }
@@ -442,8 +481,26 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
           (rc = upload(pi.data(), pi.size() * sizeof(Item), reinterpret_cast<void**>(&b.dev_pack_items))) ||
           (rc = upload(ui.data(), ui.size() * sizeof(Item), reinterpret_cast<void**>(&b.dev_unpack_items))))
         return rc;
+      if (z->symmetric) {
+        auto chunks = [](const std::vector<SymmSeg>& segs) {
+          std::vector<Item> items;
+          for (size_t si = 0; si < segs.size(); ++si)
+            for (int64_t c = 0; c * kSymmChunkBytes < segs[si].bytes; ++c)
+              items.push_back(Item{(uint32_t)si, (uint32_t)c});
+          return items;
+        };
+        const std::vector<Item> ri = chunks(rs_segs), ai = chunks(ag_segs);
+        b.n_rs_items = (uint32_t)ri.size();
+        b.n_ag_items = (uint32_t)ai.size();
+        if ((rc = upload(rs_segs.data(), rs_segs.size() * sizeof(SymmSeg), reinterpret_cast<void**>(&b.dev_rs_segs))) ||
+            (rc = upload(ag_segs.data(), ag_segs.size() * sizeof(SymmSeg), reinterpret_cast<void**>(&b.dev_ag_segs))) ||
+            (rc = upload(ri.data(), ri.size() * sizeof(Item), reinterpret_cast<void**>(&b.dev_rs_items))) ||
+            (rc = upload(ai.data(), ai.size() * sizeof(Item), reinterpret_cast<void**>(&b.dev_ag_items))))
+          return rc;
+      }
       z->kernels_per_step += (b.n_pack_items > 0) + (b.n_unpack_items > 0);
-      if (b.slot_elems > 0) z->collectives_per_step += 2;
+      if (z->symmetric) z->kernels_per_step += (b.n_rs_items > 0) + (b.n_ag_items > 0) + 2;  // + 2 barriers
+      else if (b.slot_elems > 0) z->collectives_per_step += 2;  // NCCL calls
     }
   }
   RAFB200_CUDA(cudaStreamSynchronize(nullptr));  // descriptor tables are in place
@@ -479,6 +536,8 @@ int rafb200_zero_attach_symmetric(rafb200_zero_t z, void* const* g_peer, void* g
     z->sig_peers.ptr[q] = signal_peer[q];
   }
   RAFB200_CUDA(cudaMalloc(reinterpret_cast<void**>(&z->dev_err), 16));
+  RAFB200_CUDA(cudaMalloc(reinterpret_cast<void**>(&z->g_red),
+                          (size_t)(z->flat_elems / z->n + 8) * dtype_size(z->g_dtype)));
   RAFB200_CUDA(cudaMemset(z->dev_err, 0, 16));
   RAFB200_CUDA(cudaStreamCreateWithFlags(&z->gather_stream, cudaStreamNonBlocking));
   RAFB200_CUDA(cudaEventCreateWithFlags(&z->ev_gather, cudaEventDisableTiming));
@@ -490,13 +549,27 @@ int rafb200_zero_attach_symmetric(rafb200_zero_t z, void* const* g_peer, void* g
   z->g_mc = g_mc;
   z->p_mc = p_mc;
   z->symmetric = true;
-  if (comm_blocks > 0) z->comm_blocks = comm_blocks;
+  // Plain peer loads need more requests in flight than switch-side reductions do.
+  z->comm_blocks = comm_blocks > 0 ? comm_blocks : (g_mc ? 128 : 2 * z->sm_count);
   int64_t at = 0;
   for (auto& b : z->buckets) {
+    b.base_elems = at;
     b.g_flat = z->g_flat + (size_t)at * dtype_size(z->g_dtype);
     b.p_flat = z->p_flat + (size_t)at * dtype_size(z->param_dtype);
     at += b.slot_elems * z->n;
   }
+  return RAFB200_OK;
+}
+
+int rafb200_zero_arena_offsets(rafb200_zero_t z, int64_t* elem_offset, int* natural) {
+  RAFB200_REQUIRE(z && z->symmetric, "rafb200_zero_arena_offsets: attach symmetric memory first");
+  for (auto& b : z->buckets)
+    for (size_t j = 0; j < b.tensors.size(); ++j) {
+      const int i = b.tensors[j];
+      const int64_t se = z->plan.shard_elems[i];
+      if (elem_offset) elem_offset[i] = b.base_elems + z->n * b.off[j];
+      if (natural) natural[i] = (((se + 7) & ~(int64_t)7) == se) ? 1 : 0;
+    }
   return RAFB200_OK;
 }
 
@@ -633,9 +706,8 @@ static int step_impl(rafb200_zero_t z, const rafb200_hyper* h, int step, void* c
         // every rank has packed this bucket -> sum this rank's slot over all ranks, in place
         rc = symm_barrier(z->sig_peers, z->n, z->rank, 0, ++z->epoch[0], z->dev_err, ms);
         if (rc != RAFB200_OK) return rc;
-        const size_t off = (size_t)(b.g_flat - z->g_flat) + (size_t)z->rank * b.slot_elems * gs;
-        rc = symm_reduce_scatter(z->g_peers, z->g_mc, off, z->g_flat + off, b.slot_elems * gs, z->g_dtype,
-                                 z->n, z->comm_blocks, ms);
+        rc = symm_reduce_scatter(z->g_peers, z->g_mc, z->g_red, b.dev_rs_segs, b.dev_rs_items, b.n_rs_items,
+                                 z->g_dtype, z->n, z->comm_blocks, ms);
       }
       if (rc != RAFB200_OK) return rc;
       RAFB200_CUDA(cudaEventRecord(b.rs_done, ms));
@@ -654,9 +726,8 @@ static int step_impl(rafb200_zero_t z, const rafb200_hyper* h, int step, void* c
         rc = rafb200_allgather(z->comm, b.p_flat + (size_t)z->rank * b.slot_elems * ps, b.p_flat,
                                b.slot_elems, z->param_dtype, ms);
       if ((z->stage_mask & 8) && z->symmetric) {
-        const size_t off = (size_t)(b.p_flat - z->p_flat) + (size_t)z->rank * b.slot_elems * ps;
-        rc = symm_allgather(z->p_peers, z->p_mc, off, z->p_flat + off, b.slot_elems * ps, z->n, z->rank,
-                            z->comm_blocks, as);
+        rc = symm_allgather(z->p_peers, z->p_mc, z->p_flat, b.dev_ag_segs, b.dev_ag_items, b.n_ag_items, z->n,
+                            z->rank, z->comm_blocks, as);
         if (rc != RAFB200_OK) return rc;
         // every rank's slot has landed here before the unpack reads the buffer
         rc = symm_barrier(z->sig_peers, z->n, z->rank, 1, ++z->epoch[1], z->dev_err, as);

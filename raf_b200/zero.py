@@ -176,7 +176,33 @@ class ZeroStep:
             pa([b + p_off for b in bases]), (mc + p_off) if mc else None,
             pa([b + sig_off for b in bases]), int(comm_blocks)))
         self._symm = (buf, handle)  # keeps the mapping alive
+        self._arena = (g_off, p_off)
         self.multicast = bool(mc)
+
+    def arena_views(self):
+        """(grads, params): per tensor a view of its region of the symmetric gradient /
+        parameter buffer in the tensor's own shape, or None where the shard size is not a
+        multiple of 8 elements.  Binding these tensors makes the step copy-free for them."""
+        import numpy as np
+
+        k = self.plan.k
+        off = np.zeros(k, np.int64)
+        nat = np.zeros(k, np.int32)
+        check(_lib.load().rafb200_zero_arena_offsets(self.handle, off.ctypes.data, nat.ctypes.data))
+        buf = self._symm[0]
+        g_off, p_off = self._arena
+        grads, params = [], []
+        for i, shape in enumerate(self.plan.shapes):
+            n = numel(shape)
+            if not nat[i]:
+                grads.append(None)
+                params.append(None)
+                continue
+            for out, base, dt in ((grads, g_off, self.g_dtype), (params, p_off, self.param_dtype)):
+                es = torch.empty((), dtype=dt).element_size()
+                lo = base + int(off[i]) * es
+                out.append(buf[lo:lo + n * es].view(dt).view(shape if len(shape) else ()))
+        return grads, params
 
     def status(self):
         """Synchronise the device; raise if a bounded cross-GPU wait of a step ran out."""

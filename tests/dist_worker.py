@@ -94,7 +94,9 @@ def check_collectives(comm):
     comm.check()
 
 
-MODES = ["nccl", "multimem", "peer"]  # collectives by NCCL / own kernels with / without multicast
+# collectives by NCCL / own kernels with / without multicast / own kernels on gradients and
+# parameters that live inside the symmetric buffer (no pack and unpack copies)
+MODES = ["nccl", "multimem", "peer", "view"]
 
 
 def run_zero(comm, out_dir, mode):
@@ -102,10 +104,14 @@ def run_zero(comm, out_dir, mode):
     for case, (optimizer, g_dtype, p_dtype) in enumerate(CASES):
         plan = Plan(SHAPES, n, r, BUCKET)
         z = ZeroStep(plan, comm, g_dtype, p_dtype, optimizer)
+        gviews = pviews = None
         if mode != "nccl":
-            z.attach_symmetric(multicast=(mode == "multimem"))
-            if mode == "multimem":
+            z.attach_symmetric(multicast=(mode != "peer"))
+            if mode != "peer":
                 assert z.multicast, "no multicast address on this box"
+            if mode == "view":
+                gviews, pviews = z.arena_views()
+                assert any(x is not None for x in gviews) and any(x is None for x in gviews)
         rng = np.random.default_rng(0)
         full_p = [(rng.standard_normal(numel(s)) * 0.02).astype(np.float32) for s in SHAPES]
         tp, tm, tv = [], [], []
@@ -117,6 +123,8 @@ def run_zero(comm, out_dir, mode):
             tm.append(torch.zeros(se, device="cuda"))
             tv.append(torch.zeros(se, device="cuda"))
         params = [torch.zeros(numel(s), dtype=TORCH[p_dtype], device="cuda") for s in SHAPES]
+        if pviews is not None:
+            params = [pv.reshape(-1) if pv is not None else own for pv, own in zip(pviews, params)]
         scale = 2.0 ** -15 if g_dtype == "float16" else 1.0
         hyper = make_hyper(optimizer, learning_rate=0.1 if optimizer == "sgd" else 1e-3, mu=0.9,
                            beta1=0.9, beta2=0.999, eps=1e-6, weight_decay=0.01, grad_scale=scale,
@@ -124,6 +132,11 @@ def run_zero(comm, out_dir, mode):
         saved = {}
         for step in range(1, STEPS + 1):
             grads = [local_grad(r, step, i, numel(s), g_dtype, 1 / scale).cuda() for i, s in enumerate(SHAPES)]
+            if gviews is not None:  # "backward" writes straight into the symmetric buffer
+                for i, gv in enumerate(gviews):
+                    if gv is not None:
+                        gv.reshape(-1).copy_(grads[i])
+                        grads[i] = gv.reshape(-1)
             z.bind(grads, params, tp, tm, tv)
             z.step(hyper, step)
             z.status()
@@ -137,6 +150,8 @@ def run_zero(comm, out_dir, mode):
             saved[f"v_{i}"] = tv[i].cpu().numpy()
             saved[f"param_{i}"] = params[i].float().cpu().numpy()
         kernels, collectives = z.launch_counts()
+        if mode == "view":
+            assert kernels <= 7 * plan.num_buckets
         saved["counts"] = np.array([kernels, collectives, plan.num_buckets])
         np.savez(os.path.join(out_dir, f"case{case}_{mode}_rank{r}.npz"), **saved)
         z.close()
