@@ -348,7 +348,7 @@ def main():
         args.collectives = "multimem"
     if world > 1 and not args.update_blocks and wl["optimizer"] == "lans":
         # leave 16 SMs' worth of block slots to the collective kernels running beside the update
-        args.update_blocks = 2 * (torch.cuda.get_device_properties(dev).multi_processor_count - 16)
+        args.update_blocks = 3 * (torch.cuda.get_device_properties(dev).multi_processor_count - 16)
     collectives_used = args.collectives if world > 1 else "none"
     views_used = 0
     gsets = [[randn(numel(s), 1e-3 * wl["loss_scale"], gdt) for s in shapes] for _ in range(nsets)]
