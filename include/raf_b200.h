@@ -412,7 +412,7 @@ RAFB200_API int rafb200_zero_step(rafb200_zero_t zero, const rafb200_hyper* hype
  * barriers per bucket whose waits are bounded (10 s); rafb200_zero_status
  * synchronises the device and returns RAFB200_DEVICE_WAIT_EXPIRED if one ran
  * out.  comm_blocks = thread blocks per collective kernel (0 = default: 128 with a
- * multicast address, two per SM without).
+ * multicast address, four per SM without).
  * How the memory is obtained is the caller's business (cuMemCreate +
  * cuMulticastBindMem, or torch.distributed._symmetric_memory as the Python
  * layer of this package does).  Call between rafb200_zero_create and

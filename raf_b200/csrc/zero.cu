@@ -550,7 +550,7 @@ int rafb200_zero_attach_symmetric(rafb200_zero_t z, void* const* g_peer, void* g
   z->p_mc = p_mc;
   z->symmetric = true;
   // Plain peer loads need more requests in flight than switch-side reductions do.
-  z->comm_blocks = comm_blocks > 0 ? comm_blocks : (g_mc ? 128 : 2 * z->sm_count);
+  z->comm_blocks = comm_blocks > 0 ? comm_blocks : (g_mc ? 128 : 4 * z->sm_count);
   int64_t at = 0;
   for (auto& b : z->buckets) {
     b.base_elems = at;
