@@ -342,6 +342,8 @@ def main():
     m = [torch.zeros_like(x) for x in p]
     v = [torch.zeros_like(x) for x in p]
     params = [torch.zeros(numel(s), dtype=pdt, device=dev) for s in shapes]
+    if world == 1 and pdt == torch.float32:
+        params = p  # one rank, fp32 model: the parameters are the master copy (no second write)
     # Gradient sets: the step leaves the caller's gradients untouched (they are packed into
     # the bucket buffers first), so a set can be reused; two sets alternate.
     nsets = 1 if world == 1 else 2
@@ -535,7 +537,10 @@ def main():
                        "bucket_elems": wl["bucket_elems"], "buckets": plan.num_buckets if world > 1 else 1,
                        "gradient_sets": nsets, "collectives": collectives_used,
                        "tensors_inside_symmetric_buffer": views_used,
-                       "l2": f"inputs larger than L2 ({wl['bytes_per_elem'] * shard_elems >> 20} MiB touched per step per rank)"},
+                       "l2": (f"inputs larger than L2 ({wl['bytes_per_elem'] * shard_elems >> 20} MiB touched per step per rank)"
+                              if wl['bytes_per_elem'] * shard_elems > (126 << 20) else
+                              f"working set of {wl['bytes_per_elem'] * shard_elems >> 20} MiB fits the 126 MB L2 and is not "
+                              "flushed between steps: not a DRAM-bound measurement")},
             "roofline": roofline,
             "step_roofline": {"bound_ms": bound_ms, "frac": bound_ms / ms_step,
                               "collective_bytes_per_direction": coll_bytes,

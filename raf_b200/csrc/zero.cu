@@ -426,7 +426,9 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
       lv[j] = v ? v[i] : nullptr;
       if (z->n == 1) {
         lg[j] = grads[i];
-        lo[j] = params[i];
+        // An fp32 model whose parameter IS the master copy (python/raf/optim/lans.py:218,
+        // `weight = param`) gets no second write.
+        lo[j] = (params[i] == static_cast<void*>(p[i])) ? nullptr : params[i];
         continue;
       }
       // This rank updates its own row block inside the flat buffers, in place.
