@@ -352,8 +352,11 @@ def main():
         # against 2.47 ms); from four ranks on the multicast kernels win
         args.collectives = "peer" if world == 2 else "multimem"
     if world > 1 and not args.update_blocks and wl["optimizer"] == "lans":
-        # leave 16 SMs' worth of block slots to the collective kernels running beside the update
-        args.update_blocks = 3 * (torch.cuda.get_device_properties(dev).multi_processor_count - 16)
+        # leave block slots to the collective kernels running beside the update: 16 SMs' worth
+        # with the multicast kernels, one block per SM with peer loads (measured 2.13 against
+        # 2.25 ms at two ranks)
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        args.update_blocks = 2 * sms if args.collectives == "peer" else 3 * (sms - 16)
     collectives_used = args.collectives if world > 1 else "none"
     views_used = 0
     gsets = [[randn(numel(s), 1e-3 * wl["loss_scale"], gdt) for s in shapes] for _ in range(nsets)]
