@@ -111,7 +111,7 @@ int rafb200_tensor_list_create(int k, const int64_t* numel, int g_dtype, int out
       for (uint32_t c = 0; c < l->host_desc[i].nchunks; ++c) items.push_back(Item{(uint32_t)i, c});
     rc = upload_items(items, &l->dev_items, &l->n_items);
     if (rc != RAFB200_OK) break;
-    // Defaults.  A block holds up to four tickets and two blocks run per SM, so about
+    // Defaults.  A block holds up to three tickets and three blocks run per SM, so about
     // eight items per SM are in flight; that many items are placed between the last item
     // of a phase of a tensor and the first item that depends on it.  With the round-robin
     // order of the three passes the step time is flat in this value (0 to 32 per SM
