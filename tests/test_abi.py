@@ -108,3 +108,20 @@ def test_comm_adopt_world_of_one_and_bad_arguments(lib):
     assert lib.rafb200_comm_adopt(None, 2, 0, C.byref(h)) == 1  # world of two without a handle
     assert b"NULL ncclComm_t" in lib.rafb200_last_error()
     assert lib.rafb200_comm_adopt(None, 1, 3, C.byref(h)) == 1  # rank outside the world
+
+
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 with nothing but libc headers."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no gcc")
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "raf_b200.h"\n'
+                   "int main(void) { rafb200_hyper h; h.optimizer = RAFB200_OPT_LANS; "
+                   "return rafb200_version() > 0 && h.optimizer == 2 ? 0 : 1; }\n")
+    r = subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-pedantic", "-fsyntax-only",
+                        "-I", os.path.join(ROOT, "include"), str(src)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
