@@ -404,12 +404,10 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
     // queue up - at most kStages of them - and the producer only blocks on a norm when
     // it has no free slot left to fill.  While it waits, data keeps streaming in.
     PendStage* pend = reinterpret_cast<PendStage*>(smem + L::kPendOff);
-    uint32_t resolved_ctr = 0;   // stages [resolved_ctr, stage_ctr) that are not yet resolved
     uint32_t pend_head = 0, pend_count = 0;
     // last norms seen final, per (tensor, phase C?) - lane 0 only
     uint32_t known_t = kTicketEnd;
     uint4 known_nrm = make_uint4(0, 0, 0, 0);
-    (void)resolved_ctr;
 
     auto ratios = [&](uint32_t phase, const uint4& nrm, float* cs, float* rm, float* rg) {
       *cs = s1.gscale;
@@ -462,7 +460,6 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
         resolve_stage(ps.slot, ps.phase, known_nrm);
         pend_head = (pend_head + 1) % kStages;
         --pend_count;
-        ++resolved_ctr;
       }
       return bad;
     };
@@ -566,7 +563,6 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
           const bool settled = !want || (known_t == t && norms_final(known_nrm, phase == kPhaseC));
           if (settled && pend_count == 0) {
             resolve_stage(slot, phase, known_nrm);
-            ++resolved_ctr;
           } else {
             PendStage& ps = pend[(pend_head + pend_count) % kStages];
             ps.slot = slot;

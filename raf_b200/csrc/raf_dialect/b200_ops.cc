@@ -12,6 +12,8 @@
 #include "raf/nccl_communicator.h"
 #include "../../schema/optimizer.h"
 #include "../../schema/communication.h"
+#include "../../schema/transform.h"
+#include "../../schema/memory.h"
 #include "raf_b200.h"
 
 namespace raf { namespace op { namespace b200 {
@@ -179,4 +181,271 @@ class GroupReduceScatterB200 : public OpEnv {
 };
 RAF_REGISTER_DIALECT_OP(b200, _group_reduce_scatter, 20);
 RAF_OP_ENV_MAKER("raf.op.b200._group_reduce_scatter", GroupReduceScatterB200::make);
+
+// ---- the remaining ops of the path: same three steps (parse the schema in the constructor,
+// request stream / communicator, forward DLTensor::data in Execute) ---------------------------
+
+// Shared by the collectives: RAF's communicator object, adopted once.
+class CommEnv : public OpEnv {
+ protected:
+  void* stream_{nullptr};
+  void* communicator_{nullptr};
+  rafb200_comm_t comm_{nullptr};
+  explicit CommEnv(const CallValues& cv, const Value& rank_list) {
+    RequestStream(&stream_, cv->device, StreamTagEnum::CudaCommunicate());
+    RequestDistributed(&communicator_, "nccl", rank_list);
+  }
+  ~CommEnv() { rafb200_comm_destroy(comm_); }
+  rafb200_comm_t Comm() {
+    if (!comm_) {
+      auto* c = reinterpret_cast<distributed::communicator::NCCLCommunicatorObj*>(communicator_);
+      Check(rafb200_comm_adopt(c->nccl_comm, c->size, c->rank, &comm_));
+    }
+    return comm_;
+  }
+};
+
+class ReduceScatterB200 : public CommEnv {
+  std::string computation_;
+ public:
+  explicit ReduceScatterB200(const CallValues& cv)
+      : CommEnv(cv, cv->args.as<op::schema::ReduceScatterArgs>()->rank_list) {
+    static auto fidx = ir::Op::GetAttrMap<op::FRAFSchemaFieldIndex>("FRAFSchemaFieldIndex");
+    static auto base = ir::Op::Get("raf.op._reduce_scatter");
+    this->arg_indices = {fidx[base]("x")};
+    computation_ = cv->args.as<op::schema::ReduceScatterArgs>()->computation;
+  }
+  std::string name() const override { return TruncateName(GetUniqueName("raf.op.b200._reduce_scatter")); }
+  void Execute(const CallValues& cv) override {
+    Execute({cv->args.as<op::schema::ReduceScatterArgs>()->x}, cv->out);
+  }
+  void Execute(const std::vector<Value>& inputs, Value output) override {
+    const DLTensor* x = ir::Downcast<TensorValue>(inputs[0]);
+    DLTensor* y = ir::Downcast<TensorValue>(output);
+    Check(rafb200_reduce_scatter(Comm(), x->data, y->data, Numel(y), DTypeOf(x, &error_msgs),
+                                 computation_.c_str(), stream_));
+  }
+  static OpEnv* make(const CallValues& cv) { return new ReduceScatterB200(cv); }
+};
+RAF_REGISTER_DIALECT_OP(b200, _reduce_scatter, 20);
+RAF_OP_ENV_MAKER("raf.op.b200._reduce_scatter", ReduceScatterB200::make);
+
+class AllGatherB200 : public CommEnv {
+ public:
+  explicit AllGatherB200(const CallValues& cv)
+      : CommEnv(cv, cv->args.as<op::schema::AllgatherArgs>()->rank_list) {
+    static auto fidx = ir::Op::GetAttrMap<op::FRAFSchemaFieldIndex>("FRAFSchemaFieldIndex");
+    static auto base = ir::Op::Get("raf.op._allgather");
+    this->arg_indices = {fidx[base]("x")};
+    // NCCL gathers on axis 0; python/raf/distributed/op.py:20-88 swaps other axes in and out.
+    if (cv->args.as<op::schema::AllgatherArgs>()->axis != 0) error_msgs.push_back("b200._allgather: axis 0 only");
+  }
+  std::string name() const override { return TruncateName(GetUniqueName("raf.op.b200._allgather")); }
+  void Execute(const CallValues& cv) override {
+    Execute({cv->args.as<op::schema::AllgatherArgs>()->x}, cv->out);
+  }
+  void Execute(const std::vector<Value>& inputs, Value output) override {
+    const DLTensor* x = ir::Downcast<TensorValue>(inputs[0]);
+    DLTensor* y = ir::Downcast<TensorValue>(output);
+    Check(rafb200_allgather(Comm(), x->data, y->data, Numel(x), DTypeOf(x, &error_msgs), stream_));
+  }
+  static OpEnv* make(const CallValues& cv) { return new AllGatherB200(cv); }
+};
+RAF_REGISTER_DIALECT_OP(b200, _allgather, 20);
+RAF_OP_ENV_MAKER("raf.op.b200._allgather", AllGatherB200::make);
+
+// _group_allgather writes into the caller's `out` tuple (TRAFInplaceUpdate {2:0}).
+class GroupAllGatherB200 : public CommEnv {
+ public:
+  explicit GroupAllGatherB200(const CallValues& cv) : CommEnv(cv, NullValue<Value>()) {
+    static auto fidx = ir::Op::GetAttrMap<op::FRAFSchemaFieldIndex>("FRAFSchemaFieldIndex");
+    static auto base = ir::Op::Get("raf.op._group_allgather");
+    this->arg_indices = {fidx[base]("tensor_list"), fidx[base]("out")};
+    if (cv->args.as<op::schema::GroupAllgatherArgs>()->axis != 0)
+      error_msgs.push_back("b200._group_allgather: axis 0 only");
+  }
+  std::string name() const override { return TruncateName(GetUniqueName("raf.op.b200._group_allgather")); }
+  void Execute(const CallValues& cv) override {
+    auto args = cv->args.as<op::schema::GroupAllgatherArgs>();
+    Execute({TupleValue::make(ir::Array<Value>(args->tensor_list.begin(), args->tensor_list.end())),
+             TupleValue::make(ir::Array<Value>(args->out.begin(), args->out.end()))}, cv->out);
+  }
+  void Execute(const std::vector<Value>& inputs, Value output) override {
+    auto in = ir::Downcast<TupleValue>(inputs[0]);
+    auto out = ir::Downcast<TupleValue>(inputs[1]);
+    const int k = in->fields.size();
+    std::vector<const void*> src(k);
+    std::vector<void*> dst(k);
+    std::vector<int64_t> count(k);
+    int dtype = RAFB200_F32;
+    for (int i = 0; i < k; ++i) {
+      const DLTensor* x = ir::Downcast<TensorValue>(in->fields[i]);
+      DLTensor* y = ir::Downcast<TensorValue>(out->fields[i]);
+      src[i] = x->data; dst[i] = y->data; count[i] = Numel(x); dtype = DTypeOf(x, &error_msgs);
+    }
+    Check(rafb200_group_allgather(Comm(), k, src.data(), dst.data(), count.data(), dtype, stream_));
+  }
+  static OpEnv* make(const CallValues& cv) { return new GroupAllGatherB200(cv); }
+};
+RAF_REGISTER_DIALECT_OP(b200, _group_allgather, 20);
+RAF_OP_ENV_MAKER("raf.op.b200._group_allgather", GroupAllGatherB200::make);
+
+// _allreduce is in place on every tensor of x (TRAFInplaceUpdate {0:0}); no packing workspace.
+class AllReduceB200 : public CommEnv {
+  std::string computation_;
+ public:
+  explicit AllReduceB200(const CallValues& cv)
+      : CommEnv(cv, cv->args.as<op::schema::AllreduceArgs>()->rank_list) {
+    static auto fidx = ir::Op::GetAttrMap<op::FRAFSchemaFieldIndex>("FRAFSchemaFieldIndex");
+    static auto base = ir::Op::Get("raf.op._allreduce");
+    this->arg_indices = {fidx[base]("x")};
+    computation_ = cv->args.as<op::schema::AllreduceArgs>()->computation;
+  }
+  std::string name() const override { return TruncateName(GetUniqueName("raf.op.b200._allreduce")); }
+  void Execute(const CallValues& cv) override {
+    auto args = cv->args.as<op::schema::AllreduceArgs>();
+    Execute({TupleValue::make(ir::Array<Value>(args->x.begin(), args->x.end()))}, cv->out);
+  }
+  void Execute(const std::vector<Value>& inputs, Value output) override {
+    auto in = ir::Downcast<TupleValue>(inputs[0]);
+    for (size_t i = 0; i < in->fields.size(); ++i) {
+      const DLTensor* x = ir::Downcast<TensorValue>(in->fields[i]);
+      DLTensor* y = in->fields.size() == 1 ? static_cast<DLTensor*>(ir::Downcast<TensorValue>(output))
+                                           : static_cast<DLTensor*>(ir::Downcast<TensorValue>(
+                                                 ir::Downcast<TupleValue>(output)->fields[i]));
+      Check(rafb200_allreduce(Comm(), x->data, y->data, Numel(x), DTypeOf(x, &error_msgs),
+                              computation_.c_str(), stream_));
+    }
+  }
+  static OpEnv* make(const CallValues& cv) { return new AllReduceB200(cv); }
+};
+RAF_REGISTER_DIALECT_OP(b200, _allreduce, 20);
+RAF_OP_ENV_MAKER("raf.op.b200._allreduce", AllReduceB200::make);
+
+// cast / group_cast / fuse_tensor / defuse_tensor run on the compute stream.
+class CastB200 : public OpEnv {
+  void* stream_{nullptr};
+ public:
+  explicit CastB200(const CallValues& cv) {
+    static auto fidx = ir::Op::GetAttrMap<op::FRAFSchemaFieldIndex>("FRAFSchemaFieldIndex");
+    static auto base = ir::Op::Get("raf.op.cast");
+    this->arg_indices = {fidx[base]("data")};
+    RequestStream(&stream_, cv->device, StreamTagEnum::CudaCompute());
+  }
+  std::string name() const override { return TruncateName(GetUniqueName("raf.op.b200.cast")); }
+  void Execute(const CallValues& cv) override { Execute({cv->args.as<op::schema::CastArgs>()->data}, cv->out); }
+  void Execute(const std::vector<Value>& inputs, Value output) override {
+    const DLTensor* x = ir::Downcast<TensorValue>(inputs[0]);
+    DLTensor* y = ir::Downcast<TensorValue>(output);
+    Check(rafb200_cast(x->data, DTypeOf(x, &error_msgs), y->data, DTypeOf(y, &error_msgs), Numel(x), stream_));
+  }
+  static OpEnv* make(const CallValues& cv) { return new CastB200(cv); }
+};
+RAF_REGISTER_DIALECT_OP(b200, cast, 20);
+RAF_OP_ENV_MAKER("raf.op.b200.cast", CastB200::make);
+
+class GroupCastB200 : public OpEnv {
+  void* stream_{nullptr};
+ public:
+  explicit GroupCastB200(const CallValues& cv) {
+    static auto fidx = ir::Op::GetAttrMap<op::FRAFSchemaFieldIndex>("FRAFSchemaFieldIndex");
+    static auto base = ir::Op::Get("raf.op.group_cast");
+    this->arg_indices = {fidx[base]("tensor_list")};
+    RequestStream(&stream_, cv->device, StreamTagEnum::CudaCompute());
+  }
+  std::string name() const override { return TruncateName(GetUniqueName("raf.op.b200.group_cast")); }
+  void Execute(const CallValues& cv) override {
+    auto args = cv->args.as<op::schema::GroupCastArgs>();
+    Execute({TupleValue::make(ir::Array<Value>(args->tensor_list.begin(), args->tensor_list.end()))}, cv->out);
+  }
+  void Execute(const std::vector<Value>& inputs, Value output) override {
+    auto in = ir::Downcast<TupleValue>(inputs[0]);
+    auto out = ir::Downcast<TupleValue>(output);
+    const int k = in->fields.size();
+    if (k == 0) return;
+    std::vector<const void*> src(k);
+    std::vector<void*> dst(k);
+    std::vector<int64_t> numel(k);
+    for (int i = 0; i < k; ++i) {
+      const DLTensor* x = ir::Downcast<TensorValue>(in->fields[i]);
+      DLTensor* y = ir::Downcast<TensorValue>(out->fields[i]);
+      src[i] = x->data; dst[i] = y->data; numel[i] = Numel(x);
+    }
+    const DLTensor* x0 = ir::Downcast<TensorValue>(in->fields[0]);
+    const DLTensor* y0 = ir::Downcast<TensorValue>(out->fields[0]);
+    Check(rafb200_group_cast(k, src.data(), DTypeOf(x0, &error_msgs), dst.data(), DTypeOf(y0, &error_msgs),
+                             numel.data(), stream_));
+  }
+  static OpEnv* make(const CallValues& cv) { return new GroupCastB200(cv); }
+};
+RAF_REGISTER_DIALECT_OP(b200, group_cast, 20);
+RAF_OP_ENV_MAKER("raf.op.b200.group_cast", GroupCastB200::make);
+
+// fuse_tensor / defuse_tensor (replace CudaFuseTensor / CudaDefuseTensor,
+// src/op/dialect/cuda/memory.cc:20-134): one launch instead of one copy per tensor.
+class FuseTensorB200 : public OpEnv {
+  void* stream_{nullptr};
+ public:
+  explicit FuseTensorB200(const CallValues& cv) {
+    static auto fidx = ir::Op::GetAttrMap<op::FRAFSchemaFieldIndex>("FRAFSchemaFieldIndex");
+    static auto base = ir::Op::Get("raf.op.fuse_tensor");
+    this->arg_indices = {fidx[base]("data")};
+    RequestStream(&stream_, cv->device, StreamTagEnum::MemCudaToCuda1());
+  }
+  std::string name() const override { return TruncateName(GetUniqueName("raf.op.b200.fuse_tensor")); }
+  void Execute(const CallValues& cv) override {
+    auto args = cv->args.as<op::schema::FuseTensorArgs>();
+    Execute({TupleValue::make(ir::Array<Value>(args->data.begin(), args->data.end()))}, cv->out);
+  }
+  void Execute(const std::vector<Value>& inputs, Value output) override {
+    auto in = ir::Downcast<TupleValue>(inputs[0]);
+    DLTensor* flat = ir::Downcast<TensorValue>(output);
+    const int k = in->fields.size();
+    std::vector<const void*> src(k);
+    std::vector<int64_t> numel(k), offset(k);
+    int64_t at = 0;
+    for (int i = 0; i < k; ++i) {
+      const DLTensor* x = ir::Downcast<TensorValue>(in->fields[i]);
+      src[i] = x->data; numel[i] = Numel(x); offset[i] = at; at += numel[i];
+    }
+    Check(rafb200_fuse_tensor(k, src.data(), numel.data(), offset.data(), flat->dtype.bits / 8, flat->data, stream_));
+  }
+  static OpEnv* make(const CallValues& cv) { return new FuseTensorB200(cv); }
+};
+RAF_REGISTER_DIALECT_OP(b200, fuse_tensor, 20);
+RAF_OP_ENV_MAKER("raf.op.b200.fuse_tensor", FuseTensorB200::make);
+
+class DefuseTensorB200 : public OpEnv {
+  void* stream_{nullptr};
+  std::vector<int64_t> sizes_;
+ public:
+  explicit DefuseTensorB200(const CallValues& cv) {
+    static auto fidx = ir::Op::GetAttrMap<op::FRAFSchemaFieldIndex>("FRAFSchemaFieldIndex");
+    static auto base = ir::Op::Get("raf.op.defuse_tensor");
+    this->arg_indices = {fidx[base]("data")};
+    sizes_ = cv->args.as<op::schema::DefuseTensorArgs>()->sizes;
+    RequestStream(&stream_, cv->device, StreamTagEnum::MemCudaToCuda2());
+  }
+  std::string name() const override { return TruncateName(GetUniqueName("raf.op.b200.defuse_tensor")); }
+  void Execute(const CallValues& cv) override {
+    Execute({cv->args.as<op::schema::DefuseTensorArgs>()->data}, cv->out);
+  }
+  void Execute(const std::vector<Value>& inputs, Value output) override {
+    const DLTensor* flat = ir::Downcast<TensorValue>(inputs[0]);
+    auto out = ir::Downcast<TupleValue>(output);
+    const int k = out->fields.size();
+    std::vector<void*> dst(k);
+    std::vector<int64_t> offset(k);
+    int64_t at = 0;
+    for (int i = 0; i < k; ++i) {
+      DLTensor* y = ir::Downcast<TensorValue>(out->fields[i]);
+      dst[i] = y->data; offset[i] = at; at += sizes_[i];
+    }
+    Check(rafb200_defuse_tensor(k, dst.data(), sizes_.data(), offset.data(), flat->dtype.bits / 8, flat->data, stream_));
+  }
+  static OpEnv* make(const CallValues& cv) { return new DefuseTensorB200(cv); }
+};
+RAF_REGISTER_DIALECT_OP(b200, defuse_tensor, 20);
+RAF_OP_ENV_MAKER("raf.op.b200.defuse_tensor", DefuseTensorB200::make);
+
 }}}  // namespace raf::op::b200
