@@ -149,6 +149,20 @@ RAFB200_API int rafb200_lans(rafb200_tensor_list_t list, int step, const float* 
                              int bias_correction, float weight_decay, int grad_averaging, int mode,
                              int normalize_grad, float grad_scale, void* workspace,
                              size_t workspace_bytes, void* stream);
+/* The order in which the LANS kernel hands out its work items for a list of
+ * these element counts (host only, no GPU needed; for inspection and tests).
+ * An item is two words: bits 31..30 of the first = phase (0 gradient norm,
+ * 1 moments + update norms, 2 parameter update), bits 29..0 = tensor index; the
+ * second = index of the 4096-element chunk inside the tensor.  Blocks draw items
+ * in this order from one counter; an item of phase 1 waits for every phase-0
+ * item of its tensor and an item of phase 2 for every phase-1 item of its tensor,
+ * all of which come earlier in the order, so a running block only ever waits
+ * for items that running blocks hold.  The reference has no such object: its
+ * six passes are separate launches (multi_tensor_lans.cu:401-450).
+ * items may be NULL to query *count alone; capacity counts items. */
+RAFB200_API int rafb200_lans_schedule(int k, const int64_t* numel, int with_norm_phase,
+                                      int64_t window_elems, int slack_items, uint32_t* items,
+                                      size_t capacity, size_t* count);
 /* Synchronises `stream`, then reports whether the last rafb200_lans on this
  * workspace completed (RAFB200_OK) or a bounded device wait expired.
  * norms_host (optional, 4*k floats, tensor-major) receives

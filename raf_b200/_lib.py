@@ -53,6 +53,7 @@ SIGNATURES = {
     "rafb200_sgd_list": (_i, [_vp, _f, _f, _f, _f, _vp]),
     "rafb200_lans_workspace_bytes": (_sz, [_vp]),
     "rafb200_lans": (_i, [_vp, _i, _vp, _f, _f, _f, _f, _i, _f, _i, _i, _i, _f, _vp, _sz, _vp]),
+    "rafb200_lans_schedule": (_i, [_i, _vp, _i, _i64, _i, _vp, _sz, _P(_sz)]),
     "rafb200_lans_status": (_i, [_vp, _vp, _vp, _vp]),
     "rafb200_lans_tensor_static": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _i64, _i, _f, _f, _f, _f,
                                         _i, _f, _i, _i, _i, _f, _vp]),

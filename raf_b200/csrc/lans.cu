@@ -1111,6 +1111,30 @@ int rafb200_lans_tensor_static(const void* g, int g_dtype, float* p, float* m, f
   }
 }
 
+int rafb200_lans_schedule(int k, const int64_t* numel, int with_norm_phase, int64_t window_elems,
+                          int slack_items, uint32_t* items, size_t capacity, size_t* count) {
+  RAFB200_REQUIRE(k >= 0 && (k == 0 || numel) && count && window_elems >= 0 && slack_items >= 0,
+                  "rafb200_lans_schedule: bad arguments");
+  std::vector<uint32_t> nchunks(k);
+  for (int i = 0; i < k; ++i) {
+    RAFB200_REQUIRE(numel[i] >= 0, "rafb200_lans_schedule: numel[%d] < 0", i);
+    nchunks[i] = (uint32_t)((numel[i] + kChunkElems - 1) / kChunkElems);
+  }
+  int64_t window_chunks = window_elems / kChunkElems;
+  if (window_chunks < 1) window_chunks = 1;
+  const std::vector<Item> sched = build_lans_schedule(nchunks, with_norm_phase != 0, window_chunks, slack_items);
+  *count = sched.size();
+  if (items) {
+    RAFB200_REQUIRE(capacity >= sched.size(), "rafb200_lans_schedule: %zu items, room for %zu", sched.size(),
+                    capacity);
+    for (size_t i = 0; i < sched.size(); ++i) {
+      items[2 * i] = sched[i].tensor_phase;
+      items[2 * i + 1] = sched[i].chunk;
+    }
+  }
+  return RAFB200_OK;
+}
+
 int rafb200_lans_status(rafb200_tensor_list_t list, const void* workspace, float* norms_host,
                         void* stream) {
   RAFB200_REQUIRE(list && workspace, "rafb200_lans_status: NULL argument");
