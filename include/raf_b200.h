@@ -370,6 +370,10 @@ RAFB200_API int rafb200_plan_totals(rafb200_plan_t plan, int64_t* elems, int64_t
  *   params[i]  full model parameter, dim0 x row_elems, param_dtype: receives
  *              the all-gathered update.
  *   p/m/v[i]   fp32 master shard and optimizer state, shard_elems[i] each.
+ * Binding is a set-up operation: when a pointer differs from the previous
+ * bind it synchronises the device and rebuilds the device tables (it returns at
+ * once when nothing changed).  Bind once and let backward write into the bound
+ * gradient tensors; do not re-bind inside a timed step loop.
  * With more than one rank the state object owns two rank-major flat buffers per
  * bucket (gradients, parameter copies; padded elements x dtype size each in
  * total).  A step is, per bucket: one pack kernel (row block r of every gradient

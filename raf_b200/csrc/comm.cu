@@ -269,6 +269,8 @@ int rafb200_comm_create(int world_size, int rank, int device, const char* store_
 int rafb200_comm_destroy(rafb200_comm_t c) {
   if (!c) return RAFB200_OK;
   int rc = RAFB200_OK;
+  // Buffers the caller forgot to hand back: deregister and free them with the communicator.
+  while (!c->regs.empty()) rafb200_comm_free(c, c->regs.begin()->first);
   if (c->nccl && !c->borrowed) {
     ncclResult_t r = ncclCommDestroy(c->nccl);
     if (r != ncclSuccess) rc = nccl_fail(r, "ncclCommDestroy");
