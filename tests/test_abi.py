@@ -125,3 +125,24 @@ def test_header_is_plain_c(tmp_path):
     r = subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-pedantic", "-fsyntax-only",
                         "-I", os.path.join(ROOT, "include"), str(src)], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
+
+
+def test_no_cpu_fallback(tmp_path):
+    """The product has no host path: CPU tensors are refused, and a missing library is an error
+    at load time, not a silent switch to something else."""
+    import subprocess
+    import sys
+
+    import torch
+
+    from raf_b200 import op
+
+    x = torch.zeros(8)
+    with pytest.raises(ValueError, match="no CPU path"):
+        op.sgd_(x, x.clone(), x.clone(), 0.1, 0.9)
+    with pytest.raises(ValueError, match="no CPU path"):
+        op.cast(x, "float16")
+    env = dict(os.environ, RAFB200_LIB=str(tmp_path / "absent" / "libraf_b200.so"), PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-c", "from raf_b200 import _lib; _lib.load()"], env=env,
+                       capture_output=True, text=True)
+    assert r.returncode != 0 and "libraf_b200.so" in r.stderr
