@@ -312,9 +312,21 @@ int rafb200_zero_create(rafb200_plan_t plan, rafb200_comm_t comm, int g_dtype, i
     const int nb = (z->n == 1) ? (k > 0 ? 1 : 0) : plan->nbuckets;
     z->buckets.resize(nb);
     for (int i = 0; i < k; ++i) z->buckets[z->n == 1 ? 0 : plan->bucket_of[i]].tensors.push_back(i);
-    if (z->n == 1 && plan->nbuckets > 1) {
-      z->hbuckets.resize(plan->nbuckets);
-      for (int i = 0; i < k; ++i) z->hbuckets[plan->bucket_of[i]].tensors.push_back(i);
+    if (z->n == 1 && k > 1) {
+      // Host-buffer form on one rank: groups of about 16 Mi elements (32-64 MB over PCIe, a
+      // few ms each way), small enough that the first copy in and the last copy out, which
+      // nothing overlaps, stay short.
+      constexpr int64_t kHostGroupElems = 16ll << 20;
+      int64_t run = 0;
+      for (int i = 0; i < k; ++i) {
+        if (z->hbuckets.empty() || (run > 0 && run + plan->numel[i] > kHostGroupElems)) {
+          z->hbuckets.emplace_back();
+          run = 0;
+        }
+        z->hbuckets.back().tensors.push_back(i);
+        run += plan->numel[i];
+      }
+      if (z->hbuckets.size() < 2) z->hbuckets.clear();
     }
     int64_t flat_elems = 0;
     for (auto* set : {&z->buckets, &z->hbuckets}) {
