@@ -858,7 +858,8 @@ std::vector<Item> build_lans_schedule(const std::vector<uint32_t>& nchunks, bool
   // (bursts, 2:1 to 8:1 catch-up) re-read less but stalled more and measured slower, and
   // visiting the tensors smallest first cut the DRAM reads by 12 % but left the huge ones
   // as an unoverlapped tail (2.33 ms); huge tensors first, the rest smallest first, with
-  // phase C catching up to one tensor behind cut the reads by 7 % and took 2.39 ms.  Fewer
+  // phase C catching up to one tensor behind cut the reads by 7 % and took 2.39 ms (2.42 ms
+  // with the tiny tensors left mixed among the medium ones).  Fewer
   // DRAM bytes did not buy time in any of them: what limits the kernel once phase C runs
   // close behind phase B is the wait for the norms, not bandwidth.
   while (Cc.t < k) {
