@@ -40,10 +40,10 @@ NVLINK_MEASURED_GBS = 770.0  # peer copy, per direction per GPU, measured on thi
 # DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (workload, n_gpus, shard_of) -> bytes
 MEASURED_TRAFFIC = {
-    ("bert_lans", 1, 1): 14644761344,   # profiles/lans_kernel_bert_large_n1.md
-    ("bert_lans", 1, 8): 1695229304,    # profiles/lans_kernel_bert_large_shard8_full.md
-    ("rn50_sgd", 1, 1): 454225920,      # profiles/update_list_kernel_sgd_rn50.md
-    ("gpt2_adam", 1, 8): 1184124416,    # profiles/update_list_kernel_adam_gpt2_shard8.md
+    ("bert_lans", 1, 1): 14644761344,
+    ("bert_lans", 1, 8): 1695229304,
+    ("rn50_sgd", 1, 1): 454225920,
+    ("gpt2_adam", 1, 8): 1184124416,
 }
 
 
