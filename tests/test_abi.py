@@ -146,3 +146,33 @@ def test_no_cpu_fallback(tmp_path):
     r = subprocess.run([sys.executable, "-c", "from raf_b200 import _lib; _lib.load()"], env=env,
                        capture_output=True, text=True)
     assert r.returncode != 0 and "libraf_b200.so" in r.stderr
+
+
+def test_plan_geometry_random_shapes_vs_oracle():
+    """Shard rows, padding and bucket membership for random tensor lists, world sizes and bucket
+    sizes, against the oracle's restatement of the partition passes."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    from raf_b200.zero import Plan, numel
+
+    shape = st.lists(st.integers(0, 40), min_size=1, max_size=3).map(tuple)
+
+    @settings(max_examples=80, deadline=None)
+    @given(st.lists(shape, min_size=1, max_size=10), st.sampled_from([1, 2, 3, 4, 8]),
+           st.sampled_from([1, 10, 100, 1000, 1 << 40]))
+    def run(shapes, n, bucket):
+        sizes = [numel(s) for s in shapes]
+        nb, bucket_of = O.plan_buckets(sizes, bucket, rule=1)
+        for rank in {0, n - 1}:
+            plan = Plan(shapes, n, rank, bucket)
+            assert plan.num_buckets == nb and plan.bucket_of.tolist() == bucket_of.tolist()
+            for i, s in enumerate(shapes):
+                rows = O.shard_rows(s[0], n)
+                row = numel(s[1:]) if len(s) > 1 else 1
+                assert plan.shard_rows[i] == rows == -(-s[0] // n)
+                assert plan.shard_elems[i] == rows * row and plan.padded_elems[i] == rows * row * n
+            assert plan.total_shard * n == plan.total_padded >= plan.total_elems == sum(sizes)
+            plan.close()
+
+    run()
