@@ -404,6 +404,7 @@ def main():
         return float(t.item())
 
     step_no = 0
+    barrier()  # ranks finish their set-up at different times; the step's own waits are bounded
     for w in range(args.warmup):
         step_no += 1
         zs[step_no % nsets].step(hyper, step_no, compute, comm_stream)
