@@ -83,13 +83,27 @@ RAFB200_API int rafb200_tensor_list_destroy(rafb200_tensor_list_t list);
 RAFB200_API int64_t rafb200_tensor_list_total_elems(rafb200_tensor_list_t list);
 
 /* Scheduling knobs of the LANS kernel for this list (see rafb200_lans):
- * window_elems = how far (in elements) the norm pass may run ahead of the
- * update pass so that the re-read hits L2; slack_items = work items placed
- * between the last norm item of a tensor and its first update item;
- * max_blocks = cap on the persistent grid (0 = fill the GPU), used to leave
- * SMs to a concurrent collective.  Defaults are chosen at creation. */
-RAFB200_API int rafb200_tensor_list_tune(rafb200_tensor_list_t list, int64_t window_elems,
-                                         int slack_items, int max_blocks);
+ * lead_elems = how far (in elements) the gradient-norm items run ahead of the
+ * other items; gap_items = work items placed between a tensor's last parked item
+ * and its streamed update items (0 = one per shared-memory slot of the grid);
+ * max_blocks = cap on the persistent grid (0 = one block per SM), used to leave
+ * SMs to a concurrent collective.  Defaults are chosen at creation; a change
+ * rebuilds the work-item table (and synchronises the device first). */
+RAFB200_API int rafb200_tensor_list_tune(rafb200_tensor_list_t list, int64_t lead_elems,
+                                         int gap_items, int max_blocks);
+/* Bound of every wait inside the LANS kernel, in milliseconds (default 2000).
+ * When a wait runs out the kernel records it and returns; rafb200_lans_status
+ * then reports RAFB200_DEVICE_WAIT_EXPIRED.  The reference has no in-kernel
+ * waits: its passes are separate launches. */
+RAFB200_API int rafb200_tensor_list_set_wait_limit(rafb200_tensor_list_t list, int limit_ms);
+/* Replaces the work-item table of the LANS kernel for this list by the caller's
+ * (same encoding as rafb200_lans_schedule; used with and without gradient
+ * normalisation), for experiments with other orders.  The caller is responsible
+ * for the order's dependencies: an item that is placed before the items it waits
+ * for makes the kernel give up after the wait limit.  rafb200_tensor_list_tune
+ * restores the built-in order. */
+RAFB200_API int rafb200_tensor_list_set_lans_items(rafb200_tensor_list_t list, const uint32_t* items,
+                                                   size_t count);
 
 /* ------------------------------------------------------------------------- */
 /* Optimizer updates (shard-local)                                            */
@@ -122,10 +136,14 @@ RAFB200_API int rafb200_sgd_list(rafb200_tensor_list_t list, float learning_rate
  *   (scripts/src_codegen/def_schema.py:678-694; host src/op/dialect/cuda/lans.cc:25-165;
  *    kernels src/op/dialect/cuda/kernels/multi_tensor_lans.cu:95-450).
  * Same argument meaning and per-element formulas.  Differences, all deliberate:
- *   - one persistent launch instead of about fifty; per-tensor norms are
- *     reduced warp-shuffle-then-block in the same kernel and summed across
- *     chunks in double precision (exact, hence independent of arrival order,
- *     for any realistic tensor), not in the reference's chunk/tree order;
+ *   - one persistent launch instead of about fifty.  A chunk of a tensor is
+ *     loaded into shared memory once and stays there while the tensor-wide
+ *     norms stage 2 needs are completed by the other thread blocks, so every
+ *     array is read once and written once; only the part of a tensor that
+ *     exceeds what the grid can hold on chip is read a second time.  Per-tensor
+ *     norms are reduced warp-shuffle-then-block in the same kernel and summed
+ *     across chunks in double precision (exact, hence independent of arrival
+ *     order, for any realistic tensor), not in the reference's chunk/tree order;
  *     reciprocals and square roots use the approximate (<= 1 ulp) hardware
  *     forms with fused multiply-adds: p, m, v agree with the reference
  *     arithmetic to ~3e-6 relative after 10 steps, inside the 1e-5 the path
@@ -151,18 +169,29 @@ RAFB200_API int rafb200_lans(rafb200_tensor_list_t list, int step, const float* 
                              size_t workspace_bytes, void* stream);
 /* The order in which the LANS kernel hands out its work items for a list of
  * these element counts (host only, no GPU needed; for inspection and tests).
- * An item is two words: bits 31..30 of the first = phase (0 gradient norm,
- * 1 moments + update norms, 2 parameter update), bits 29..0 = tensor index; the
- * second = index of the 4096-element chunk inside the tensor.  Blocks draw items
- * in this order from one counter; an item of phase 1 waits for every phase-0
- * item of its tensor and an item of phase 2 for every phase-1 item of its tensor,
- * all of which come earlier in the order, so a running block only ever waits
- * for items that running blocks hold.  The reference has no such object: its
- * six passes are separate launches (multi_tensor_lans.cu:401-450).
+ * An item is two words: bits 31..30 of the first = kind, bits 29..0 = tensor
+ * index; the second = index of the item's chunk inside the tensor.  Kinds:
+ *   0  gradient norm: sum of squares of 7168 (16-bit gradients) / 4096 (fp32)
+ *      elements of g;
+ *   1  "streamed" stage 1 of 1024 elements: sums of squares of p, update_m,
+ *      update_g only;
+ *   2  "streamed" update of 1024 elements: stage 1 again, then stage 2, stores;
+ *   3  "parked": stage 1 and, once the tensor's norms are final, stage 2 of 1024
+ *      elements that stay in shared memory in between.
+ * Blocks draw items in this order from one counter.  Kinds 1 and 3 wait for every
+ * kind-0 item of their tensor (only with normalize_grad); kind 2 and the second
+ * half of kind 3 wait for every kind-1 and kind-3 item of their tensor.  An item
+ * only waits for items that come earlier in the order, and at most
+ * two thirds of the grid's shared-memory slots (slots_total = blocks x 15 slots
+ * for 16-bit gradients, x 13 for fp32) ever hold parked items of one tensor, so a
+ * running block only ever waits for items that running blocks hold.  The
+ * reference has no such object: its six passes are separate launches
+ * (multi_tensor_lans.cu:401-450).  lead_elems and gap_items as in
+ * rafb200_tensor_list_tune (gap_items 0 = slots_total).
  * items may be NULL to query *count alone; capacity counts items. */
-RAFB200_API int rafb200_lans_schedule(int k, const int64_t* numel, int with_norm_phase,
-                                      int64_t window_elems, int slack_items, uint32_t* items,
-                                      size_t capacity, size_t* count);
+RAFB200_API int rafb200_lans_schedule(int k, const int64_t* numel, int g_dtype, int with_norm_phase,
+                                      int slots_total, int64_t lead_elems, int gap_items,
+                                      uint32_t* items, size_t capacity, size_t* count);
 /* Synchronises `stream`, then reports whether the last rafb200_lans on this
  * workspace completed (RAFB200_OK) or a bounded device wait expired.
  * norms_host (optional, 4*k floats, tensor-major) receives
@@ -182,7 +211,7 @@ RAFB200_API int rafb200_lans_status(rafb200_tensor_list_t list, const void* work
  * g_dtype; out NULL or of out_dtype); the header, control words, descriptor row
  * and work-item table that rafb200_lans keeps in its workspace and list object
  * live in a fixed device array that is part of the library image instead.
- *   - Limit: numel <= 4,194,304 (4 Mi elements, the size the 25 KB array is laid
+ *   - Limit: numel <= 4,194,304 (4 Mi elements, the size the 74 KB array is laid
  *     out for).  Larger tensors are refused with RAFB200_INVALID_ARGUMENT; use
  *     rafb200_lans for them.  `step` is a host integer.
  *   - The first call on each device looks up the array's device address (once,
@@ -427,10 +456,15 @@ RAFB200_API int rafb200_zero_step(rafb200_zero_t zero, const rafb200_hyper* hype
  * multimem.st of this rank's slot, on two streams so that they use the links
  * in opposite directions at the same time; without a multicast address the
  * same kernels read / write the peers one by one.  Ranks meet at two flag
- * barriers per bucket whose waits are bounded (10 s); rafb200_zero_status
- * synchronises the device and returns RAFB200_DEVICE_WAIT_EXPIRED if one ran
- * out.  comm_blocks = thread blocks per collective kernel (0 = default: 128 with a
- * multicast address, four per SM without).
+ * barriers per bucket whose waits are bounded (10 s unless changed with
+ * rafb200_zero_set_wait_limit).  When a wait runs out the kernel records it in
+ * host-mapped memory: the next rafb200_zero_step / rafb200_zero_step_host on that
+ * rank queues nothing and returns RAFB200_DEVICE_WAIT_EXPIRED (no device
+ * synchronisation needed), and so does rafb200_zero_status after synchronising.
+ * The ranks are then out of step (the late rank's barrier epochs lag): destroy
+ * the state on every rank and create it again; results of the step that timed
+ * out are invalid.  comm_blocks = thread blocks per collective kernel
+ * (0 = default: 128 with a multicast address, four per SM without).
  * How the memory is obtained is the caller's business (cuMemCreate +
  * cuMulticastBindMem, or torch.distributed._symmetric_memory as the Python
  * layer of this package does).  Call between rafb200_zero_create and
@@ -454,6 +488,18 @@ RAFB200_API int rafb200_zero_attach_symmetric(rafb200_zero_t zero, void* const* 
  * modified (sums go to a shard-sized buffer of the step object). */
 RAFB200_API int rafb200_zero_arena_offsets(rafb200_zero_t zero, int64_t* elem_offset, int* natural);
 RAFB200_API int rafb200_zero_status(rafb200_zero_t zero);
+/* Bound of every cross-GPU wait of the symmetric mode, in milliseconds (default
+ * 10000).  A rank may legitimately be late by a data-loader stall or a checkpoint:
+ * choose the limit above the longest skew the job tolerates.  The reference has no
+ * such limit: a rank that never joins a collective hangs the job
+ * (src/op/dialect/nccl/nccl.cc:308,387 enqueue and never look back). */
+RAFB200_API int rafb200_zero_set_wait_limit(rafb200_zero_t zero, int limit_ms);
+/* Device address of the gradient block the update of tensor `tensor` reads: the
+ * caller's gradient with one rank, this rank's reduced row block (the output of
+ * the reduce-scatter, valid once a step's reduce-scatter of that bucket is
+ * complete) otherwise.  shard_elems[tensor] elements of the gradient dtype.  It is
+ * what the sliced `dxi` of python/raf/optim/lans.py:254-259 holds. */
+RAFB200_API int rafb200_zero_shard_grad(rafb200_zero_t zero, int tensor, const void** ptr);
 /* Measurement aid: issue only the selected stages of a multi-rank step
  * (bit 0 pack, 1 reduce-scatter, 2 update, 3 all-gather, 4 unpack; default 31).
  * With a stage missing the results are meaningless; every rank must use the
@@ -471,9 +517,26 @@ RAFB200_API int rafb200_zero_set_update_blocks(rafb200_zero_t zero, int max_bloc
 /* caller without device buffers (a CPU executor) would use.  Copies run on    */
 /* `stream`; pinned host memory makes them asynchronous.                       */
 /* ------------------------------------------------------------------------- */
+/* The call enqueues and returns; `compute_stream` ends up waiting for the last  */
+/* copy to the host.  One cudaMemcpyAsync per tensor and direction, unless the   */
+/* caller declared arenas (below).                                               */
 RAFB200_API int rafb200_zero_step_host(rafb200_zero_t zero, const rafb200_hyper* hyper, int step,
                                        const void* const* grads_host, void* const* params_host,
                                        void* compute_stream, void* comm_stream);
+/* Declares [base, base + bytes) - host or device memory - to be ONE allocation.
+ * rafb200_zero_step_host merges the copies of tensors that follow one another
+ * without a gap on both sides when source and destination each lie inside one
+ * declared range: a caller that keeps its host gradients in one pinned arena, its
+ * host parameters in another and the bound device tensors likewise pays one copy
+ * per bucket and direction instead of one per tensor (782 for BERT-large).
+ * Undeclared memory is never merged, because a copy may not span two allocations. */
+RAFB200_API int rafb200_zero_declare_arena(rafb200_zero_t zero, const void* base, size_t bytes);
+/* What rafb200_zero_step_host copies back: 0 (default) the whole of every
+ * parameter on every rank; 1 only the rows this rank owns (rows
+ * [rank*shard_rows, (rank+1)*shard_rows) of each tensor, written at the same
+ * offset of params_host[i]), so that n ranks sharing one host move each
+ * parameter across PCIe once, not n times. */
+RAFB200_API int rafb200_zero_set_host_output(rafb200_zero_t zero, int mode);
 
 #ifdef __cplusplus
 }

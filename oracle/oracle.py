@@ -70,12 +70,24 @@ def lib():
         L.oracle_plan_buckets.restype = C.c_int
         L.oracle_plan_buckets.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p]
         L.oracle_num_threads.restype = C.c_int
+        L.oracle_set_num_threads.restype = C.c_int
+        L.oracle_set_num_threads.argtypes = [C.c_int]
         _lib = L
     return _lib
 
 
 def num_threads() -> int:
     return lib().oracle_num_threads()
+
+
+def use_all_host_threads() -> int:
+    """Thread count = the cores this process may run on, whatever OMP_NUM_THREADS a
+    launcher exported (torch.distributed.run sets it to 1); returns the count in use."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:  # pragma: no cover
+        n = os.cpu_count() or 1
+    return lib().oracle_set_num_threads(n)
 
 
 # --------------------------------------------------------------------------- dtypes

@@ -48,6 +48,18 @@ ORACLE_API int oracle_num_threads(void) {
 #endif
 }
 
+/* Sets the thread count of every later call (a launcher may have exported
+ * OMP_NUM_THREADS=1 before this library was loaded); returns the count in use. */
+ORACLE_API int oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
+
 /* ------------------------------------------------------------------------ */
 /* 16-bit float conversions.  raf.op.cast lowers to topi.cast               */
 /* (python/raf/_tvm_op/transform.py:444-450, declared at                    */

@@ -53,7 +53,9 @@ SIGNATURES = {
     "rafb200_sgd_list": (_i, [_vp, _f, _f, _f, _f, _vp]),
     "rafb200_lans_workspace_bytes": (_sz, [_vp]),
     "rafb200_lans": (_i, [_vp, _i, _vp, _f, _f, _f, _f, _i, _f, _i, _i, _i, _f, _vp, _sz, _vp]),
-    "rafb200_lans_schedule": (_i, [_i, _vp, _i, _i64, _i, _vp, _sz, _P(_sz)]),
+    "rafb200_lans_schedule": (_i, [_i, _vp, _i, _i, _i, _i64, _i, _vp, _sz, _P(_sz)]),
+    "rafb200_tensor_list_set_wait_limit": (_i, [_vp, _i]),
+    "rafb200_tensor_list_set_lans_items": (_i, [_vp, _vp, _sz]),
     "rafb200_lans_status": (_i, [_vp, _vp, _vp, _vp]),
     "rafb200_lans_tensor_static": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _i64, _i, _f, _f, _f, _f,
                                         _i, _f, _i, _i, _i, _f, _vp]),
@@ -92,6 +94,10 @@ SIGNATURES = {
     "rafb200_zero_arena_offsets": (_i, [_vp, _vp, _vp]),
     "rafb200_zero_status": (_i, [_vp]),
     "rafb200_zero_set_stage_mask": (_i, [_vp, _i]),
+    "rafb200_zero_set_wait_limit": (_i, [_vp, _i]),
+    "rafb200_zero_set_host_output": (_i, [_vp, _i]),
+    "rafb200_zero_declare_arena": (_i, [_vp, _vp, _sz]),
+    "rafb200_zero_shard_grad": (_i, [_vp, _i, _P(_vp)]),
     "rafb200_zero_launch_counts": (_i, [_vp, _P(_i), _P(_i)]),
     "rafb200_zero_set_update_blocks": (_i, [_vp, _i]),
     "rafb200_zero_step_host": (_i, [_vp, _P(Hyper), _i, _vp, _vp, _vp, _vp]),

@@ -58,8 +58,20 @@ struct Item {
 constexpr uint32_t kPhaseShift = 30;
 constexpr uint32_t kTensorMask = (1u << kPhaseShift) - 1u;
 
-constexpr int kChunkElems = 4096;  // elements per work item
+constexpr int kChunkElems = 4096;  // elements per work item of the SGD / Adam kernels
 constexpr int kBlockThreads = 256;
+
+// Work items of the LANS kernel.  The two top bits of Item::tensor_phase are the kind:
+//   A    sum of squares of a chunk of kLansAElems* gradient elements
+//   Bs   stage 1 of a chunk of kLansElems elements, sums only ("streamed")
+//   Cs   stage 1 again and stage 2 of the same chunk, stores everything
+//   BCp  both on a chunk that stays in shared memory in between ("parked")
+constexpr uint32_t kKindA = 0, kKindBs = 1, kKindCs = 2, kKindBCp = 3;
+constexpr int kLansElems = 1024;      // elements per Bs / Cs / BCp item = one shared-memory slot
+constexpr int kLansAElems16 = 7168;   // gradient elements per A item (what a slot holds), 16-bit g
+constexpr int kLansAElems32 = 4096;   // the same for fp32 gradients
+constexpr int kLansSlots16 = 15;      // slots per block (one block per SM): 15 x 14 KB, 16-bit g
+constexpr int kLansSlots32 = 13;      // 13 x 16 KB, fp32 g
 
 // Per-tensor control words of the LANS kernel (zeroed at the start of every call).
 // A norm word is "final" when its top bit is set: the publisher stores the bits of
@@ -74,20 +86,23 @@ constexpr int kBlockThreads = 256;
 // on the order in which blocks arrive; outside that range the order can show in the
 // 53rd bit, far below the fp32 rounding of the norm.
 struct LansCtl {
-  unsigned int arrived_a;  // chunks of phase A that have added their partial
-  unsigned int arrived_b;
-  unsigned int pad_[2];
+  // first 64-byte line: read-mostly, polled by the blocks that wait for the tensor
   unsigned int norm[4];    // ||g||, ||p||, ||update_m||, ||update_g||: bits | 0x80000000 once final
+  unsigned int pad0_[12];
+  // second line: updated with atomics by the blocks that add their parts
+  unsigned int arrived_a;  // gradient-norm items that have added their partial
+  unsigned int arrived_b;  // stage-1 chunks that have added theirs
+  unsigned int pad1_[6];
   double sumsq[4];         // running sums of squares of the same four quantities
 };
 constexpr unsigned int kNormValid = 0x80000000u;
-static_assert(sizeof(LansCtl) == 64, "LansCtl is 64 bytes");
+static_assert(sizeof(LansCtl) == 128, "LansCtl is two 64-byte lines");
 
 struct LansHeader {
   unsigned int ticket;   // next work item to hand out
   unsigned int error;    // 0, or the code of the bounded wait that expired
   unsigned int error_item;
-  unsigned int pad_;
+  unsigned int sched_iters;  // polling iterations of block 0's scheduler warp (a cheap health figure)
   float inv_bc1;         // reciprocal bias corrections when `step` lives on the device
   float inv_bc2;
 };
@@ -110,13 +125,14 @@ struct rafb200_tensor_list_s {
   // single-phase item table (SGD / Adam), tensor-major
   rafb200::Item* dev_items = nullptr;
   uint32_t n_items = 0;
-  // LANS schedule (three phases interleaved), rebuilt when tuned
-  rafb200::Item* dev_lans_items = nullptr;       // with the gradient-norm phase
-  uint32_t n_lans_items = 0;
-  rafb200::Item* dev_lans_items_nonorm = nullptr;  // normalize_grad == 0: no phase A
-  uint32_t n_lans_items_nonorm = 0;
-  int64_t window_elems = 0;
-  int slack_items = 0;
+  // LANS schedule, rebuilt when tuned: per-block item lists (offsets, then items)
+  uint32_t* dev_lans_lists = nullptr;         // with the gradient-norm items
+  uint32_t* dev_lans_lists_nonorm = nullptr;  // normalize_grad == 0: no A items
+  int64_t lead_elems = 0;   // how far the gradient-norm pass runs ahead
+  int gap_items = 0;        // items between a tensor's last parked item and its streamed updates
   int max_blocks = 0;
   int sm_count = 0;
+  int lans_grid = 0;        // blocks the LANS schedule was built for
+  bool custom_items = false;
+  uint64_t wait_ns = 2000000000ull;  // bound of every wait inside the LANS kernel
 };

@@ -1,27 +1,47 @@
-// raf.op.lans as ONE persistent kernel.
+// raf.op.lans as ONE persistent kernel that keeps a tensor on chip between its passes.
 //
 // The reference runs four norm reductions and two element-wise stages as about
 // fifty launches with a global dependency between them
-// (src/op/dialect/cuda/kernels/multi_tensor_lans.cu:401-450).  Here the work of
-// a call is a list of items (tensor, chunk, phase):
-//   phase A  sum of squares of the (scaled) gradient chunk            -> ||g||
-//   phase B  stage 1 on the chunk, results NOT stored: sums of squares of
-//            p, update_m, update_g                                     -> norms
-//   phase C  stage 1 again (same instructions, same bits), then stage 2 with the
-//            trust ratios; writes p, m, v and the model-dtype parameter copy.
-// Blocks draw items from a ticket counter in list order.  An item depends only
-// on items with smaller tickets (B of a tensor on all its A items, C on all its
-// B items), and a ticket is only ever held by a running block, so the bounded
-// waits below cannot deadlock whatever the number of resident blocks.  The
-// host orders the list so that a tensor's C items follow its B items closely:
-// the second read of g, p, m, v then comes out of L2 and HBM traffic approaches
-// one read and one write per array.
+// (src/op/dialect/cuda/kernels/multi_tensor_lans.cu:401-450) and moves about 68 bytes
+// per element.  The dependencies are real: stage 1 needs ||g|| of the whole tensor,
+// stage 2 needs ||p||, ||update_m|| and ||update_g|| of the whole tensor.  Here one
+// block per SM owns a set of shared-memory SLOTS of 1024 elements (g, p, m, v); a
+// slot is filled once by the TMA unit and keeps its data while the tensor-wide norm it
+// waits for is being completed by the other blocks:
+//   item A    (7168 / 4096 elements of g)  sum of squares of the scaled gradient -> ||g||.
+//             Runs a few million elements ahead of the rest, so ||g|| is final
+//             when a tensor's other items are drawn (the re-read of g comes from L2).
+//   item BCp  "parked": load g, p, m, v once; when ||g|| is final compute stage 1,
+//             store m and v, leave p, update_m, update_g in the slot and add the
+//             sums of squares to the tensor's accumulators; when the three norms are
+//             final, finish stage 2 from the slot and store p and the model-dtype copy.
+//             DRAM traffic: every array read once and written once.
+//   items Bs + Cs  "streamed", for the part of a tensor that exceeds what the grid can
+//             park (about two thirds of all slots): Bs computes the sums and stores
+//             nothing, Cs loads the chunk again, recomputes stage 1 with the same
+//             instructions (same bits) and stores everything.
+// The host fixes the order of the items and deals them out to the blocks in turn, so
+// every block runs its own list in order.  An item only ever waits for items that come
+// earlier in the global order, and a tensor's parked items never fill all the slots of a
+// block, so the bounded waits below cannot deadlock.
 //
-// Norms: every chunk adds its fp32 partial sums to per-tensor double-precision
-// accumulators; the block that adds the last chunk of a tensor takes the square
-// root and publishes the norm together with its "final" bit in one word.
+// Roles inside a block (608 threads):
+//   warps 0-15  four consumer groups of four warps; group q serves the slots s with
+//               s % 4 == q, so the threads that park a chunk are the ones that finish it.
+//               When an item's last operation is done, warp 0 of the group starts the next
+//               resolved item in the slot right away (bulk copies + first operation).
+//   warp 16     prefetcher: resolves the block's items ahead of their use (item ->
+//               descriptor -> the norms its first operation needs are final) into a ring.
+//   warp 17     parker: lane s polls the norm words of the tensor whose chunk is parked in
+//               slot s and queues the chunk's second half; lanes that wait for the same
+//               tensor share one load, so one round trip to L2 serves every slot.
+//   warp 18     publisher: collects the groups' partial sums, adds them (in double
+//               precision) to the tensor's accumulators, counts arrivals; the last
+//               arrival takes the square root and publishes the norm together with its
+//               "final" bit in one word.
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
@@ -33,13 +53,13 @@ namespace rafb200 {
 void bias_corrections(float beta1, float beta2, int step, int bias_correction, float* bc1,
                       float* bc2);
 
-constexpr int kPhaseA = 0, kPhaseB = 1, kPhaseC = 2;
-constexpr unsigned kErrWaitA = 1, kErrWaitB = 2, kErrRing = 3;
+constexpr uint32_t kOpA = 0, kOpB = 1, kOpBP = 2, kOpC = 3, kOpCP = 4, kOpEnd = 7;
+constexpr unsigned kErrWaitG = 1, kErrWaitN = 2, kErrRing = 3, kErrData = 4, kErrDone = 5;
 
 struct LansParams {
   const TensorDesc* descs;
+  const uint32_t* block_off;  // block b runs items[block_off[b] .. block_off[b + 1])
   const Item* items;
-  uint32_t nitems;
   LansHeader* hdr;
   LansCtl* ctl;
   LansStage1 s1;
@@ -47,8 +67,8 @@ struct LansParams {
   const float* step_dev;
   int bias_correction;
   uint64_t wait_ns;  // bound of every wait inside the kernel
+  void* trace;       // development aid, see LANS_TRACE
 };
-
 
 __device__ __forceinline__ uint64_t global_ns() {
   uint64_t t;
@@ -64,39 +84,20 @@ __device__ __forceinline__ uint4 ld_norms(const LansCtl* c) {
                : "l"(c->norm));
   return r;
 }
-// B needs ||g|| (word 0), C needs ||p||, ||update_m||, ||update_g|| (words 1-3; they
-// are published together with, or after, word 0).
-__device__ __forceinline__ bool norms_final(const uint4& n, bool phase_c) {
-  return phase_c ? ((n.y & n.z & n.w) >> 31) != 0 : (n.x >> 31) != 0;
+__device__ __forceinline__ uint4 ld_global_v4(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+__device__ __forceinline__ uint2 ld_global_v2(const void* p) {
+  uint2 r;
+  asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(p));
+  return r;
 }
 __device__ __forceinline__ float norm_value(unsigned bits) {
   return __uint_as_float(bits & ~kNormValid);
-}
-
-// Bounded wait until the norms a phase needs are final: gives up after `wait_ns`
-// nanoseconds (or as soon as another block has reported an error) and returns false.
-__device__ __forceinline__ bool wait_norms(const LansCtl* c, bool phase_c, uint4* out,
-                                           LansHeader* hdr, unsigned code, uint32_t ticket,
-                                           uint64_t wait_ns) {
-  uint4 n = ld_norms(c);
-  if (!norms_final(n, phase_c)) {
-    const uint64_t t0 = global_ns();
-    unsigned spins = 0, ns = 32;
-    do {
-      __nanosleep(ns);
-      if (ns < 1024) ns <<= 1;
-      if ((++spins & 15u) == 0) {
-        if (*reinterpret_cast<volatile unsigned*>(&hdr->error) != 0) return false;
-        if (global_ns() - t0 > wait_ns) {
-          if (atomicCAS(&hdr->error, 0u, code) == 0u) hdr->error_item = ticket;
-          return false;
-        }
-      }
-      n = ld_norms(c);
-    } while (!norms_final(n, phase_c));
-  }
-  *out = n;
-  return true;
 }
 
 // `step` as a 0-d fp32 device tensor (python/raf/optim/lans.py:239): the bias
@@ -129,6 +130,20 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+// Non-blocking: has the phase with this parity completed?
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Potentially blocking test: the hardware may suspend the thread for a short,
+// implementation-defined time while the phase is incomplete.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -139,30 +154,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
-}
-// Same, but the hardware may keep the thread suspended for up to `hint_ns` while the
-// phase is incomplete: a waiting warp then leaves the issue slots of its scheduler to
-// the warps that have work (here: the producer warp that everybody is waiting for).
-__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity,
-                                                      uint32_t hint_ns) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(hint_ns)
-      : "memory");
-  return ok != 0;
-}
-// Bounded: try_wait blocks for a short hardware-defined time per call; the loop
-// gives up after `wait_ns` nanoseconds and returns false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_t wait_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_ns();
-  while (!mbar_try_wait(bar, parity))
-    if (global_ns() - t0 > wait_ns) return false;
-  return true;
 }
 // One-dimensional bulk copy global -> this CTA's shared memory through the TMA
 // unit; completion is signalled on `bar` by byte count.  Both addresses are
@@ -175,135 +166,24 @@ __device__ __forceinline__ void tma_load_1d(uint32_t dst, const void* src, uint3
       "l"(src), "r"(bytes), "r"(bar), "l"(policy)
       : "memory");
 }
-
-// ---- kernel geometry ---------------------------------------------------------------
-// A work item is one chunk (kChunkElems elements) of one tensor in one phase.  It is
-// streamed as stages: the g, p, m and v slices of kStageElems elements (phases B, C),
-// or the whole chunk of g (phase A), copied into shared memory by TMA.  kStages stages
-// form a ring per block.  Three kinds of warps share a block:
-//   warps 0-7  consumers: wait for a stage, pull their elements into registers, give
-//              the slot back, compute, store p/m/v and the parameter copy (phase C) or
-//              accumulate sums of squares (A, B).  They never touch a block-wide
-//              barrier and never wait on global memory.
-//   warp 8     producer (one thread): draws tickets, resolves each item's dependency
-//              (bounded wait on the tensor's flag), fills the ring with bulk copies.
-//   warp 9     publisher: adds the consumers' per-warp partial sums of an item, writes
-//              them to global memory, counts arrivals per tensor and - for the last
-//              chunk of a tensor - adds all chunk partials in a fixed order, takes the
-//              square root and releases the tensor's flag.
-// Three blocks of two stages each are resident per SM (~170 KB of copies in flight per SM,
-// 24 consumer warps): measured 1-4 % faster than two blocks of three stages; deeper rings
-// did not help and stages of half the size cost 15 %.
-#ifndef RAFB200_LANS_STAGE_VECS
-#define RAFB200_LANS_STAGE_VECS 2
-#endif
-constexpr int kStageVecs = RAFB200_LANS_STAGE_VECS;  // 4-element vectors per consumer thread per B/C stage
-constexpr int kStageElems = kBlockThreads * 4 * kStageVecs;  // 2048
-#ifndef RAFB200_LANS_STAGES
-#define RAFB200_LANS_STAGES 2  // ring depth per block
-#endif
-#ifndef RAFB200_LANS_BLOCKS
-#define RAFB200_LANS_BLOCKS 3  // resident blocks per SM the ring and registers are sized for
-#endif
-constexpr int kStages = RAFB200_LANS_STAGES;
-constexpr int kConsumers = kBlockThreads;        // 256
-constexpr int kConsumerWarps = kConsumers / 32;  // 8
-constexpr int kLansThreads = kConsumers + 64;    // + producer warp + publisher warp
-constexpr int kRedSlots = 4;                     // ring of pending reductions
-constexpr uint32_t kTicketEnd = 0xffffffffu;
-constexpr uint32_t kRedEnd = 3u;
-static_assert(kChunkElems % kStageElems == 0, "a chunk is a whole number of stages");
-static_assert(kChunkElems % (kConsumers * kVec) == 0, "phase A walks a chunk in whole passes");
-
-struct __align__(16) StageMeta {
-  const void* g;  // global addresses of the stage's first element (stores, unaligned fallback)
-  float* p;
-  float* m;
-  float* v;
-  void* out;
-  uint32_t ticket;      // kTicketEnd: no more work (or a wait expired) - consumers leave
-  uint32_t n;           // elements in this stage
-  uint32_t nbulk;       // leading elements that were delivered into shared memory
-  uint32_t flags;       // bits 0-1 phase, bit 2 first stage of its item, bit 3 last stage
-  uint32_t tensor;
-  uint32_t part_index;  // slot of the item's partial sums
-  uint32_t nchunks;
-  uint32_t first_chunk;
-  float cs;             // gradient multiplier  grad_scale / (||g|| + eps)
-  float ratio_m;        // -beta1 * lr * ||p|| / ||update_m||   (phase C)
-  float ratio_g;        // -beta3 * lr * ||p|| / ||update_g||
-  uint32_t pad_;
-};
-static_assert(sizeof(StageMeta) == 96, "StageMeta is 96 bytes");
-
-struct __align__(16) RedSlot {
-  float val[3][kConsumerWarps];  // per consumer warp: sums of squares of this item
-  uint32_t phase;                // kPhaseA, kPhaseB or kRedEnd (consumers have left)
-  uint32_t tensor;
-  uint32_t part_index;
-  uint32_t nchunks;
-  uint32_t first_chunk;
-  uint32_t pad_[3];
-};
-static_assert(sizeof(RedSlot) == 128, "RedSlot is 128 bytes");
-
-// A stage that has been issued but whose norms were not final yet.
-struct __align__(16) PendStage {
-  uint32_t slot, phase, tensor, ticket;
-};
-
-// Metadata of one of the (up to four) tickets a block holds, filled by cp.async.
-struct __align__(16) ChainSlot {
-  uint32_t ticket;
-  uint32_t pad_;
-  Item item;
-  unsigned int norm[4];
-  TensorDesc d;
-};
-static_assert(sizeof(ChainSlot) == 96, "ChainSlot is 96 bytes");
-
-__device__ __forceinline__ void cp_async8(void* smem_dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(src)
-               : "memory");
+// Orders this thread's earlier generic-proxy accesses to shared memory before later
+// accesses of the async proxy (the next bulk copy into the same slot).
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
-__device__ __forceinline__ void cp_async16_ca(void* smem_dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(src)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async16_cg(void* smem_dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(src)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.wait_all;" ::: "memory");
-}
-
-template <typename GT>
-struct LansSmem {
-  static constexpr int kGBytes = kStageElems * sizeof(GT);
-  static constexpr int kFBytes = kStageElems * 4;
-  static constexpr int kStageBytes = kGBytes + 3 * kFBytes;
-  static_assert(kChunkElems * sizeof(GT) <= kStageBytes, "a phase-A stage holds a chunk of g");
-  static constexpr int kMetaOff = kStages * kStageBytes;
-  static constexpr int kRedOff = kMetaOff + kStages * (int)sizeof(StageMeta);
-  static constexpr int kChainOff = kRedOff + kRedSlots * (int)sizeof(RedSlot);
-  static constexpr int kPendOff = kChainOff + 4 * (int)sizeof(ChainSlot);
-  static constexpr int kBarOff = kPendOff + kStages * (int)sizeof(PendStage);
-  static constexpr int kTotal = kBarOff + (2 * kStages + 2 * kRedSlots) * 8;
-};
 
 // Bounded wait on an mbarrier that also gives up as soon as any block has reported an
-// error; a timeout reports kErrRing itself.
+// error; a timeout reports `code` itself.
 __device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, LansHeader* hdr,
-                                          uint32_t where, uint64_t wait_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
+                                          unsigned code, uint32_t where, uint64_t wait_ns) {
+  if (mbar_test(bar, parity)) return true;
   const uint64_t t0 = global_ns();
   unsigned polls = 0;
-  while (!mbar_try_wait_suspend(bar, parity, 4000u)) {
+  while (!mbar_try_wait(bar, parity)) {
     if ((++polls & 15u) == 0) {
       if (*reinterpret_cast<volatile unsigned*>(&hdr->error) != 0) return false;
       if (global_ns() - t0 > wait_ns) {
-        if (atomicCAS(&hdr->error, 0u, kErrRing) == 0u) hdr->error_item = where;
+        if (atomicCAS(&hdr->error, 0u, code) == 0u) hdr->error_item = where;
         return false;
       }
     }
@@ -311,30 +191,137 @@ __device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, LansHea
   return true;
 }
 
+#ifdef RAFB200_LANS_TRACE
+// Development aid (not built by default): block 0 logs (event, a, b, time) records behind
+// the control words of the workspace.
+#define LANS_TRACE(ev, a, b)                                                                      \
+  do {                                                                                            \
+    if (blockIdx.x == 0) {                                                                        \
+      unsigned* tb__ = reinterpret_cast<unsigned*>(P.trace);                                      \
+      const unsigned i__ = atomicAdd(tb__, 1u);                                                   \
+      if (i__ < 16000u) {                                                                         \
+        const uint64_t t__ = global_ns();                                                         \
+        tb__[4 + 4 * i__] = (ev);                                                                 \
+        tb__[5 + 4 * i__] = (a);                                                                  \
+        tb__[6 + 4 * i__] = (b);                                                                  \
+        tb__[7 + 4 * i__] = (unsigned)(t__ & 0xffffffffu);                                        \
+      }                                                                                           \
+    }                                                                                             \
+  } while (0)
+#else
+#define LANS_TRACE(ev, a, b) do { } while (0)
+#endif
+
+// ---- kernel geometry ---------------------------------------------------------------
+constexpr int kGroups = 4;                       // consumer groups per block
+constexpr int kGroupThreads = 128;               // four warps
+constexpr int kConsumerWarps = kGroups * 4;      // 16
+constexpr int kPrefWarp = kConsumerWarps;        // 16: resolves the block's items ahead of their use
+constexpr int kParkWarp = kConsumerWarps + 1;    // 17: finishes parked chunks, serves idle slots
+constexpr int kPubWarp = kConsumerWarps + 2;     // 18: adds partial sums to the tensors' accumulators
+constexpr int kLansThreads = (kConsumerWarps + 3) * 32;  // 608
+constexpr int kQueueDepth = 8;                   // >= 2 x slots per group: never overflows
+constexpr int kRing = 32;                        // resolved items waiting for a slot
+constexpr int kBVecs = kLansElems / (kGroupThreads * kVec);  // 2 vectors per thread per chunk
+static_assert(kBVecs * kGroupThreads * kVec == kLansElems, "a chunk is whole passes of a group");
+
+// A resolved work item: everything a group needs to run it.  The same 64 bytes serve as
+// ring entry and as the description of what a slot currently holds.
+struct __align__(16) SlotMeta {
+  const void* g;  // global addresses of the item's first element (stores, unaligned fallback)
+  float* p;
+  float* m;
+  float* v;
+  void* out;
+  uint32_t n_nbulk;    // low half: elements; high half: leading elements delivered by bulk copy
+  uint32_t tensor_op;  // bits 29..0 tensor, bits 31..30 first operation (kOpA, kOpB, kOpBP, kOpC)
+  uint32_t nparts;     // arrivals that complete the norm(s) this item adds to
+  float cs;            // gradient multiplier  grad_scale / (||g|| + eps)
+  float ratio_m;       // -beta1 * lr * ||p|| / ||update_m||   (kOpC)
+  float ratio_g;       // -beta3 * lr * ||p|| / ||update_g||
+};
+static_assert(sizeof(SlotMeta) == 64, "SlotMeta is 64 bytes");
+
+struct __align__(16) RedSlot {
+  float val[3][4];  // per warp of the group: sums of squares of this item
+  uint32_t tensor;
+  uint32_t is_a;    // 1: ||g||^2 ; 0: ||p||^2, ||update_m||^2, ||update_g||^2
+  uint32_t nparts;
+  uint32_t pad_;
+};
+static_assert(sizeof(RedSlot) == 64, "RedSlot is 64 bytes");
+
+// Block-wide control words in shared memory.
+struct LansCtrl {
+  int avail;            // ring entries published and not yet claimed
+  uint32_t head;        // next ring entry to claim
+  uint32_t consumed;    // ring entries copied out (their ring slot may be rewritten)
+  uint32_t done_items;  // items of this block that have finished
+  uint32_t free_mask;   // slots without an item that nobody is refilling
+  uint32_t parked_mask; // slots whose chunk waits for its tensor's norms
+  uint32_t tail[kGroups];
+  uint32_t item_cnt[16], pub_cnt[16], op_cnt[16];  // per slot: parities of its barriers
+};
+
+template <typename GT>
+struct LansGeo {
+  static constexpr int kGBytes = kLansElems * (int)sizeof(GT);
+  static constexpr int kFBytes = kLansElems * 4;
+  static constexpr int kSlotBytes = kGBytes + 3 * kFBytes;  // 14336 (16-bit g) | 16384 (fp32 g)
+  static constexpr int kAElems = sizeof(GT) == 2 ? kLansAElems16 : kLansAElems32;
+  static constexpr int kSlots = sizeof(GT) == 2 ? kLansSlots16 : kLansSlots32;
+  static_assert(kAElems * (int)sizeof(GT) <= kSlotBytes, "an A item fits a slot");
+  static_assert(kSlots <= 16 && kSlots <= kGroups * (kQueueDepth / 2), "per-slot tables hold 16");
+  static constexpr int kMetaOff = kSlots * kSlotBytes;
+  static constexpr int kRingOff = kMetaOff + kSlots * (int)sizeof(SlotMeta);
+  static constexpr int kRedOff = kRingOff + kRing * (int)sizeof(SlotMeta);
+  static constexpr int kQueueOff = kRedOff + kSlots * (int)sizeof(RedSlot);
+  static constexpr int kCtrlOff = kQueueOff + kGroups * kQueueDepth * 16;
+  static constexpr int kBarOff = (kCtrlOff + (int)sizeof(LansCtrl) + 15) & ~15;
+  // barriers: data, done, redfull, redempty per slot; queue entries; end of consumers
+  static constexpr int kNumBars = 4 * kSlots + kGroups * kQueueDepth + 1;
+  static constexpr int kTotal = kBarOff + kNumBars * 8;
+  static_assert(kTotal <= 232448, "fits the 227 KB of shared memory a block may use");
+};
+
+__device__ __forceinline__ uint32_t ld_shared_volatile(const uint32_t* p) {
+  return *reinterpret_cast<const volatile uint32_t*>(p);
+}
+
 template <typename GT, typename OT>
-__global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel(const LansParams P) {
+__global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams P) {
   extern __shared__ __align__(128) unsigned char smem[];
-  using L = LansSmem<GT>;
-  StageMeta* s_meta = reinterpret_cast<StageMeta*>(smem + L::kMetaOff);
+  using L = LansGeo<GT>;
+  constexpr int S = L::kSlots;
+  SlotMeta* s_meta = reinterpret_cast<SlotMeta*>(smem + L::kMetaOff);
+  SlotMeta* s_ring = reinterpret_cast<SlotMeta*>(smem + L::kRingOff);
   RedSlot* s_red = reinterpret_cast<RedSlot*>(smem + L::kRedOff);
-  const uint32_t bar_full = smem_u32(smem + L::kBarOff);
-  const uint32_t bar_empty = bar_full + kStages * 8;
-  const uint32_t red_full = bar_empty + kStages * 8;
-  const uint32_t red_empty = red_full + kRedSlots * 8;
+  uint4* s_queue = reinterpret_cast<uint4*>(smem + L::kQueueOff);
+  LansCtrl* ctrl = reinterpret_cast<LansCtrl*>(smem + L::kCtrlOff);
+  const uint32_t bar_data = smem_u32(smem + L::kBarOff);
+  const uint32_t bar_done = bar_data + S * 8;
+  const uint32_t bar_redfull = bar_done + S * 8;
+  const uint32_t bar_redempty = bar_redfull + S * 8;
+  const uint32_t bar_queue = bar_redempty + S * 8;
+  const uint32_t bar_end = bar_queue + kGroups * kQueueDepth * 8;
   const uint32_t data_base = smem_u32(smem);
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
+  const uint32_t list_lo = P.block_off[blockIdx.x], list_hi = P.block_off[blockIdx.x + 1];
+  const uint32_t n_list = list_hi - list_lo;
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar_full + 8 * s, 2);                // issue (+ transaction bytes) and resolve
-      mbar_init(bar_empty + 8 * s, kConsumerWarps);  // one arrive per consumer warp
+    for (int s = 0; s < S; ++s) {
+      mbar_init(bar_data + 8 * s, 1);      // whoever starts the item (+ transaction bytes)
+      mbar_init(bar_done + 8 * s, 4);      // the four warps of the slot's group
+      mbar_init(bar_redfull + 8 * s, 4);
+      mbar_init(bar_redempty + 8 * s, 1);  // the publisher
     }
-    for (int s = 0; s < kRedSlots; ++s) {
-      mbar_init(red_full + 8 * s, kConsumerWarps);
-      mbar_init(red_empty + 8 * s, 1);               // the publisher
-    }
+    for (int q = 0; q < kGroups * kQueueDepth; ++q) mbar_init(bar_queue + 8 * q, 1);
+    mbar_init(bar_end, kConsumerWarps);
+    memset(ctrl, 0, sizeof(LansCtrl));
+    ctrl->free_mask = (1u << S) - 1u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -344,594 +331,806 @@ __global__ void __launch_bounds__(kLansThreads, RAFB200_LANS_BLOCKS) lans_kernel
     s1.inv_bc1 = __ldcg(&P.hdr->inv_bc1);
     s1.inv_bc2 = __ldcg(&P.hdr->inv_bc2);
   }
+  const uint64_t pol_keep = make_policy_keep(), pol_stream = make_policy_stream();
 
-  if (warp == kConsumerWarps) {
-    // =============================== producer ===============================
-    // Resolving an item is a chain of dependent L2 round trips: ticket -> item ->
-    // descriptor and norms.  It is software-pipelined three items deep through shared
-    // memory with cp.async, so that no instruction ever waits for a load issued in
-    // the same iteration (a register pipeline cannot do that across lanes: the
-    // scoreboard tracks registers per warp):
-    //   iteration i   draws the ticket of item i+3,
-    //                 starts the copy of item i+2's table entry (its ticket was drawn
-    //                 in iteration i-1),
-    //                 starts the copies of item i+1's descriptor and norm words,
-    //                 issues item i, whose metadata landed during iteration i-1.
-    // A block thus holds at most four tickets and works them off in order.  Lane 0
-    // runs the chain; lanes 0-3 issue the four bulk copies of a stage (g, p, m, v).
-    const uint64_t pol_keep = make_policy_keep(), pol_stream = make_policy_stream();
-    uint32_t stage_ctr = 0;
-    int failed = 0;
-    ChainSlot* chain = reinterpret_cast<ChainSlot*>(smem + L::kChainOff);
-    auto fetch_item = [&](uint32_t seq) {  // lane 0; the slot's ticket has been stored
-      ChainSlot& c = chain[seq & 3u];
-      if (c.ticket < P.nitems) cp_async8(&c.item, P.items + c.ticket);
-    };
-    auto fetch_desc = [&](uint32_t seq) {  // lane 0; the slot's item has landed
-      ChainSlot& c = chain[seq & 3u];
-      if (c.ticket < P.nitems) {
-        const uint32_t t = c.item.tensor_phase & kTensorMask;
-        const char* src = reinterpret_cast<const char*>(P.descs + t);
-        char* dst = reinterpret_cast<char*>(&c.d);
-        cp_async16_ca(dst, src);
-        cp_async16_ca(dst + 16, src + 16);
-        cp_async16_ca(dst + 32, src + 32);
-        cp_async16_ca(dst + 48, src + 48);
-        cp_async16_cg(c.norm, P.ctl[t].norm);  // L2 copy: the publisher may just have written it
-      }
-    };
-    if (lane == 0) {  // prologue: items 0, 1, 2
-      chain[0].ticket = atomicAdd(&P.hdr->ticket, 1u);
-      chain[1].ticket = atomicAdd(&P.hdr->ticket, 1u);
-      chain[2].ticket = atomicAdd(&P.hdr->ticket, 1u);
-      fetch_item(0);
-      fetch_item(1);
-      cp_async_wait_all();
-      fetch_desc(0);
-      cp_async_wait_all();
+  // Hands one entry of a group's queue to that group.  Called by a single thread.
+  auto push_op = [&](uint32_t slot, uint32_t op, uint32_t dpar, uint32_t rpar, float cs, float rm, float rg) {
+    const uint32_t grp = slot & 3u;
+    const uint32_t opar = atomicAdd(&ctrl->op_cnt[slot], 1u) & 1u;
+    const uint32_t tail = atomicAdd(&ctrl->tail[grp], 1u);
+    const uint32_t qi = grp * kQueueDepth + (tail % kQueueDepth);
+    s_queue[qi] = make_uint4(op | (slot << 3) | (dpar << 8) | (rpar << 9) | (opar << 10), __float_as_uint(cs),
+                             __float_as_uint(rm), __float_as_uint(rg));
+    mbar_arrive(bar_queue + 8 * qi);
+  };
+  // Claims the oldest published ring entry for the (empty) slot `slot`: copies it into the
+  // slot's description, starts the bulk copies and queues the item's first operation.
+  // Returns false when the ring is empty.  Called by a single thread that owns the slot.
+  auto start_next = [&](uint32_t slot) -> bool {
+    if (atomicSub(&ctrl->avail, 1) <= 0) {
+      atomicAdd(&ctrl->avail, 1);
+      return false;
     }
-    __syncwarp();
-
-    // One iteration.  The ticket atomic is issued by lane 1 at the top and its result
-    // is only touched (stored to shared memory) at the bottom, after the stages of
-    // item `seq` have been issued: nothing waits for its round trip.
-    // Issue and resolve are decoupled.  The bulk copies of a stage do not depend on the
-    // tensor's norms, only the consumers' arithmetic does, so a stage is ISSUED (first
-    // arrival on its full barrier, plus the copies' bytes) as soon as a ring slot is
-    // free, and RESOLVED (multiplier and trust ratios written into its metadata, second
-    // arrival) once the norms it needs are final.  A stage whose norms were already
-    // final when the item's metadata was fetched is resolved on the spot; the others
-    // queue up - at most kStages of them - and the producer only blocks on a norm when
-    // it has no free slot left to fill.  While it waits, data keeps streaming in.
-    PendStage* pend = reinterpret_cast<PendStage*>(smem + L::kPendOff);
-    uint32_t pend_head = 0, pend_count = 0;
-    // last norms seen final, per (tensor, phase C?) - lane 0 only
-    uint32_t known_t = kTicketEnd;
-    uint4 known_nrm = make_uint4(0, 0, 0, 0);
-
-    auto ratios = [&](uint32_t phase, const uint4& nrm, float* cs, float* rm, float* rg) {
-      *cs = s1.gscale;
-      *rm = 0.f;
-      *rg = 0.f;
-      if (phase != kPhaseA) *cs = s1.grad_multiplier(norm_value(nrm.x));
-      if (phase == kPhaseC) {  // multi_tensor_lans.cu:347-353
-        const float pn = norm_value(nrm.y), umn = norm_value(nrm.z), ugn = norm_value(nrm.w);
-        float a = (umn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, umn)) : P.lr;
-        float b2 = (ugn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, ugn)) : P.lr;
-        *rm = -mul(a, s1.beta1);
-        *rg = -mul(b2, s1.beta3);
+    const uint32_t h = atomicAdd(&ctrl->head, 1u) % kRing;
+    __threadfence_block();
+    const uint4* src = reinterpret_cast<const uint4*>(&s_ring[h]);
+    uint4* dst = reinterpret_cast<uint4*>(&s_meta[slot]);
+    const uint4 e0 = src[0], e1 = src[1], e2 = src[2], e3 = src[3];
+    dst[0] = e0;
+    dst[1] = e1;
+    dst[2] = e2;
+    dst[3] = e3;
+    __threadfence_block();
+    atomicAdd(&ctrl->consumed, 1u);
+    const uint32_t op = e2.w >> 30, nbulk = e2.z >> 16;
+    const uint32_t dpar = atomicAdd(&ctrl->item_cnt[slot], 1u) & 1u;
+    const uint32_t my_data = bar_data + 8 * slot;
+    if (nbulk > 0) {
+      const char* gsrc = reinterpret_cast<const char*>(((uint64_t)e0.y << 32) | e0.x);
+      const char* psrc = reinterpret_cast<const char*>(((uint64_t)e0.w << 32) | e0.z);
+      const char* msrc = reinterpret_cast<const char*>(((uint64_t)e1.y << 32) | e1.x);
+      const char* vsrc = reinterpret_cast<const char*>(((uint64_t)e1.w << 32) | e1.z);
+      const uint32_t gb = nbulk * (uint32_t)sizeof(GT), fb = nbulk * 4u;
+      const uint32_t dstaddr = data_base + slot * L::kSlotBytes;
+      if (op == kOpA) {
+        mbar_arrive_expect_tx(my_data, gb);
+        tma_load_1d(dstaddr, gsrc, gb, my_data, pol_keep);  // stage 1 reads it again soon
+      } else {
+        mbar_arrive_expect_tx(my_data, gb + 3u * fb);
+        tma_load_1d(dstaddr, gsrc, gb, my_data, pol_stream);
+        tma_load_1d(dstaddr + L::kGBytes, psrc, fb, my_data, pol_stream);
+        tma_load_1d(dstaddr + L::kGBytes + L::kFBytes, msrc, fb, my_data, pol_stream);
+        tma_load_1d(dstaddr + L::kGBytes + 2 * L::kFBytes, vsrc, fb, my_data, pol_stream);
       }
-    };
-    auto needs_norms = [&](uint32_t phase) {
-      return (phase == kPhaseB && s1.normalize) || phase == kPhaseC;
-    };
-    // lane 0: second arrival of stage `slot` with the final multipliers
-    auto resolve_stage = [&](uint32_t slot, uint32_t phase, const uint4& nrm) {
-      float cs, rm, rg;
-      ratios(phase, nrm, &cs, &rm, &rg);
-      StageMeta& mt = s_meta[slot];
-      mt.cs = cs;
-      mt.ratio_m = rm;
-      mt.ratio_g = rg;
-      mbar_arrive(bar_full + 8 * slot);
-    };
-    // lane 0: resolve the oldest pending stage, waiting (bounded) for its norms if need be,
-    // then every following pending stage that the same norms settle.
-    auto resolve_oldest = [&]() -> int {
-      int bad = 0;
-      bool waited = false;
-      while (pend_count > 0) {
-        const PendStage ps = pend[pend_head];
-        const bool phase_c = ps.phase == kPhaseC;
-        const bool settled = !needs_norms(ps.phase) ||
-                             (known_t == ps.tensor && norms_final(known_nrm, phase_c));
-        if (!settled) {
-          if (waited) break;  // one blocking wait per call; the rest stays queued
-          uint4 nrm;
-          if (!wait_norms(P.ctl + ps.tensor, phase_c, &nrm, P.hdr, phase_c ? kErrWaitB : kErrWaitA,
-                          ps.ticket, P.wait_ns)) {
-            bad = 1;
-            break;
-          }
-          known_t = ps.tensor;
-          known_nrm = nrm;
-          waited = true;
+    } else {
+      mbar_arrive(my_data);
+    }
+    uint32_t rpar = 0;
+    if (op != kOpC) rpar = atomicAdd(&ctrl->pub_cnt[slot], 1u) & 1u;
+    LANS_TRACE(1u, slot, op);
+    push_op(slot, op, dpar, rpar, __uint_as_float(e3.y), __uint_as_float(e3.z), __uint_as_float(e3.w));
+    return true;
+  };
+
+  if (warp == kPrefWarp) {
+    // =============================== prefetcher ===============================
+    // Lane j resolves the entries j, j + 32, ... of the block's list: item -> descriptor of
+    // its tensor (kept while the tensor stays the same) -> the norms the item's first
+    // operation needs, final -> ring.  Entries are published in list order.
+    enum : uint32_t { F_ITEM, F_DESC, F_NORM, F_WRITE, F_PUB, F_DONE };
+    uint32_t e = (uint32_t)lane;
+    uint32_t st = e < n_list ? (uint32_t)F_ITEM : (uint32_t)F_DONE;
+    uint32_t tp = 0, chunk = 0, my_t = 0xffffffffu, pub_next = 0;
+    uint4 d0 = make_uint4(0, 0, 0, 0), d1 = d0, d2 = d0, d3 = d0, nrm = d0;
+    bool have_g = false, have_n = false;
+    float cs = s1.gscale, rm = 0.f, rg = 0.f;
+    uint64_t t_enter = 0;
+    const bool normalize = s1.normalize != 0;
+    int failed = 0;
+    for (uint32_t iter = 1;; ++iter) {
+      const uint32_t st_in = st;
+      // ---- global requests of this iteration, all issued before any is used ----
+      uint2 it = make_uint2(0, 0);
+      if (st_in == F_ITEM) it = ld_global_v2(P.items + list_lo + e);
+      if (st_in == F_DESC) {
+        const char* src = reinterpret_cast<const char*>(P.descs + my_t);
+        d0 = ld_global_v4(src);
+        d1 = ld_global_v4(src + 16);
+        d2 = ld_global_v4(src + 32);
+        d3 = ld_global_v4(src + 48);
+      }
+      const bool poll = st_in == F_DESC || st_in == F_NORM;
+      // lanes that wait for the same tensor share one load of its norm words
+      const unsigned same_t = __match_any_sync(0xffffffffu, poll ? my_t : (0x80000000u | (uint32_t)lane));
+      const int poll_leader = __ffs(same_t) - 1;
+      uint4 nrm_new = make_uint4(0, 0, 0, 0);
+      if (poll && poll_leader == lane) nrm_new = ld_norms(P.ctl + my_t);
+      // ---- consume ----
+      nrm_new.x = __shfl_sync(0xffffffffu, nrm_new.x, poll_leader);
+      nrm_new.y = __shfl_sync(0xffffffffu, nrm_new.y, poll_leader);
+      nrm_new.z = __shfl_sync(0xffffffffu, nrm_new.z, poll_leader);
+      nrm_new.w = __shfl_sync(0xffffffffu, nrm_new.w, poll_leader);
+      if (poll) {
+        nrm = nrm_new;
+        if (!have_g && (nrm.x >> 31)) {
+          have_g = true;
+          cs = s1.grad_multiplier(norm_value(nrm.x));
         }
-        resolve_stage(ps.slot, ps.phase, known_nrm);
-        pend_head = (pend_head + 1) % kStages;
-        --pend_count;
+        if (!have_n && ((nrm.y & nrm.z & nrm.w) >> 31)) {  // multi_tensor_lans.cu:347-353
+          have_n = true;
+          const float pn = norm_value(nrm.y), umn = norm_value(nrm.z), ugn = norm_value(nrm.w);
+          const float a = (umn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, umn)) : P.lr;
+          const float b2 = (ugn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, ugn)) : P.lr;
+          rm = -mul(a, s1.beta1);
+          rg = -mul(b2, s1.beta3);
+        }
       }
-      return bad;
-    };
+      if (st_in == F_ITEM) {
+        tp = it.x;
+        chunk = it.y;
+        const uint32_t t = tp & kTensorMask;
+        if (t != my_t) {
+          my_t = t;
+          have_g = have_n = false;
+          cs = s1.gscale;
+          st = F_DESC;
+        } else {
+          st = F_NORM;
+        }
+      } else if (st_in == F_DESC) {
+        st = F_NORM;
+      }
+      const uint32_t kind = tp >> kPhaseShift;
+      if (st == F_NORM) {
+        const bool need_g = normalize && kind != kKindA;
+        const bool need_n = kind == kKindCs;
+        if ((!need_g || have_g) && (!need_n || have_n)) st = F_WRITE;
+      }
+      if (st == F_WRITE && e < ld_shared_volatile(&ctrl->consumed) + kRing) {
+        const char* dg = reinterpret_cast<const char*>(((uint64_t)d0.y << 32) | d0.x);
+        float* dp = reinterpret_cast<float*>(((uint64_t)d0.w << 32) | d0.z);
+        float* dm = reinterpret_cast<float*>(((uint64_t)d1.y << 32) | d1.x);
+        float* dv = reinterpret_cast<float*>(((uint64_t)d1.w << 32) | d1.z);
+        char* dout = reinterpret_cast<char*>(((uint64_t)d2.y << 32) | d2.x);
+        const int64_t numel = (int64_t)(((uint64_t)d2.w << 32) | d2.z);
+        const uint32_t flags = d3.z;
+        const int per = (kind == kKindA) ? L::kAElems : kLansElems;
+        const int64_t start = (int64_t)chunk * per;
+        const int64_t left = numel - start;
+        const int n = left < per ? (int)left : per;
+        constexpr int gran = 16 / (int)sizeof(GT);  // elements per 16 bytes of gradient
+        const int nbulk = (flags & kFlagBulk) ? (n / gran) * gran : 0;
+        const uint32_t op = kind == kKindA ? kOpA : kind == kKindBs ? kOpB : kind == kKindCs ? kOpC : kOpBP;
+        SlotMeta& mt = s_ring[e % kRing];
+        mt.g = dg + start * (int64_t)sizeof(GT);
+        mt.p = dp + start;
+        mt.m = dm + start;
+        mt.v = dv + start;
+        mt.out = dout ? dout + start * (int64_t)sizeof(OT) : nullptr;
+        mt.n_nbulk = (uint32_t)n | ((uint32_t)nbulk << 16);
+        mt.tensor_op = my_t | (op << 30);
+        mt.nparts = (uint32_t)((numel + per - 1) / per);
+        mt.cs = (op == kOpA) ? s1.gscale : cs;
+        mt.ratio_m = rm;
+        mt.ratio_g = rg;
+        st = F_PUB;
+      }
+      // ---- publish in list order ----
+      const unsigned written = __ballot_sync(0xffffffffu, st == F_PUB);
+      const uint32_t l0 = pub_next & 31u;
+      const unsigned rot = __funnelshift_r(written, written, l0);  // bit i = lane (l0 + i) % 32
+      const int npub = (rot == 0xffffffffu) ? 32 : __ffs(~rot) - 1;
+      if (npub > 0) {
+        __threadfence_block();
+        if (lane == 0) LANS_TRACE(7u, (uint32_t)npub, pub_next);
+        if (lane == 0) atomicAdd(&ctrl->avail, npub);
+        if ((((uint32_t)lane - l0) & 31u) < (uint32_t)npub) {
+          e += kRing;
+          st = e < n_list ? (uint32_t)F_ITEM : (uint32_t)F_DONE;
+        }
+        pub_next += (uint32_t)npub;
+      }
+      if (st != st_in) t_enter = 0;
+      // ---- bounded waits, errors, end ----
+      if ((iter & 31u) == 0) {
+        const uint64_t now = global_ns();
+        if (st == F_NORM) {
+          if (t_enter == 0) {
+            t_enter = now;
+          } else if (now - t_enter > P.wait_ns) {
+            if (atomicCAS(&P.hdr->error, 0u, kind == kKindCs ? kErrWaitN : kErrWaitG) == 0u)
+              P.hdr->error_item = list_lo + e;
+          }
+        }
+        if (*reinterpret_cast<volatile unsigned*>(&P.hdr->error) != 0) failed = 1;
+      }
+      if (__all_sync(0xffffffffu, st == F_DONE) || __any_sync(0xffffffffu, failed != 0)) break;
+      if (npub == 0 && !__any_sync(0xffffffffu, st != st_in)) __nanosleep(100);
+    }
+    if (blockIdx.x == 0 && lane == 0) P.hdr->sched_iters = pub_next;
+    return;
+  }
 
-    auto iteration = [&](uint32_t seq) -> bool {
-      uint32_t drawn = 0;
-      if (lane == 1) drawn = atomicAdd(&P.hdr->ticket, 1u);  // item seq + 3
-      {
-      if (lane == 0) {
-        cp_async_wait_all();  // copies of the previous iteration
-        fetch_item(seq + 2);  // its ticket was stored at the bottom of the previous iteration
-        fetch_desc(seq + 1);
+  if (warp == kParkWarp) {
+    // ================================= parker =================================
+    // Lane s looks after slot s: finishes its parked chunk when the tensor's norms are final,
+    // and refills it when it ran empty while the ring had nothing to offer.
+    const bool active = lane < S;
+    const uint32_t bit = 1u << lane;
+    uint64_t t_parked = 0;
+    int failed = 0;
+    for (uint32_t iter = 1;; ++iter) {
+      const uint32_t parked_mask = ld_shared_volatile(&ctrl->parked_mask);
+      const bool parked = active && (parked_mask & bit);
+      uint32_t my_t = 0x80000000u | (uint32_t)lane;
+      if (parked) my_t = s_meta[lane].tensor_op & kTensorMask;
+      const unsigned same_t = __match_any_sync(0xffffffffu, my_t);
+      const int leader = __ffs(same_t) - 1;
+      uint4 nrm = make_uint4(0, 0, 0, 0);
+      if (parked && leader == lane) nrm = ld_norms(P.ctl + my_t);
+      nrm.y = __shfl_sync(0xffffffffu, nrm.y, leader);
+      nrm.z = __shfl_sync(0xffffffffu, nrm.z, leader);
+      nrm.w = __shfl_sync(0xffffffffu, nrm.w, leader);
+      if (parked && ((nrm.y & nrm.z & nrm.w) >> 31)) {  // multi_tensor_lans.cu:347-353
+        const float pn = norm_value(nrm.y), umn = norm_value(nrm.z), ugn = norm_value(nrm.w);
+        const float a = (umn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, umn)) : P.lr;
+        const float b2 = (ugn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, ugn)) : P.lr;
+        atomicAnd(&ctrl->parked_mask, ~bit);
+        LANS_TRACE(6u, (uint32_t)lane, my_t);
+        push_op((uint32_t)lane, kOpCP, 0, 0, 0.f, -mul(a, s1.beta1), -mul(b2, s1.beta3));
+        t_parked = 0;
+      }
+      if (active && (ld_shared_volatile(&ctrl->free_mask) & bit) && !failed) {
+        atomicAnd(&ctrl->free_mask, ~bit);
+        if (!start_next((uint32_t)lane)) atomicOr(&ctrl->free_mask, bit);
       }
       __syncwarp();
-        }
-      auto finish = [&]() {
-        if (lane == 1) chain[(seq + 3u) & 3u].ticket = drawn;
-        __syncwarp();
-      };
-      const ChainSlot& c = chain[seq & 3u];
-      const uint32_t ticket = c.ticket;
-      if (ticket >= P.nitems) {
-        finish();
-        return false;
-      }
-      const uint32_t tp = c.item.tensor_phase, chunk = c.item.chunk;
-      const TensorDesc d = c.d;
-      const uint4 nrm0 = *reinterpret_cast<const uint4*>(c.norm);  // as of one iteration ago
-      const uint32_t t = tp & kTensorMask;
-      const uint32_t phase = tp >> kPhaseShift;
-      const bool want = needs_norms(phase);
-      const bool have = !want || norms_final(nrm0, phase == kPhaseC);
-      if (lane == 0 && want && have) {
-        known_t = t;
-        known_nrm = nrm0;
-      }
-
-      const int64_t start = (int64_t)chunk * kChunkElems;
-      const int64_t left = d.numel - start;
-      const int len = left < kChunkElems ? (int)left : kChunkElems;
-      const bool bulk_ok = (d.flags & kFlagBulk) != 0;
-      const uint64_t pol = (phase == kPhaseC) ? pol_stream : pol_keep;
-      const int stage_cap = (phase == kPhaseA) ? kChunkElems : kStageElems;
-      const int gran = 16 / (int)sizeof(GT);  // elements per 16 bytes of gradient
-      // lane q (0..3) copies array q of every stage: g, p, m, v
-      const char* my_src = lane == 0   ? static_cast<const char*>(d.g)
-                           : lane == 1 ? reinterpret_cast<const char*>(d.p)
-                           : lane == 2 ? reinterpret_cast<const char*>(d.m)
-                                       : reinterpret_cast<const char*>(d.v);
-      const uint32_t my_esize = lane == 0 ? (uint32_t)sizeof(GT) : 4u;
-      const uint32_t my_dst_off = lane == 0 ? 0u : (uint32_t)(L::kGBytes + (lane - 1) * L::kFBytes);
-      const bool my_copy = lane < (phase == kPhaseA ? 1 : 4);
-      for (int off = 0; off < len; off += stage_cap) {
-        const uint32_t slot = stage_ctr % kStages;
-        const uint32_t use = stage_ctr / kStages;
-        // A free slot: take it.  None free: settle pending stages first (their consumers
-        // are what frees slots), and only with nothing pending wait for the consumers.
-        if (lane == 0) {
-          const uint32_t eb = bar_empty + 8 * slot, par = (use & 1u) ^ 1u;
-          while (!failed && !mbar_try_wait(eb, par)) {
-            if (pend_count > 0) {
-              failed = resolve_oldest();
-            } else {
-              failed = ring_wait(eb, par, P.hdr, ticket, P.wait_ns) ? 0 : 1;
-              break;
-            }
+      const bool all_done = ld_shared_volatile(&ctrl->done_items) >= n_list;
+      if ((iter & 31u) == 0) {
+        const uint64_t now = global_ns();
+        if (parked) {
+          if (t_parked == 0) {
+            t_parked = now;
+          } else if (now - t_parked > P.wait_ns) {
+            if (atomicCAS(&P.hdr->error, 0u, kErrWaitN) == 0u) P.hdr->error_item = 0x80000000u | my_t;
           }
         }
-        failed = __shfl_sync(0xffffffffu, failed, 0);
-        if (failed) {
-          finish();
-          return false;
-        }
-        const int n = (len - off) < stage_cap ? (len - off) : stage_cap;
-        const int nbulk = bulk_ok ? (n / gran) * gran : 0;
-        const uint32_t full = bar_full + 8 * slot;
-        {
-        if (lane == 0) {
-          StageMeta& mt = s_meta[slot];
-          const int64_t e = start + off;
-          mt.g = static_cast<const char*>(d.g) + e * (int64_t)sizeof(GT);
-          mt.p = d.p + e;
-          mt.m = d.m + e;
-          mt.v = d.v + e;
-          mt.out = d.out ? static_cast<char*>(d.out) + e * (int64_t)sizeof(OT) : nullptr;
-          mt.ticket = ticket;
-          mt.n = (uint32_t)n;
-          mt.nbulk = (uint32_t)nbulk;
-          mt.flags = phase | (off == 0 ? 4u : 0u) | (off + stage_cap >= len ? 8u : 0u);
-          mt.tensor = t;
-          mt.part_index = d.first_chunk + chunk;
-          mt.nchunks = d.nchunks;
-          mt.first_chunk = d.first_chunk;
-          if (nbulk > 0) {
-            const uint32_t gb = (uint32_t)nbulk * (uint32_t)sizeof(GT), fb = (uint32_t)nbulk * 4u;
-            mbar_arrive_expect_tx(full, phase == kPhaseA ? gb : gb + 3u * fb);  // arrival 1 of 2
-          } else {
-            mbar_arrive(full);
-          }
-          // arrival 2 of 2: now if the norms are known, later otherwise
-          const bool settled = !want || (known_t == t && norms_final(known_nrm, phase == kPhaseC));
-          if (settled && pend_count == 0) {
-            resolve_stage(slot, phase, known_nrm);
-          } else {
-            PendStage& ps = pend[(pend_head + pend_count) % kStages];
-            ps.slot = slot;
-            ps.phase = phase;
-            ps.tensor = t;
-            ps.ticket = ticket;
-            ++pend_count;
-          }
-        }
-        __syncwarp();
-        }
-        {
-          if (my_copy && nbulk > 0)
-            tma_load_1d(data_base + slot * L::kStageBytes + my_dst_off,
-                        my_src + (start + off) * (int64_t)my_esize, (uint32_t)nbulk * my_esize, full,
-                        pol);
-          __syncwarp();
-        }
-        ++stage_ctr;
+        if (*reinterpret_cast<volatile unsigned*>(&P.hdr->error) != 0) failed = 1;
       }
-      finish();
-      return true;
-    };
-    for (uint32_t seq = 0; iteration(seq); ++seq) {
+      if (all_done || __any_sync(0xffffffffu, failed != 0)) break;
+      if (parked_mask == 0) __nanosleep(200);
     }
-    // settle what is still pending (each wait is bounded)
-    if (lane == 0) {
-      while (!failed && pend_count > 0) failed = resolve_oldest();
+    // every group gets its end marker; then nothing of this block may still be in flight
+    if (lane < kGroups) {
+      const uint32_t tail = atomicAdd(&ctrl->tail[lane], 1u);
+      const uint32_t qi = (uint32_t)lane * kQueueDepth + (tail % kQueueDepth);
+      s_queue[qi] = make_uint4(kOpEnd, 0, 0, 0);
+      mbar_arrive(bar_queue + 8 * qi);
     }
-    failed = __shfl_sync(0xffffffffu, failed, 0);
-    if (lane == 0) cp_async_wait_all();  // nothing of this thread may still be in flight
-    // Terminator.  Every stage published before it is consumed (its copies have
-    // landed) before the consumers see it, so nothing is in flight when they leave.
-    if (lane == 0) {
-      const uint32_t slot = stage_ctr % kStages;
-      if (ring_wait(bar_empty + 8 * slot, ((stage_ctr / kStages) & 1u) ^ 1u, P.hdr, kTicketEnd,
-                    P.wait_ns)) {
-        s_meta[slot].ticket = kTicketEnd;
-        mbar_arrive(bar_full + 8 * slot);
-        mbar_arrive(bar_full + 8 * slot);
-      }
+    ring_wait(bar_end, 0, P.hdr, kErrRing, 0x3000u, P.wait_ns);
+    if (active) {
+      const uint32_t items = ld_shared_volatile(&ctrl->item_cnt[lane]);
+      if (items > 0) ring_wait(bar_data + 8 * lane, (items - 1u) & 1u, P.hdr, kErrData, (uint32_t)lane, P.wait_ns);
     }
     return;
   }
 
-  if (warp == kConsumerWarps + 1) {
+  if (warp == kPubWarp) {
     // =============================== publisher ===============================
-    for (uint32_t r = 0;; ++r) {
-      const uint32_t buf = r % kRedSlots, use = r / kRedSlots;
-      if (!ring_wait(red_full + 8 * buf, use & 1u, P.hdr, r, P.wait_ns)) return;
-      const RedSlot& rs = s_red[buf];
-      const uint32_t phase = rs.phase;
-      if (phase == kRedEnd) return;
-      const uint32_t t = rs.tensor, nchunks = rs.nchunks;
-      const int nq = (phase == kPhaseA) ? 1 : 3;
-      float sum = 0.f;
-      if (lane < nq) {
+    const bool active = lane < S;
+    uint32_t n_seen = 0;  // publications of this lane's slot read so far
+    for (;;) {
+      const bool end = mbar_test(bar_end, 0);  // every consumer warp has left (checked first)
+      const bool ready = active && mbar_test(bar_redfull + 8 * lane, n_seen & 1u);
+      double q0 = 0.0, q1 = 0.0, q2 = 0.0;
+      uint32_t key = 0xffffffffu, nparts = 0;
+      if (ready) {
+        const RedSlot& rs = s_red[lane];
+        q0 = (double)rs.val[0][0] + (double)rs.val[0][1] + (double)rs.val[0][2] + (double)rs.val[0][3];
+        q1 = (double)rs.val[1][0] + (double)rs.val[1][1] + (double)rs.val[1][2] + (double)rs.val[1][3];
+        q2 = (double)rs.val[2][0] + (double)rs.val[2][1] + (double)rs.val[2][2] + (double)rs.val[2][3];
+        key = (rs.tensor << 1) | (rs.is_a & 1u);
+        nparts = rs.nparts;
+        mbar_arrive(bar_redempty + 8 * lane);  // the slot has been read
+        ++n_seen;
+      }
+      unsigned pending = __ballot_sync(0xffffffffu, ready);
+      if (pending == 0) {
+        if (end) break;
+        __nanosleep(64);
+        continue;
+      }
+      // Items of the same tensor and kind that completed since the last look go out as one
+      // update of the tensor's accumulators (the lowest of their lanes does it), and all such
+      // groups go out at the same time: one pair of round trips to L2 per look, however many
+      // tensors the block has chunks of.
+      if (lane == 0) LANS_TRACE(4u, pending, 0u);
+      const unsigned same = __match_any_sync(0xffffffffu, ready ? key : (0x80000000u | (uint32_t)lane));
+      const bool leads = ready && (__ffs(same) - 1) == lane;
+      double a0 = 0.0, a1 = 0.0, a2 = 0.0;
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; ++w) sum += rs.val[lane][w];
+      for (int l = 0; l < S; ++l) {
+        const double b0 = __shfl_sync(0xffffffffu, q0, l), b1 = __shfl_sync(0xffffffffu, q1, l),
+                     b2 = __shfl_sync(0xffffffffu, q2, l);
+        const double w = (double)((same >> l) & 1u);  // 1.0 for the lanes of this group, else 0.0
+        a0 = fma(b0, w, a0);
+        a1 = fma(b1, w, a1);
+        a2 = fma(b2, w, a2);
+      }
+      if (leads) {
+        const bool is_a = (key & 1u) != 0;
+        LansCtl* ctl = P.ctl + (key >> 1);
+        // A -> ||g||^2 ; B -> ||p||^2, ||update_m||^2, ||update_g||^2
+        if (is_a) {
+          atomicAdd(&ctl->sumsq[0], a0);
+        } else {
+          atomicAdd(&ctl->sumsq[1], a0);
+          atomicAdd(&ctl->sumsq[2], a1);
+          atomicAdd(&ctl->sumsq[3], a2);
+        }
+        __threadfence();
+        const unsigned cnt = (unsigned)__popc(same);
+        const unsigned old = atomicAdd(is_a ? &ctl->arrived_a : &ctl->arrived_b, cnt);
+        LANS_TRACE(5u, key, old + cnt == nparts);
+        if (old + cnt == nparts) {
+          // Every part of the tensor has been added: publish the norm(s), value and
+          // "final" bit in one word each.
+          __threadfence();
+          for (int w = is_a ? 0 : 1; w < (is_a ? 1 : 4); ++w) {
+            const double total = *reinterpret_cast<volatile double*>(&ctl->sumsq[w]);
+            *reinterpret_cast<volatile unsigned*>(&ctl->norm[w]) =
+                __float_as_uint(sqrtf((float)total)) | kNormValid;
+          }
+        }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(red_empty + 8 * buf);  // the slot has been read
-      // lane q owns quantity q: A -> ||g||^2 ; B -> ||p||^2, ||update_m||^2, ||update_g||^2
-      LansCtl* ctl = P.ctl + t;
-      const int word = (phase == kPhaseA) ? 0 : 1 + lane;
-      if (lane < nq) {
-        atomicAdd(&ctl->sumsq[word], (double)sum);
-        __threadfence();
-      }
-      __syncwarp();
-      unsigned is_last = 0;
-      if (lane == 0) {
-        const unsigned old = atomicAdd(phase == kPhaseA ? &ctl->arrived_a : &ctl->arrived_b, 1u);
-        is_last = (old + 1u == nchunks);
-      }
-      is_last = __shfl_sync(0xffffffffu, is_last, 0);
-      if (is_last && lane < nq) {
-        // Every chunk of the tensor has been added: publish the norm, value and
-        // "final" bit in one word.
-        __threadfence();
-        const double total = *reinterpret_cast<volatile double*>(&ctl->sumsq[word]);
-        *reinterpret_cast<volatile unsigned*>(&ctl->norm[word]) =
-            __float_as_uint(sqrtf((float)total)) | kNormValid;
-      }
     }
+    return;
   }
 
   // ================================ consumers ================================
-  // Thread `tid` owns, in every stage, the vectors of four elements at q*1024 + 4*tid:
-  // 16-byte shared-memory reads without bank conflicts, coalesced 16-byte stores.
-  // Lanes past the end of a ragged stage hold zeros, which add nothing to any sum.
+  // Thread `gtid` of a group owns, in every chunk, the vectors of four elements at
+  // q*512 + 4*gtid: 16-byte shared-memory accesses without bank conflicts, coalesced
+  // 16-byte stores.  Lanes past the end of a ragged chunk hold zeros, which add nothing
+  // to any sum.  One warp of the group (they take turns) also turns the slot over when an
+  // item's last operation is done: it starts the next item of the ring in it right away.
+  const int grp = warp >> 2, wig = warp & 3, gtid = tid & (kGroupThreads - 1);
   Policies pol;
   pol.init();
-  float acc[3] = {0.f, 0.f, 0.f};
-  uint32_t red_ctr = 0;
-  // Hands this warp's sums of the finished item (or the end marker) to the publisher.
-  auto hand_over = [&](uint32_t phase, uint32_t tensor, uint32_t part_index, uint32_t nchunks,
-                       uint32_t first_chunk) {
-    float v0 = 0.f, v1 = 0.f, v2 = 0.f;
-    if (phase != kRedEnd) v0 = warp_sum(acc[0]);
-    if (phase == kPhaseB) {
-      v1 = warp_sum(acc[1]);
-      v2 = warp_sum(acc[2]);
-    }
-    if (lane == 0) {
-      const uint32_t buf = red_ctr % kRedSlots, use = red_ctr / kRedSlots;
-      ring_wait(red_empty + 8 * buf, (use & 1u) ^ 1u, P.hdr, red_ctr, P.wait_ns);
-      RedSlot& rs = s_red[buf];
-      rs.val[0][warp] = v0;
-      rs.val[1][warp] = v1;
-      rs.val[2][warp] = v2;
-      if (warp == 0) {
-        rs.phase = phase;
-        rs.tensor = tensor;
-        rs.part_index = part_index;
-        rs.nchunks = nchunks;
-        rs.first_chunk = first_chunk;
-      }
-      mbar_arrive(red_full + 8 * buf);
-    }
-    ++red_ctr;
-  };
-
-  for (uint32_t stage_ctr = 0;; ++stage_ctr) {
-    const uint32_t slot = stage_ctr % kStages;
-    {
-    if (!ring_wait(bar_full + 8 * slot, (stage_ctr / kStages) & 1u, P.hdr, stage_ctr, P.wait_ns))
-      break;
-        }
-    const StageMeta& mt = s_meta[slot];
-    if (mt.ticket == kTicketEnd) break;
-    const uint32_t phase = mt.flags & 3u;
-    const bool first = (mt.flags & 4u) != 0, last = (mt.flags & 8u) != 0;
-    const int n = (int)mt.n, nbulk = (int)mt.nbulk;
+#ifdef RAFB200_LANS_TRACE
+  long long c_queue = 0, c_data = 0, c_op = 0, c_duty = 0, c_pub = 0, c_t = clock64(), c_n = 0;
+#define LANS_TICK(acc) do { const long long n__ = clock64(); acc += n__ - c_t; c_t = n__; } while (0)
+#else
+#define LANS_TICK(acc) do { } while (0)
+#endif
+  for (uint32_t i = 0;; ++i) {
+    const uint32_t qi = (uint32_t)grp * kQueueDepth + (i % kQueueDepth);
+    bool ok = ring_wait(bar_queue + 8 * qi, (i / kQueueDepth) & 1u, P.hdr, kErrRing, 0x1000u | (uint32_t)grp,
+                        P.wait_ns);
+    if (!__all_sync(0xffffffffu, ok)) break;  // every lane of the warp leaves, or none
+    LANS_TICK(c_queue);
+    const uint4 ent = s_queue[qi];
+    const uint32_t op = ent.x & 7u, slot = (ent.x >> 3) & 31u, dpar = (ent.x >> 8) & 1u, rpar = (ent.x >> 9) & 1u,
+                   opar = (ent.x >> 10) & 1u;
+    if (op == kOpEnd) break;
+    const float cs = __uint_as_float(ent.y), ratio_m = __uint_as_float(ent.z), ratio_g = __uint_as_float(ent.w);
+    const SlotMeta mt = s_meta[slot];
+    const int n = (int)(mt.n_nbulk & 0xffffu), nbulk = (int)(mt.n_nbulk >> 16);
     const GT* gg = static_cast<const GT*>(mt.g);
-    const uint32_t tensor = mt.tensor, part_index = mt.part_index, nchunks = mt.nchunks,
-                   first_chunk = mt.first_chunk;
-    const unsigned char* sbase = smem + slot * L::kStageBytes;
-    if (first) acc[0] = acc[1] = acc[2] = 0.f;
-
-    if (phase == kPhaseA) {
-      // The whole chunk of g sits in the stage: four vectors per thread.
-      constexpr int kPasses = kChunkElems / (kConsumers * kVec);
-      F4 rg[kPasses];
-#pragma unroll
-      for (int q = 0; q < kPasses; ++q) {
-        const int e = q * (kConsumers * kVec) + tid * kVec;
-        if (e < nbulk) {
-          rg[q] = Elem<GT>::smem4(sbase + e * sizeof(GT));
-        } else {
-#pragma unroll
-          for (int j = 0; j < kVec; ++j)
-            rg[q].x[j] = (e + j < n) ? Elem<GT>::to_f32(gg[e + j]) : 0.f;
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_empty + 8 * slot);  // values are in registers
-#pragma unroll
-      for (int q = 0; q < kPasses; ++q)
-#pragma unroll
-        for (int j = 0; j < kVec; ++j) {
-          const float x = rg[q].x[j] * s1.gscale;
-          acc[0] = fmaf(x, x, acc[0]);
-        }
-      if (last) hand_over(kPhaseA, tensor, part_index, nchunks, first_chunk);
-      continue;
-    }
-
-    // ---- phases B and C: g, p, m, v of kStageElems elements ----
     float* gp = mt.p;
     float* gm = mt.m;
     float* gv = mt.v;
     OT* gout = static_cast<OT*>(mt.out);
-    const float cs = mt.cs, ratio_m = mt.ratio_m, ratio_g = mt.ratio_g;
-    const bool whole = nbulk == kStageElems;  // the common case: nothing ragged or unaligned
-    F4 rg[kStageVecs], rp[kStageVecs], rm[kStageVecs], rv[kStageVecs];
-    int cnt[kStageVecs];
+    unsigned char* sbase = smem + slot * L::kSlotBytes;
+    const uint32_t my_done = bar_done + 8 * slot;
+    if (op != kOpCP) {  // first use of the slot's data: wait for the copies
+      ok = ring_wait(bar_data + 8 * slot, dpar, P.hdr, kErrData, slot, P.wait_ns);
+      if (!__all_sync(0xffffffffu, ok)) break;
+    }
+    float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f;
+    bool publishes = false;
+    LANS_TICK(c_data);
+
+    if (op == kOpA) {
+      constexpr int kPasses = L::kAElems / (kGroupThreads * kVec);
+#pragma unroll 2
+      for (int q = 0; q < kPasses; ++q) {
+        const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+        F4 r;
+        if (e < nbulk) {
+          r = Elem<GT>::smem4(sbase + e * sizeof(GT));
+        } else {
 #pragma unroll
-    for (int q = 0; q < kStageVecs; ++q) {
-      const int e = q * (kConsumers * kVec) + tid * kVec;
-      if (whole || e < nbulk) {
-        cnt[q] = kVec;
-        rg[q] = Elem<GT>::smem4(sbase + e * sizeof(GT));
-        rp[q] = Elem<float>::smem4(sbase + L::kGBytes + e * 4);
-        rm[q] = Elem<float>::smem4(sbase + L::kGBytes + L::kFBytes + e * 4);
-        rv[q] = Elem<float>::smem4(sbase + L::kGBytes + 2 * L::kFBytes + e * 4);
-      } else {
-        cnt[q] = e < n ? ((n - e) < kVec ? (n - e) : kVec) : 0;
+          for (int j = 0; j < kVec; ++j) r.x[j] = (e + j < n) ? Elem<GT>::to_f32(gg[e + j]) : 0.f;
+        }
 #pragma unroll
         for (int j = 0; j < kVec; ++j) {
-          const bool ok = j < cnt[q];
-          rg[q].x[j] = ok ? Elem<GT>::to_f32(gg[e + j]) : 0.f;
-          rp[q].x[j] = ok ? gp[e + j] : 0.f;
-          rm[q].x[j] = ok ? gm[e + j] : 0.f;
-          rv[q].x[j] = ok ? gv[e + j] : 0.f;
+          const float x = r.x[j] * s1.gscale;
+          acc0 = fmaf(x, x, acc0);
         }
       }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar_empty + 8 * slot);  // values are in registers
-
-    if (phase == kPhaseB) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(my_done);
+      publishes = true;
+    } else if (op == kOpCP) {
+      // stage 2 from the parked chunk: p, update_m, update_g are in the slot
+      F4 rp[kBVecs], um[kBVecs], ug[kBVecs];
 #pragma unroll
-      for (int q = 0; q < kStageVecs; ++q)
+      for (int q = 0; q < kBVecs; ++q) {
+        const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+        rp[q] = Elem<float>::smem4(sbase + L::kGBytes + e * 4);
+        um[q] = Elem<float>::smem4(sbase + L::kGBytes + L::kFBytes + e * 4);
+        ug[q] = Elem<float>::smem4(sbase + L::kGBytes + 2 * L::kFBytes + e * 4);
+      }
+      fence_proxy_async_smem();  // the next bulk copy into this slot comes after these accesses
+      __syncwarp();
+      if (lane == 0) mbar_arrive(my_done);
 #pragma unroll
-        for (int j = 0; j < kVec; ++j) {
-          float um, ug, mm = rm[q].x[j], vv = rv[q].x[j];
-          const float pp = rp[q].x[j];
-          s1(rg[q].x[j], pp, mm, vv, cs, um, ug);
-          acc[0] = fmaf(pp, pp, acc[0]);
-          acc[1] = fmaf(um, um, acc[1]);
-          acc[2] = fmaf(ug, ug, acc[2]);
-        }
-      if (last) hand_over(kPhaseB, tensor, part_index, nchunks, first_chunk);
-    } else {  // phase C
+      for (int q = 0; q < kBVecs; ++q) {
+        const int e = q * (kGroupThreads * kVec) + gtid * kVec;
 #pragma unroll
-      for (int q = 0; q < kStageVecs; ++q) {
-        const int e = q * (kConsumers * kVec) + tid * kVec;
-#pragma unroll
-        for (int j = 0; j < kVec; ++j) {
-          float um, ug;
-          s1(rg[q].x[j], rp[q].x[j], rm[q].x[j], rv[q].x[j], cs, um, ug);
-          // p - ratio_m*update_m - ratio_g*update_g  (:385; the ratios carry the minus sign)
-          rp[q].x[j] = fmaf(ratio_g, ug, fmaf(ratio_m, um, rp[q].x[j]));
-        }
-        if (whole || e < nbulk) {  // aligned: 16-byte stores
+        for (int j = 0; j < kVec; ++j)
+          rp[q].x[j] = fmaf(ratio_g, ug[q].x[j], fmaf(ratio_m, um[q].x[j], rp[q].x[j]));
+        if (e < nbulk) {
           Elem<float>::template store4<kStream>(gp + e, rp[q], pol);
-          Elem<float>::template store4<kStream>(gm + e, rm[q], pol);
-          Elem<float>::template store4<kStream>(gv + e, rv[q], pol);
           if (gout) Elem<OT>::template store4<kStream>(gout + e, rp[q], pol);
         } else {
 #pragma unroll
           for (int j = 0; j < kVec; ++j)
-            if (j < cnt[q]) {
+            if (e + j < n) {
               gp[e + j] = rp[q].x[j];
-              gm[e + j] = rm[q].x[j];
-              gv[e + j] = rv[q].x[j];
               if (gout) gout[e + j] = Elem<OT>::from_f32(rp[q].x[j]);
             }
         }
       }
+    } else {
+      // ---- B (sums only), BP (sums, store m and v, park p / update_m / update_g), C ----
+      F4 rg[kBVecs], rp[kBVecs], rm[kBVecs], rv[kBVecs];
+#pragma unroll
+      for (int q = 0; q < kBVecs; ++q) {
+        const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+        if (e < nbulk) {
+          rg[q] = Elem<GT>::smem4(sbase + e * sizeof(GT));
+          rp[q] = Elem<float>::smem4(sbase + L::kGBytes + e * 4);
+          rm[q] = Elem<float>::smem4(sbase + L::kGBytes + L::kFBytes + e * 4);
+          rv[q] = Elem<float>::smem4(sbase + L::kGBytes + 2 * L::kFBytes + e * 4);
+        } else {
+#pragma unroll
+          for (int j = 0; j < kVec; ++j) {
+            const bool in = e + j < n;
+            rg[q].x[j] = in ? Elem<GT>::to_f32(gg[e + j]) : 0.f;
+            rp[q].x[j] = in ? gp[e + j] : 0.f;
+            rm[q].x[j] = in ? gm[e + j] : 0.f;
+            rv[q].x[j] = in ? gv[e + j] : 0.f;
+          }
+        }
+      }
+      if (op != kOpBP) {  // values are in registers: the slot can be refilled
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(my_done);
+      }
+      if (op == kOpC) {
+#pragma unroll
+        for (int q = 0; q < kBVecs; ++q) {
+          const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+#pragma unroll
+          for (int j = 0; j < kVec; ++j) {
+            float a, b;
+            s1(rg[q].x[j], rp[q].x[j], rm[q].x[j], rv[q].x[j], cs, a, b);
+            // p - ratio_m*update_m - ratio_g*update_g  (:385; the ratios carry the minus sign)
+            rp[q].x[j] = fmaf(ratio_g, b, fmaf(ratio_m, a, rp[q].x[j]));
+          }
+          if (e < nbulk) {  // aligned: 16-byte stores
+            Elem<float>::template store4<kStream>(gp + e, rp[q], pol);
+            Elem<float>::template store4<kStream>(gm + e, rm[q], pol);
+            Elem<float>::template store4<kStream>(gv + e, rv[q], pol);
+            if (gout) Elem<OT>::template store4<kStream>(gout + e, rp[q], pol);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kVec; ++j)
+              if (e + j < n) {
+                gp[e + j] = rp[q].x[j];
+                gm[e + j] = rm[q].x[j];
+                gv[e + j] = rv[q].x[j];
+                if (gout) gout[e + j] = Elem<OT>::from_f32(rp[q].x[j]);
+              }
+          }
+        }
+      } else {
+        publishes = true;
+#pragma unroll
+        for (int q = 0; q < kBVecs; ++q) {
+          const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+          F4 a, b;
+#pragma unroll
+          for (int j = 0; j < kVec; ++j) {
+            const float pp = rp[q].x[j];
+            s1(rg[q].x[j], pp, rm[q].x[j], rv[q].x[j], cs, a.x[j], b.x[j]);
+            acc0 = fmaf(pp, pp, acc0);
+            acc1 = fmaf(a.x[j], a.x[j], acc1);
+            acc2 = fmaf(b.x[j], b.x[j], acc2);
+          }
+          if (op == kOpBP) {
+            // m and v are final; p, update_m and update_g wait in the slot for the norms
+            float4* sp = reinterpret_cast<float4*>(sbase + L::kGBytes + e * 4);
+            float4* sm = reinterpret_cast<float4*>(sbase + L::kGBytes + L::kFBytes + e * 4);
+            float4* sv = reinterpret_cast<float4*>(sbase + L::kGBytes + 2 * L::kFBytes + e * 4);
+            *sm = make_float4(a.x[0], a.x[1], a.x[2], a.x[3]);
+            *sv = make_float4(b.x[0], b.x[1], b.x[2], b.x[3]);
+            if (e < nbulk) {
+              Elem<float>::template store4<kStream>(gm + e, rm[q], pol);
+              Elem<float>::template store4<kStream>(gv + e, rv[q], pol);
+            } else {
+              *sp = make_float4(rp[q].x[0], rp[q].x[1], rp[q].x[2], rp[q].x[3]);
+#pragma unroll
+              for (int j = 0; j < kVec; ++j)
+                if (e + j < n) {
+                  gm[e + j] = rm[q].x[j];
+                  gv[e + j] = rv[q].x[j];
+                }
+            }
+          }
+        }
+        if (op == kOpBP) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(my_done);
+        }
+      }
     }
+
+    LANS_TICK(c_op);
+    // The bookkeeping after an operation goes to a different warp of the group each time.
+    const bool duty = (uint32_t)wig == (i & 3u);
+    if (op == kOpBP) {
+      // every warp of the group has parked its part: the parker may finish the chunk as soon
+      // as the norms are final (which needs this chunk's sums, handed over below)
+      if (duty) {
+        if (lane == 0) {
+          ok = ring_wait(my_done, opar, P.hdr, kErrDone, slot, P.wait_ns);
+          if (ok) atomicOr(&ctrl->parked_mask, 1u << slot);
+        }
+        if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+      }
+    } else if (duty) {
+      // The item is finished.  When the other three warps have let go of the slot too,
+      // the next item of the ring starts in it; with the ring empty the parker takes over.
+      if (lane == 0) {
+        ok = ring_wait(my_done, opar, P.hdr, kErrDone, slot, P.wait_ns);
+        if (ok) {
+          atomicAdd(&ctrl->done_items, 1u);
+          if (!start_next(slot)) atomicOr(&ctrl->free_mask, 1u << slot);
+        }
+      }
+      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+    }
+
+    LANS_TICK(c_duty);
+    if (publishes) {
+      const float v0 = warp_sum(acc0);
+      float v1 = 0.f, v2 = 0.f;
+      if (op != kOpA) {
+        v1 = warp_sum(acc1);
+        v2 = warp_sum(acc2);
+      }
+      // the publisher has read this slot's previous sums
+      if (lane == 0) ok = ring_wait(bar_redempty + 8 * slot, rpar ^ 1u, P.hdr, kErrRing, 0x2000u | slot, P.wait_ns);
+      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+      if (lane == 0) {
+        RedSlot& rs = s_red[slot];
+        rs.val[0][wig] = v0;
+        rs.val[1][wig] = v1;
+        rs.val[2][wig] = v2;
+        if (wig == 0) {
+          rs.tensor = mt.tensor_op & kTensorMask;
+          rs.is_a = (op == kOpA) ? 1u : 0u;
+          rs.nparts = mt.nparts;
+        }
+        mbar_arrive(bar_redfull + 8 * slot);
+      }
+    }
+    LANS_TICK(c_pub);
+#ifdef RAFB200_LANS_TRACE
+    ++c_n;
+#endif
   }
-  // No more stages (or a wait expired): release the publisher.
-  hand_over(kRedEnd, 0, 0, 0, 0);
+#ifdef RAFB200_LANS_TRACE
+  if (blockIdx.x == 5 && lane == 0) {
+    long long* o = reinterpret_cast<long long*>(static_cast<char*>(P.trace) + 16 + 16 * 16000) + warp * 8;
+    o[0] = c_queue; o[1] = c_data; o[2] = c_op; o[3] = c_duty; o[4] = c_pub; o[5] = c_n;
+  }
+#endif
+  // No more work (or a wait expired): tell the publisher and the parker that this warp has left.
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar_end);
+}
+
+// One-tensor descriptor, per-block work-item lists and zeroed control words written by the
+// device itself: the set-up of the entry point that may not allocate or copy from host
+// memory.  Global order: A items, streamed stage-1 items, parked items, streamed updates;
+// item i of that order goes to block i % grid.
+__global__ void lans_static_init_kernel(unsigned char* ws, size_t ctl_off, size_t desc_off, size_t off_off,
+                                        size_t items_off, TensorDesc d, uint32_t n_a, uint32_t n_b,
+                                        uint32_t n_park, uint32_t grid) {
+  const uint32_t n_stream = n_b - n_park;
+  const uint32_t total = n_a + n_b + n_stream;
+  Item* items = reinterpret_cast<Item*>(ws + items_off);
+  uint32_t* off = reinterpret_cast<uint32_t*>(ws + off_off);
+  // block b owns the global positions b, b + grid, ...: (total - b + grid - 1) / grid of them
+  auto first_of = [&](uint32_t b) {  // entries of blocks 0 .. b-1
+    const uint32_t q = total / grid, r = total % grid;
+    return b * q + (b < r ? b : r);
+  };
+  for (uint32_t b = threadIdx.x; b <= grid; b += blockDim.x) off[b] = first_of(b);
+  for (uint32_t i = threadIdx.x; i < total; i += blockDim.x) {
+    Item it;
+    if (i < n_a) it = Item{kKindA << kPhaseShift, i};
+    else if (i < n_a + n_stream) it = Item{kKindBs << kPhaseShift, i - n_a};
+    else if (i < n_a + n_b) it = Item{kKindBCp << kPhaseShift, i - n_a};
+    else it = Item{kKindCs << kPhaseShift, i - n_a - n_b};
+    items[first_of(i % grid) + i / grid] = it;
+  }
+  uint32_t* head = reinterpret_cast<uint32_t*>(ws);
+  for (uint32_t i = threadIdx.x; i < (ctl_off + sizeof(LansCtl)) / 4; i += blockDim.x) head[i] = 0u;
+  if (threadIdx.x == 0) *reinterpret_cast<TensorDesc*>(ws + desc_off) = d;
 }
 
 // ---- host side -----------------------------------------------------------------
 
-// Orders the (tensor, chunk, phase) items of a list.  Dependencies always point
-// to earlier positions.  Priority C > B > A keeps a tensor's update pass right
-// behind its norm pass; `slack` items are placed between the last item of a
-// phase and the first dependent item where other work is available, so that
-// the dependent block rarely has to wait; `window` bounds how many chunks the
-// B cursor may lead the C cursor (and A lead B) when there is a choice.
-std::vector<Item> build_lans_schedule(const std::vector<uint32_t>& nchunks, bool with_a,
-                                      int64_t window_chunks, int slack) {
-  const int k = (int)nchunks.size();
+int lans_slots(int g_dtype) { return g_dtype == RAFB200_F32 ? kLansSlots32 : kLansSlots16; }
+int lans_a_elems(int g_dtype) { return g_dtype == RAFB200_F32 ? kLansAElems32 : kLansAElems16; }
+
+// How many chunks of one tensor may wait on chip at the same time, for a grid with
+// `slots_total` slots: about two thirds, and always at least four slots fewer than there are.
+uint32_t lans_park_cap(int64_t slots_total) {
+  int64_t cap = slots_total * 13 / 20;
+  if (const char* e = getenv("RAFB200_PARK_PCT")) cap = slots_total * atoi(e) / 100;  // EXPERIMENT
+  if (cap > slots_total - 4) cap = slots_total - 4;
+  return (uint32_t)(cap < 0 ? 0 : cap);
+}
+
+// Orders the work items of a list.  Dependencies always point to earlier positions:
+//   - the A items of a tensor precede its first Bs / BCp item, and the A pass runs
+//     `lead_elems` elements ahead of the rest where the list allows it;
+//   - the Bs and BCp items of the tensors come in tensor order, a tensor's Bs items first,
+//     then its BCp items (at most `park_cap` of them: the tail of the tensor);
+//   - the Cs items of a tensor follow its last BCp item, after `gap_items` further items
+//     where other work exists (the norms they wait for are then final when they are drawn),
+//     alternating with that other work so that loads and stores stay mixed.
+std::vector<Item> build_lans_schedule(const std::vector<int64_t>& numel, int a_elems, bool with_a,
+                                      uint32_t park_cap, int64_t lead_elems, int64_t gap_items) {
+  const int k = (int)numel.size();
   std::vector<Item> out;
-  uint64_t total = 0;
-  for (uint32_t n : nchunks) total += n;
-  out.reserve(total * (with_a ? 3 : 2));
-  struct Cursor {
-    int t = 0;
-    uint32_t c = 0;
-    uint64_t emitted = 0;
-  } A, B, Cc;
-  auto skip_empty = [&](Cursor& cur) {
-    while (cur.t < k && nchunks[cur.t] == 0) cur.t++;
+  struct Pending {  // the streamed update items of a tensor, released `gap_items` later
+    uint32_t tensor, next, count;
+    int64_t release_at;
   };
-  skip_empty(A);
-  skip_empty(B);
-  skip_empty(Cc);
-  std::vector<int64_t> done_a(k, -1), done_b(k, -1);
-  auto emit = [&](Cursor& cur, int phase, std::vector<int64_t>* done) {
-    const uint32_t chunk = cur.c;
-    out.push_back(Item{((uint32_t)phase << kPhaseShift) | (uint32_t)cur.t, chunk});
-    cur.emitted++;
-    if (++cur.c == nchunks[cur.t]) {
-      if (done) (*done)[cur.t] = (int64_t)out.size();
-      cur.c = 0;
-      cur.t++;
-      skip_empty(cur);
+  std::vector<Pending> pend;
+  size_t pend_head = 0;
+  int a_t = 0;
+  uint32_t a_c = 0;
+  int64_t a_done = 0, b_done = 0;
+  auto n_a_of = [&](int t) { return (uint32_t)((numel[t] + a_elems - 1) / a_elems); };
+  auto n_b_of = [&](int t) { return (uint32_t)((numel[t] + kLansElems - 1) / kLansElems); };
+  auto skip_a = [&]() {
+    while (a_t < k && n_a_of(a_t) == 0) ++a_t;
+  };
+  auto emit_a = [&]() {
+    out.push_back(Item{(kKindA << kPhaseShift) | (uint32_t)a_t, a_c});
+    const int64_t left = numel[a_t] - (int64_t)a_c * a_elems;
+    a_done += left < a_elems ? left : a_elems;
+    if (++a_c == n_a_of(a_t)) {
+      a_c = 0;
+      ++a_t;
+      skip_a();
     }
   };
-  if (!with_a) A.t = k;
-  // Round-robin: in every round each phase that may run emits one item.  The three passes
-  // then advance at the same rate, reads and writes reach DRAM in a steady 2:1 mix, and a
-  // block that holds an item whose norm is not final yet is one of few, not one of all:
-  // measured 2.21 ms against 2.45 ms for "phase C first, in bursts" on the 335 M-element list.
-  // Phase C trails phase B by the largest tensor seen so far, so on lists with tensors
-  // beyond a few MB its reads come from DRAM, not from L2; schedules that kept it closer
-  // (bursts, 2:1 to 8:1 catch-up) re-read less but stalled more and measured slower, and
-  // visiting the tensors smallest first cut the DRAM reads by 12 % but left the huge ones
-  // as an unoverlapped tail (2.33 ms); huge tensors first, the rest smallest first, with
-  // phase C catching up to one tensor behind cut the reads by 7 % and took 2.39 ms (2.42 ms
-  // with the tiny tensors left mixed among the medium ones).  Fewer
-  // DRAM bytes did not buy time in any of them: what limits the kernel once phase C runs
-  // close behind phase B is the wait for the norms, not bandwidth.
-  while (Cc.t < k) {
-    bool progressed = false;
-    {
-      const int64_t n = (int64_t)out.size();
-      const bool c_ready = Cc.t < k && B.t > Cc.t;
-      if (c_ready && (Cc.c > 0 || n - done_b[Cc.t] >= slack)) {
-        emit(Cc, kPhaseC, nullptr);
-        progressed = true;
-      }
+  auto emit_pending = [&](bool force) -> bool {
+    if (pend_head >= pend.size()) return false;
+    Pending& pd = pend[pend_head];
+    if (!force && (int64_t)out.size() < pd.release_at) return false;
+    out.push_back(Item{(kKindCs << kPhaseShift) | pd.tensor, pd.next});
+    if (++pd.next == pd.count) ++pend_head;
+    return true;
+  };
+  if (!with_a) a_t = k;
+  skip_a();
+  int64_t end_of_t = 0;
+  for (int t = 0; t < k; ++t) {
+    end_of_t += numel[t];
+    const uint32_t nb = n_b_of(t);
+    if (nb == 0) continue;
+    const uint32_t park = nb < park_cap ? nb : park_cap;
+    const uint32_t stream = nb - park;
+    for (uint32_t c = 0; c < nb; ++c) {
+      // the gradient-norm pass: complete for this tensor, and `lead_elems` ahead
+      while (a_t < k && (a_t <= t || a_done < b_done + lead_elems)) emit_a();
+      (void)end_of_t;
+      emit_pending(false);  // one streamed update item of an earlier tensor, when released
+      out.push_back(Item{((c < stream ? kKindBs : kKindBCp) << kPhaseShift) | (uint32_t)t, c});
+      const int64_t left = numel[t] - (int64_t)c * kLansElems;
+      b_done += left < kLansElems ? left : kLansElems;
     }
-    {
-      const int64_t n = (int64_t)out.size();
-      const bool b_ready = B.t < k && (!with_a || A.t > B.t);
-      if (b_ready && (B.c > 0 || !with_a || n - done_a[B.t] >= slack) &&
-          (int64_t)(B.emitted - Cc.emitted) < window_chunks) {
-        emit(B, kPhaseB, &done_b);
-        progressed = true;
-      }
-    }
-    if (with_a && A.t < k && (int64_t)(A.emitted - B.emitted) < window_chunks + 2048) {
-      emit(A, kPhaseA, &done_a);
-      progressed = true;
-    }
-    if (!progressed) {  // slack or window not met anywhere: advance what the dependencies allow
-      const bool b_ready = B.t < k && (!with_a || A.t > B.t);
-      if (with_a && A.t < k) emit(A, kPhaseA, &done_a);
-      else if (b_ready) emit(B, kPhaseB, &done_b);
-      else emit(Cc, kPhaseC, nullptr);
-    }
+    if (stream > 0) pend.push_back(Pending{(uint32_t)t, 0, stream, (int64_t)out.size() + gap_items});
+  }
+  while (emit_pending(true)) {
   }
   return out;
 }
 
-size_t lans_ctl_bytes(int k) { return 64 + sizeof(LansCtl) * (size_t)k; }
+// Deals the items of a schedule out to `grid` blocks, each block keeping the global order.
+// Stage-1 items (Bs, BCp) are dealt in turn among themselves, the other items among
+// themselves, so that a tensor's parked items spread evenly over the blocks whatever they
+// are interleaved with.  Result: off[0 .. grid] followed (8-byte aligned) by the items.
+std::vector<uint32_t> partition_lans_items(const std::vector<Item>& sched, int grid) {
+  std::vector<std::vector<Item>> per(grid);
+  uint64_t rr_b = 0, rr_o = 0;
+  for (const Item& it : sched) {
+    const uint32_t kind = it.tensor_phase >> kPhaseShift;
+    const bool stage1 = kind == kKindBs || kind == kKindBCp;
+    per[(stage1 ? rr_b++ : rr_o++) % (uint64_t)grid].push_back(it);
+  }
+  const size_t head = ((size_t)grid + 1 + 1) & ~(size_t)1;  // uint32 words before the items
+  std::vector<uint32_t> out(head + 2 * sched.size());
+  uint32_t at = 0;
+  for (int b = 0; b < grid; ++b) {
+    out[b] = at;
+    for (const Item& it : per[b]) {
+      out[head + 2 * (size_t)at] = it.tensor_phase;
+      out[head + 2 * (size_t)at + 1] = it.chunk;
+      ++at;
+    }
+  }
+  out[grid] = at;
+  return out;
+}
 
-size_t lans_workspace_bytes(int k, uint32_t total_chunks) {
-  (void)total_chunks;  // partial sums are accumulated per tensor, not stored per chunk
-  return (lans_ctl_bytes(k) + 255) & ~(size_t)255;
+size_t lans_ctl_bytes(int k) { return 128 + sizeof(LansCtl) * (size_t)k; }
+
+#ifdef RAFB200_LANS_TRACE
+size_t lans_workspace_bytes(int k) { return ((lans_ctl_bytes(k) + 255) & ~(size_t)255) + 16 + 16 * 16000 + 2048; }
+#else
+size_t lans_workspace_bytes(int k) { return (lans_ctl_bytes(k) + 255) & ~(size_t)255; }
+#endif
+
+// The persistent grid: one block per SM, or fewer when a cap leaves SMs to a concurrent
+// collective.  The schedule of a list is built for this number of blocks.
+int lans_grid(int sm_count, int max_blocks) {
+  int g = sm_count;
+  if (max_blocks > 0 && g > max_blocks) g = max_blocks;
+  return g < 1 ? 1 : g;
 }
 
 template <typename GT, typename OT>
-static int launch_lans_t(const rafb200_tensor_list_s* l, const LansParams& P, cudaStream_t s) {
-  static int occ[64] = {0};
-  const int dev = (l->device >= 0 && l->device < 64) ? l->device : 0;
-  const int smem = LansSmem<GT>::kTotal;
-  if (occ[dev] == 0) {
+static int launch_lans_t(int device, int grid, const LansParams& P, cudaStream_t s) {
+  static bool configured[64] = {false};
+  const int dev = (device >= 0 && device < 64) ? device : 0;
+  const int smem = LansGeo<GT>::kTotal;
+  if (!configured[dev]) {
     RAFB200_CUDA(cudaFuncSetAttribute(lans_kernel<GT, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, lans_kernel<GT, OT>, kLansThreads, smem) !=
-            cudaSuccess || n <= 0)
-      n = 1;
-    occ[dev] = n;
+    configured[dev] = true;
   }
-  // Persistent grid: every SM holds `occ` blocks; a cap leaves SMs to a concurrent collective.
-  int64_t grid = (int64_t)l->sm_count * occ[dev];
-  if (l->max_blocks > 0 && grid > l->max_blocks) grid = l->max_blocks;
-  if (grid > (int64_t)P.nitems) grid = P.nitems;
-  if (grid < 1) grid = 1;
   lans_kernel<GT, OT><<<(unsigned)grid, kLansThreads, smem, s>>>(P);
   RAFB200_CUDA(cudaGetLastError());
   return RAFB200_OK;
 }
 
 template <typename GT>
-static int launch_lans_g(const rafb200_tensor_list_s* l, const LansParams& P, cudaStream_t s) {
-  switch (l->out_dtype) {
-    case RAFB200_F32: return launch_lans_t<GT, float>(l, P, s);
-    case RAFB200_F16: return launch_lans_t<GT, __half>(l, P, s);
-    default: return launch_lans_t<GT, __nv_bfloat16>(l, P, s);
+static int launch_lans_g(int device, int grid, int out_dtype, const LansParams& P, cudaStream_t s) {
+  switch (out_dtype) {
+    case RAFB200_F32: return launch_lans_t<GT, float>(device, grid, P, s);
+    case RAFB200_F16: return launch_lans_t<GT, __half>(device, grid, P, s);
+    default: return launch_lans_t<GT, __nv_bfloat16>(device, grid, P, s);
   }
+}
+
+static int launch_lans(int device, int grid, int g_dtype, int out_dtype, const LansParams& P, cudaStream_t s) {
+  switch (g_dtype) {
+    case RAFB200_F32: return launch_lans_g<float>(device, grid, out_dtype, P, s);
+    case RAFB200_F16: return launch_lans_g<__half>(device, grid, out_dtype, P, s);
+    default: return launch_lans_g<__nv_bfloat16>(device, grid, out_dtype, P, s);
+  }
+}
+
+static void fill_stage1(LansParams* P, int step, float learning_rate, float beta1, float beta2, float eps,
+                        int bias_correction, float weight_decay, int grad_averaging, int mode,
+                        int normalize_grad, float grad_scale) {
+  P->s1.beta1 = beta1;
+  P->s1.beta2 = beta2;
+  P->s1.beta3 = (grad_averaging == 1) ? 1 - beta1 : 1.0f;  // lans.cc:106-109
+  P->s1.one_minus_beta2 = 1 - beta2;
+  P->s1.eps = eps;
+  float bc1, bc2;
+  bias_corrections(beta1, beta2, step, bias_correction, &bc1, &bc2);
+  P->s1.inv_bc1 = 1.0f / bc1;
+  P->s1.inv_bc2 = 1.0f / bc2;
+  P->s1.wd = weight_decay;
+  P->s1.gscale = grad_scale;
+  P->s1.mode = mode;
+  P->s1.normalize = normalize_grad ? 1 : 0;
+  P->lr = learning_rate;
+  P->bias_correction = bias_correction;
 }
 
 }  // namespace rafb200
@@ -942,23 +1141,26 @@ using namespace rafb200;
 // Everything rafb200_lans keeps in caller-provided device memory (header, per-tensor
 // control words, descriptor row, work-item table) for ONE tensor of at most
 // kStaticMaxElems elements, as a statically allocated device array: every GPU that
-// loads this library holds these 25 KB until the process exits.
-constexpr int64_t kStaticMaxElems = 4ll << 20;                          // 4,194,304 elements
-constexpr uint32_t kStaticMaxChunks = (uint32_t)(kStaticMaxElems / kChunkElems);  // 1024
-constexpr size_t kStaticCtlOff = 64, kStaticDescOff = 256, kStaticItemsOff = 512;
-constexpr size_t kStaticBytes = kStaticItemsOff + 3 * (size_t)kStaticMaxChunks * sizeof(Item);
+// loads this library holds these 76 KB until the process exits.
+constexpr int64_t kStaticMaxElems = 4ll << 20;  // 4,194,304 elements
+constexpr uint32_t kStaticMaxB = (uint32_t)(kStaticMaxElems / kLansElems);                         // 4096
+constexpr uint32_t kStaticMaxA = (uint32_t)((kStaticMaxElems + kLansAElems32 - 1) / kLansAElems32);  // 1024
+constexpr size_t kStaticCtlOff = 128, kStaticDescOff = 256, kStaticOffOff = 512, kStaticItemsOff = 2048;
+constexpr int kStaticMaxGrid = (int)((kStaticItemsOff - kStaticOffOff) / 4) - 1;  // 383 blocks
+constexpr size_t kStaticBytes = kStaticItemsOff + (size_t)(kStaticMaxA + 2 * kStaticMaxB) * sizeof(Item);
 static __device__ __align__(256) unsigned char g_lans_static_scratch[kStaticBytes];
 
 // Device address of the array above, per device.  In host code the array's name is
 // only a handle for the runtime, not an address a kernel could use: the address has
 // to be asked for, once per device, with that device current.
 static void* g_lans_static_ptr[64] = {nullptr};
+static int g_lans_static_sms[64] = {0};
 
 extern "C" {
 
 size_t rafb200_lans_workspace_bytes(rafb200_tensor_list_t list) {
   if (!list) return 0;
-  return lans_workspace_bytes(list->k, list->total_chunks);
+  return lans_workspace_bytes(list->k);
 }
 
 int rafb200_lans(rafb200_tensor_list_t list, int step, const float* step_dev, float learning_rate,
@@ -969,54 +1171,39 @@ int rafb200_lans(rafb200_tensor_list_t list, int step, const float* step_dev, fl
   RAFB200_REQUIRE(list->bound && list->has_v, "rafb200_lans: bind g, p, m and v first");
   RAFB200_REQUIRE(step_dev != nullptr || step >= 1, "rafb200_lans: step counts from 1");
   RAFB200_REQUIRE(mode == 0 || mode == 1, "rafb200_lans: mode must be 0 (L2) or 1 (decoupled)");
-  const size_t need = lans_workspace_bytes(list->k, list->total_chunks);
+  const size_t need = lans_workspace_bytes(list->k);
   RAFB200_REQUIRE(workspace && workspace_bytes >= need,
                   "rafb200_lans: workspace of %zu bytes required, got %zu", need, workspace_bytes);
   RAFB200_REQUIRE(reinterpret_cast<uintptr_t>(workspace) % 16 == 0,
                   "rafb200_lans: workspace must be 16-byte aligned");
-  if (list->total_chunks == 0) return RAFB200_OK;
+  if (list->total_elems == 0) return RAFB200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
   LansParams P;
   P.descs = list->dev_desc;
-  if (normalize_grad) {
-    P.items = list->dev_lans_items;
-    P.nitems = list->n_lans_items;
-  } else {
-    P.items = list->dev_lans_items_nonorm;
-    P.nitems = list->n_lans_items_nonorm;
-  }
+  const uint32_t* table = normalize_grad ? list->dev_lans_lists : list->dev_lans_lists_nonorm;
+  const size_t head = ((size_t)list->lans_grid + 1 + 1) & ~(size_t)1;
+  P.block_off = table;
+  P.items = reinterpret_cast<const Item*>(table + head);
   char* ws = static_cast<char*>(workspace);
   P.hdr = reinterpret_cast<LansHeader*>(ws);
-  P.ctl = reinterpret_cast<LansCtl*>(ws + 64);
-  P.s1.beta1 = beta1;
-  P.s1.beta2 = beta2;
-  P.s1.beta3 = (grad_averaging == 1) ? 1 - beta1 : 1.0f;  // lans.cc:106-109
-  P.s1.one_minus_beta2 = 1 - beta2;
-  P.s1.eps = eps;
-  float bc1, bc2;
-  bias_corrections(beta1, beta2, step_dev ? 1 : step, bias_correction, &bc1, &bc2);
-  P.s1.inv_bc1 = 1.0f / bc1;
-  P.s1.inv_bc2 = 1.0f / bc2;
-  P.s1.wd = weight_decay;
-  P.s1.gscale = grad_scale;
-  P.s1.mode = mode;
-  P.s1.normalize = normalize_grad ? 1 : 0;
-  P.lr = learning_rate;
+  P.ctl = reinterpret_cast<LansCtl*>(ws + 128);
+  fill_stage1(&P, step_dev ? 1 : step, learning_rate, beta1, beta2, eps, bias_correction, weight_decay,
+              grad_averaging, mode, normalize_grad, grad_scale);
   P.step_dev = step_dev;
-  P.bias_correction = bias_correction;
-  P.wait_ns = 2000000000ull;  // two seconds: far beyond any legitimate wait
+  P.wait_ns = list->wait_ns;
+  P.trace = nullptr;
+#ifdef RAFB200_LANS_TRACE
+  P.trace = ws + ((lans_ctl_bytes(list->k) + 255) & ~(size_t)255);
+  RAFB200_CUDA(cudaMemsetAsync(P.trace, 0, 16, s));
+#endif
 
   RAFB200_CUDA(cudaMemsetAsync(workspace, 0, lans_ctl_bytes(list->k), s));
   if (step_dev) {
     lans_bias_kernel<<<1, 1, 0, s>>>(P.hdr, step_dev, beta1, beta2, bias_correction);
     RAFB200_CUDA(cudaGetLastError());
   }
-  switch (list->g_dtype) {
-    case RAFB200_F32: return launch_lans_g<float>(list, P, s);
-    case RAFB200_F16: return launch_lans_g<__half>(list, P, s);
-    default: return launch_lans_g<__nv_bfloat16>(list, P, s);
-  }
+  return launch_lans(list->device, list->lans_grid, list->g_dtype, list->out_dtype, P, s);
 }
 
 int rafb200_lans_tensor_static(const void* g, int g_dtype, float* p, float* m, float* v,
@@ -1044,17 +1231,11 @@ int rafb200_lans_tensor_static(const void* g, int g_dtype, float* p, float* m, f
     // First call on this device (do it before any stream capture): resolve the symbol.
     void* ptr = nullptr;
     RAFB200_CUDA(cudaGetSymbolAddress(&ptr, g_lans_static_scratch));
+    RAFB200_CUDA(cudaDeviceGetAttribute(&g_lans_static_sms[device], cudaDevAttrMultiProcessorCount, device));
     g_lans_static_ptr[device] = ptr;
   }
-  char* ws = static_cast<char*>(g_lans_static_ptr[device]);
+  unsigned char* ws = static_cast<unsigned char*>(g_lans_static_ptr[device]);
 
-  // One-tensor list on the host stack: nothing here touches a device allocator.
-  rafb200_tensor_list_s one;
-  one.k = 1;
-  one.g_dtype = g_dtype;
-  one.out_dtype = out_dtype;
-  one.device = device;
-  RAFB200_CUDA(cudaDeviceGetAttribute(&one.sm_count, cudaDevAttrMultiProcessorCount, device));
   TensorDesc d{};
   d.g = g;
   d.p = p;
@@ -1069,61 +1250,51 @@ int rafb200_lans_tensor_static(const void* g, int g_dtype, float* p, float* m, f
                       (reinterpret_cast<uintptr_t>(g) % (g_dtype == RAFB200_F32 ? 16 : 8) == 0) &&
                       (!out || reinterpret_cast<uintptr_t>(out) % (out_dtype == RAFB200_F32 ? 16 : 8) == 0);
   d.flags = vec_ok ? kFlagAligned : 0u;
-  if (vec_ok && a16(g)) d.flags |= kFlagBulk;
-  const std::vector<Item> items =
-      build_lans_schedule(std::vector<uint32_t>{d.nchunks}, normalize_grad != 0,
-                          (int64_t)kStaticMaxChunks, 0);
+  if (vec_ok && a16(g) && (!out || a16(out))) d.flags |= kFlagBulk;
+
+  int grid = lans_grid(g_lans_static_sms[device], 0);
+  if (grid > kStaticMaxGrid) grid = kStaticMaxGrid;
+  const int a_elems = lans_a_elems(g_dtype);
+  const uint32_t n_a = normalize_grad ? (uint32_t)((numel + a_elems - 1) / a_elems) : 0u;
+  const uint32_t n_b = (uint32_t)((numel + kLansElems - 1) / kLansElems);
+  const uint32_t cap = lans_park_cap((int64_t)grid * lans_slots(g_dtype));
+  const uint32_t n_park = n_b < cap ? n_b : cap;
 
   LansParams P;
   P.descs = reinterpret_cast<const TensorDesc*>(ws + kStaticDescOff);
+  P.block_off = reinterpret_cast<const uint32_t*>(ws + kStaticOffOff);
   P.items = reinterpret_cast<const Item*>(ws + kStaticItemsOff);
-  P.nitems = (uint32_t)items.size();
   P.hdr = reinterpret_cast<LansHeader*>(ws);
   P.ctl = reinterpret_cast<LansCtl*>(ws + kStaticCtlOff);
-  P.s1.beta1 = beta1;
-  P.s1.beta2 = beta2;
-  P.s1.beta3 = (grad_averaging == 1) ? 1 - beta1 : 1.0f;
-  P.s1.one_minus_beta2 = 1 - beta2;
-  P.s1.eps = eps;
-  float bc1, bc2;
-  bias_corrections(beta1, beta2, step, bias_correction, &bc1, &bc2);
-  P.s1.inv_bc1 = 1.0f / bc1;
-  P.s1.inv_bc2 = 1.0f / bc2;
-  P.s1.wd = weight_decay;
-  P.s1.gscale = grad_scale;
-  P.s1.mode = mode;
-  P.s1.normalize = normalize_grad ? 1 : 0;
-  P.lr = learning_rate;
+  fill_stage1(&P, step, learning_rate, beta1, beta2, eps, bias_correction, weight_decay, grad_averaging,
+              mode, normalize_grad, grad_scale);
   P.step_dev = nullptr;
-  P.bias_correction = bias_correction;
   P.wait_ns = 2000000000ull;
+  P.trace = nullptr;
 
-  // The array keeps whatever the previous call left in it: ticket counter, error word,
-  // arrival counters, sums and norm words must start at zero; descriptor and item table
-  // are rewritten.  (Pageable sources: the runtime stages them before returning.)
-  RAFB200_CUDA(cudaMemsetAsync(ws, 0, kStaticCtlOff + sizeof(LansCtl), s));
-  RAFB200_CUDA(cudaMemcpyAsync(ws + kStaticDescOff, &d, sizeof(d), cudaMemcpyHostToDevice, s));
-  RAFB200_CUDA(cudaMemcpyAsync(ws + kStaticItemsOff, items.data(), items.size() * sizeof(Item),
-                               cudaMemcpyHostToDevice, s));
-  switch (g_dtype) {
-    case RAFB200_F32: return launch_lans_g<float>(&one, P, s);
-    case RAFB200_F16: return launch_lans_g<__half>(&one, P, s);
-    default: return launch_lans_g<__nv_bfloat16>(&one, P, s);
-  }
+  // The array keeps whatever the previous call left in it.  A small kernel on the same
+  // stream zeroes the ticket counter, the error word, the arrival counters, sums and norm
+  // words and writes this call's descriptor and item table; nothing is copied from host
+  // memory and nothing is allocated, on the device or on the host.
+  lans_static_init_kernel<<<1, 256, 0, s>>>(ws, kStaticCtlOff, kStaticDescOff, kStaticOffOff, kStaticItemsOff, d,
+                                            n_a, n_b, n_park, (uint32_t)grid);
+  RAFB200_CUDA(cudaGetLastError());
+  return launch_lans(device, grid, g_dtype, out_dtype, P, s);
 }
 
-int rafb200_lans_schedule(int k, const int64_t* numel, int with_norm_phase, int64_t window_elems,
-                          int slack_items, uint32_t* items, size_t capacity, size_t* count) {
-  RAFB200_REQUIRE(k >= 0 && (k == 0 || numel) && count && window_elems >= 0 && slack_items >= 0,
+int rafb200_lans_schedule(int k, const int64_t* numel, int g_dtype, int with_norm_phase, int slots_total,
+                          int64_t lead_elems, int gap_items, uint32_t* items, size_t capacity,
+                          size_t* count) {
+  RAFB200_REQUIRE(k >= 0 && (k == 0 || numel) && count && lead_elems >= 0 && gap_items >= 0 &&
+                      slots_total >= 1 && dtype_valid(g_dtype),
                   "rafb200_lans_schedule: bad arguments");
-  std::vector<uint32_t> nchunks(k);
+  std::vector<int64_t> n(k);
   for (int i = 0; i < k; ++i) {
     RAFB200_REQUIRE(numel[i] >= 0, "rafb200_lans_schedule: numel[%d] < 0", i);
-    nchunks[i] = (uint32_t)((numel[i] + kChunkElems - 1) / kChunkElems);
+    n[i] = numel[i];
   }
-  int64_t window_chunks = window_elems / kChunkElems;
-  if (window_chunks < 1) window_chunks = 1;
-  const std::vector<Item> sched = build_lans_schedule(nchunks, with_norm_phase != 0, window_chunks, slack_items);
+  const std::vector<Item> sched = build_lans_schedule(n, lans_a_elems(g_dtype), with_norm_phase != 0,
+                                                      lans_park_cap(slots_total), lead_elems, gap_items);
   *count = sched.size();
   if (items) {
     RAFB200_REQUIRE(capacity >= sched.size(), "rafb200_lans_schedule: %zu items, room for %zu", sched.size(),
@@ -1144,7 +1315,7 @@ int rafb200_lans_status(rafb200_tensor_list_t list, const void* workspace, float
   std::vector<char> host(lans_ctl_bytes(list->k));
   RAFB200_CUDA(cudaMemcpy(host.data(), workspace, host.size(), cudaMemcpyDeviceToHost));
   const LansHeader* hdr = reinterpret_cast<const LansHeader*>(host.data());
-  const LansCtl* ctl = reinterpret_cast<const LansCtl*>(host.data() + 64);
+  const LansCtl* ctl = reinterpret_cast<const LansCtl*>(host.data() + 128);
   if (norms_host) {
     for (int t = 0; t < list->k; ++t)
       for (int j = 0; j < 4; ++j) {

@@ -28,7 +28,7 @@ __device__ __forceinline__ uint64_t symm_now_ns() {
 // stream order is complete, hence published by the release stores; work issued after it
 // starts only when every peer has arrived.
 __global__ void xbarrier_kernel(SymmPeers sig, int world, int rank, int lane, uint32_t epoch,
-                                uint64_t timeout_ns, unsigned int* err) {
+                                uint64_t timeout_ns, unsigned int* err, unsigned int* host_err) {
   const int t = threadIdx.x;
   if (t >= world) return;
   __threadfence_system();
@@ -43,7 +43,11 @@ __global__ void xbarrier_kernel(SymmPeers sig, int world, int rank, int lane, ui
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
     if ((int32_t)(v - epoch) >= 0) break;
     if (symm_now_ns() - t0 > timeout_ns) {  // a peer never arrived: report, do not hang
-      atomicCAS(err, 0u, 0x100u | (unsigned)(lane << 4) | (unsigned)t);
+      const unsigned code = 0x100u | (unsigned)(lane << 4) | (unsigned)t;
+      if (atomicCAS(err, 0u, code) == 0u && host_err != nullptr) {
+        *reinterpret_cast<volatile unsigned int*>(host_err) = code;  // the host reads it without a sync
+        __threadfence_system();
+      }
       break;
     }
     __nanosleep(200);
@@ -200,9 +204,9 @@ static unsigned symm_grid(uint32_t nitems, int blocks) {
   return (unsigned)(g < 1 ? 1 : g);
 }
 
-int symm_barrier(const SymmPeers& sig, int world, int rank, int lane, uint32_t epoch,
-                 unsigned int* err, cudaStream_t s) {
-  xbarrier_kernel<<<1, 32, 0, s>>>(sig, world, rank, lane, epoch, 10000000000ull, err);
+int symm_barrier(const SymmPeers& sig, int world, int rank, int lane, uint32_t epoch, uint64_t limit_ns,
+                 unsigned int* err, unsigned int* host_err, cudaStream_t s) {
+  xbarrier_kernel<<<1, 32, 0, s>>>(sig, world, rank, lane, epoch, limit_ns, err, host_err);
   RAFB200_CUDA(cudaGetLastError());
   return RAFB200_OK;
 }

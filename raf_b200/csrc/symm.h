@@ -14,8 +14,10 @@ struct SymmPeers {
 };
 
 // Cross-GPU flag barrier on `lane` (epochs grow by one per call, in the same order on every rank).
-int symm_barrier(const SymmPeers& sig, int world, int rank, int lane, uint32_t epoch,
-                 unsigned int* err, cudaStream_t s);
+// A wait that exceeds `limit_ns` records (lane, late rank) in *err and, when host_err is not
+// NULL, in that word of host-mapped memory as well; later barriers then pass without waiting.
+int symm_barrier(const SymmPeers& sig, int world, int rank, int lane, uint32_t epoch, uint64_t limit_ns,
+                 unsigned int* err, unsigned int* host_err, cudaStream_t s);
 constexpr int kSymmChunkBytes = 32768;  // bytes per work item of the collective kernels
 
 // This rank's row block of one tensor inside the symmetric buffer.

@@ -16,8 +16,13 @@ int set_error(int status, const char* fmt, ...) {
   return status;
 }
 
-std::vector<Item> build_lans_schedule(const std::vector<uint32_t>& nchunks, bool with_a,
-                                      int64_t window_chunks, int slack);
+std::vector<Item> build_lans_schedule(const std::vector<int64_t>& numel, int a_elems, bool with_a,
+                                      uint32_t park_cap, int64_t lead_elems, int64_t gap_items);
+int lans_slots(int g_dtype);
+int lans_a_elems(int g_dtype);
+uint32_t lans_park_cap(int64_t slots_total);
+int lans_grid(int sm_count, int max_blocks);
+std::vector<uint32_t> partition_lans_items(const std::vector<Item>& sched, int grid);
 bool pointers_aligned(const void* g, int g_dtype, const void* p, const void* m, const void* v,
                       const void* out, int out_dtype);
 
@@ -33,16 +38,29 @@ static int upload_items(const std::vector<Item>& items, Item** dev, uint32_t* n)
   return RAFB200_OK;
 }
 
+static int upload_lists(const std::vector<Item>& sched, int grid, uint32_t** dev) {
+  if (*dev) {
+    cudaFree(*dev);
+    *dev = nullptr;
+  }
+  const std::vector<uint32_t> table = partition_lans_items(sched, grid);
+  RAFB200_CUDA(cudaMalloc(reinterpret_cast<void**>(dev), table.size() * sizeof(uint32_t)));
+  RAFB200_CUDA(cudaMemcpy(*dev, table.data(), table.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
+  return RAFB200_OK;
+}
+
 static int rebuild_lans_schedule(rafb200_tensor_list_s* l) {
-  std::vector<uint32_t> nchunks(l->k);
-  for (int i = 0; i < l->k; ++i) nchunks[i] = l->host_desc[i].nchunks;
-  int64_t window_chunks = l->window_elems / kChunkElems;
-  if (window_chunks < 1) window_chunks = 1;
-  int rc = upload_items(build_lans_schedule(nchunks, true, window_chunks, l->slack_items),
-                        &l->dev_lans_items, &l->n_lans_items);
+  l->lans_grid = lans_grid(l->sm_count, l->max_blocks);
+  const int64_t slots_total = (int64_t)l->lans_grid * lans_slots(l->g_dtype);
+  const uint32_t cap = lans_park_cap(slots_total);
+  const int64_t gap = l->gap_items > 0 ? l->gap_items : slots_total;
+  const int a_elems = lans_a_elems(l->g_dtype);
+  l->custom_items = false;
+  int rc = upload_lists(build_lans_schedule(l->numel, a_elems, true, cap, l->lead_elems, gap), l->lans_grid,
+                        &l->dev_lans_lists);
   if (rc != RAFB200_OK) return rc;
-  return upload_items(build_lans_schedule(nchunks, false, window_chunks, l->slack_items),
-                      &l->dev_lans_items_nonorm, &l->n_lans_items_nonorm);
+  return upload_lists(build_lans_schedule(l->numel, a_elems, false, cap, l->lead_elems, gap), l->lans_grid,
+                      &l->dev_lans_lists_nonorm);
 }
 
 }  // namespace rafb200
@@ -111,13 +129,13 @@ int rafb200_tensor_list_create(int k, const int64_t* numel, int g_dtype, int out
       for (uint32_t c = 0; c < l->host_desc[i].nchunks; ++c) items.push_back(Item{(uint32_t)i, c});
     rc = upload_items(items, &l->dev_items, &l->n_items);
     if (rc != RAFB200_OK) break;
-    // Defaults.  A block holds up to three tickets and three blocks run per SM, so about
-    // eight items per SM are in flight; that many items are placed between the last item
-    // of a phase of a tensor and the first item that depends on it.  With the round-robin
-    // order of the three passes the step time is flat in this value (0 to 32 per SM
-    // measured within 1 %).  The B pass may lead the C pass by 32 Mi elements at most.
-    l->slack_items = 8 * l->sm_count;
-    l->window_elems = 32ll << 20;
+    // Defaults.  The gradient-norm pass leads by 8 Mi elements: more than any tensor that is
+    // kept on chip in full and a few thousand work items of slack, yet little enough
+    // (16 MB of 16-bit gradients) that the second read of g comes from L2.  gap_items 0 =
+    // one item per slot of the grid between a tensor's last parked item and its streamed
+    // update items.
+    l->lead_elems = 8ll << 20;
+    l->gap_items = 0;
     rc = rebuild_lans_schedule(l);
   } while (false);
   if (rc != RAFB200_OK) {
@@ -168,22 +186,23 @@ int rafb200_tensor_list_destroy(rafb200_tensor_list_t l) {
   if (!l) return RAFB200_OK;
   if (l->dev_desc) cudaFree(l->dev_desc);
   if (l->dev_items) cudaFree(l->dev_items);
-  if (l->dev_lans_items) cudaFree(l->dev_lans_items);
-  if (l->dev_lans_items_nonorm) cudaFree(l->dev_lans_items_nonorm);
+  if (l->dev_lans_lists) cudaFree(l->dev_lans_lists);
+  if (l->dev_lans_lists_nonorm) cudaFree(l->dev_lans_lists_nonorm);
   delete l;
   return RAFB200_OK;
 }
 
 int64_t rafb200_tensor_list_total_elems(rafb200_tensor_list_t l) { return l ? l->total_elems : 0; }
 
-int rafb200_tensor_list_tune(rafb200_tensor_list_t l, int64_t window_elems, int slack_items,
+int rafb200_tensor_list_tune(rafb200_tensor_list_t l, int64_t lead_elems, int gap_items,
                              int max_blocks) {
   RAFB200_REQUIRE(l, "rafb200_tensor_list_tune: NULL list");
-  RAFB200_REQUIRE(window_elems >= 0 && slack_items >= 0 && max_blocks >= 0,
+  RAFB200_REQUIRE(lead_elems >= 0 && gap_items >= 0 && max_blocks >= 0,
                   "rafb200_tensor_list_tune: negative argument");
-  const bool resched = (window_elems != l->window_elems) || (slack_items != l->slack_items);
-  l->window_elems = window_elems;
-  l->slack_items = slack_items;
+  const bool resched = (lead_elems != l->lead_elems) || (gap_items != l->gap_items) ||
+                       (max_blocks != l->max_blocks) || l->custom_items;
+  l->lead_elems = lead_elems;
+  l->gap_items = gap_items;
   l->max_blocks = max_blocks;
   if (resched) {
     // The old tables may still be read by a kernel in flight.
@@ -191,6 +210,32 @@ int rafb200_tensor_list_tune(rafb200_tensor_list_t l, int64_t window_elems, int 
     return rebuild_lans_schedule(l);
   }
   return RAFB200_OK;
+}
+
+int rafb200_tensor_list_set_wait_limit(rafb200_tensor_list_t l, int limit_ms) {
+  RAFB200_REQUIRE(l && limit_ms > 0, "rafb200_tensor_list_set_wait_limit: bad arguments");
+  l->wait_ns = (uint64_t)limit_ms * 1000000ull;
+  return RAFB200_OK;
+}
+
+int rafb200_tensor_list_set_lans_items(rafb200_tensor_list_t l, const uint32_t* items, size_t count) {
+  RAFB200_REQUIRE(l && (count == 0 || items), "rafb200_tensor_list_set_lans_items: bad arguments");
+  RAFB200_REQUIRE(count < (1ull << 32), "rafb200_tensor_list_set_lans_items: too many items");
+  std::vector<Item> v(count);
+  for (size_t i = 0; i < count; ++i) {
+    v[i] = Item{items[2 * i], items[2 * i + 1]};
+    const uint32_t t = v[i].tensor_phase & kTensorMask, kind = v[i].tensor_phase >> kPhaseShift;
+    RAFB200_REQUIRE((int)t < l->k, "rafb200_tensor_list_set_lans_items: item %zu names tensor %u", i, t);
+    const int64_t per = kind == kKindA ? lans_a_elems(l->g_dtype) : kLansElems;
+    RAFB200_REQUIRE((int64_t)v[i].chunk * per < l->numel[t],
+                    "rafb200_tensor_list_set_lans_items: item %zu is past the end of tensor %u", i, t);
+  }
+  RAFB200_CUDA(cudaDeviceSynchronize());  // the old tables may still be read by a kernel in flight
+  int rc = upload_lists(v, l->lans_grid, &l->dev_lans_lists);
+  if (rc != RAFB200_OK) return rc;
+  rc = upload_lists(v, l->lans_grid, &l->dev_lans_lists_nonorm);
+  l->custom_items = true;
+  return rc;
 }
 
 }  // extern "C"

@@ -92,11 +92,7 @@ struct LansStage1 {
     } else {
       m = fmaf(beta3, sg, m * beta1);
       v = fmaf(one_minus_beta2 * sg, sg, v * beta2);
-#ifdef RAFB200_PROBE_NOMUFU
-      const float r = v * inv_bc2 + eps;
-#else
       const float r = rcp_approx(sqrt_approx(v * inv_bc2) + eps);
-#endif
       const float sp = wd * p;
       um = fmaf(m * inv_bc1, r, sp);
       ug = fmaf(sg, r, sp);

@@ -163,6 +163,20 @@ struct rafb200_zero_s {
   void* p_mc = nullptr;
   char* g_red = nullptr;             // this rank's reduced gradient blocks (plain local memory)
   unsigned int* dev_err = nullptr;   // first expired cross-GPU wait, 0 if none
+  // The same word as the host sees it without synchronising: pinned, mapped memory that the
+  // barrier kernel stores to when it gives up, read at the top of every step.
+  volatile unsigned int* host_err = nullptr;
+  unsigned int* host_err_dev = nullptr;  // device address of *host_err
+  uint64_t wait_limit_ns = 10000000000ull;
+  int host_output = 0;               // 0: full parameters to the host, 1: this rank's row blocks
+  std::vector<const void*> shard_g;  // per tensor: where the update reads its gradient block
+  // ranges the caller declared to be single allocations: copies may be merged inside them
+  std::vector<std::pair<const char*, size_t>> arenas;
+  bool in_one_arena(const void* lo, const void* hi) const {  // [lo, hi) inside one declared range
+    for (const auto& a : arenas)
+      if (static_cast<const char*>(lo) >= a.first && static_cast<const char*>(hi) <= a.first + a.second) return true;
+    return false;
+  }
   uint32_t epoch[2] = {0, 0};        // barrier lanes: 0 before reduce-scatter, 1 after all-gather
   cudaStream_t gather_stream = nullptr;
   cudaEvent_t ev_gather = nullptr;
@@ -268,6 +282,7 @@ int rafb200_zero_destroy(rafb200_zero_t z) {
   if (z->g_flat && !z->symmetric) rafb200_comm_free(z->comm, z->g_flat);
   if (z->p_flat && !z->symmetric) rafb200_comm_free(z->comm, z->p_flat);
   if (z->dev_err) cudaFree(z->dev_err);
+  if (z->host_err) cudaFreeHost(const_cast<unsigned int*>(z->host_err));
   if (z->g_red) cudaFree(z->g_red);
   if (z->gather_stream) cudaStreamDestroy(z->gather_stream);
   if (z->ev_gather) cudaEventDestroy(z->ev_gather);
@@ -482,6 +497,10 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
                              cnt * ps, 0});
       }
     }
+    if (counted) {
+      z->shard_g.resize(k);
+      for (size_t j = 0; j < nt; ++j) z->shard_g[b.tensors[j]] = lg[j];
+    }
     int rc = rafb200_tensor_list_bind(b.list, lg.data(), lp.data(), lm.data(), v ? lv.data() : nullptr,
                                       lo.data(), nullptr);
     if (rc != RAFB200_OK) return rc;
@@ -553,6 +572,15 @@ int rafb200_zero_attach_symmetric(rafb200_zero_t z, void* const* g_peer, void* g
   RAFB200_CUDA(cudaMalloc(reinterpret_cast<void**>(&z->g_red),
                           (size_t)(z->flat_elems / z->n + 8) * dtype_size(z->g_dtype)));
   RAFB200_CUDA(cudaMemset(z->dev_err, 0, 16));
+  {
+    void* h = nullptr;
+    RAFB200_CUDA(cudaHostAlloc(&h, 64, cudaHostAllocMapped));
+    memset(h, 0, 64);
+    z->host_err = static_cast<volatile unsigned int*>(h);
+    void* d = nullptr;
+    RAFB200_CUDA(cudaHostGetDevicePointer(&d, h, 0));
+    z->host_err_dev = static_cast<unsigned int*>(d);
+  }
   RAFB200_CUDA(cudaStreamCreateWithFlags(&z->gather_stream, cudaStreamNonBlocking));
   RAFB200_CUDA(cudaEventCreateWithFlags(&z->ev_gather, cudaEventDisableTiming));
   // The NCCL-registered buffers of rafb200_zero_create are not needed in this mode.
@@ -587,16 +615,46 @@ int rafb200_zero_arena_offsets(rafb200_zero_t z, int64_t* elem_offset, int* natu
   return RAFB200_OK;
 }
 
+static int wait_expired(unsigned int e) {
+  return set_error(RAFB200_DEVICE_WAIT_EXPIRED,
+                   "rafb200_zero_step: rank %u did not reach barrier lane %u within the limit; the "
+                   "ranks are out of step, destroy this state on every rank and create it again",
+                   e & 15u, (e >> 4) & 15u);
+}
+
 int rafb200_zero_status(rafb200_zero_t z) {
   RAFB200_REQUIRE(z, "rafb200_zero_status: NULL state");
   RAFB200_CUDA(cudaDeviceSynchronize());
   if (!z->dev_err) return RAFB200_OK;
   unsigned int e = 0;
   RAFB200_CUDA(cudaMemcpy(&e, z->dev_err, sizeof(e), cudaMemcpyDeviceToHost));
-  if (e != 0)
-    return set_error(RAFB200_DEVICE_WAIT_EXPIRED,
-                     "rafb200_zero_step: rank %u did not reach barrier lane %u within the limit",
-                     e & 15u, (e >> 4) & 15u);
+  if (e != 0) return wait_expired(e);
+  return RAFB200_OK;
+}
+
+int rafb200_zero_set_wait_limit(rafb200_zero_t z, int limit_ms) {
+  RAFB200_REQUIRE(z && limit_ms > 0, "rafb200_zero_set_wait_limit: bad arguments");
+  z->wait_limit_ns = (uint64_t)limit_ms * 1000000ull;
+  return RAFB200_OK;
+}
+
+int rafb200_zero_set_host_output(rafb200_zero_t z, int mode) {
+  RAFB200_REQUIRE(z && (mode == 0 || mode == 1), "rafb200_zero_set_host_output: mode must be 0 or 1");
+  z->host_output = mode;
+  return RAFB200_OK;
+}
+
+int rafb200_zero_declare_arena(rafb200_zero_t z, const void* base, size_t bytes) {
+  RAFB200_REQUIRE(z && base && bytes > 0, "rafb200_zero_declare_arena: bad arguments");
+  z->arenas.emplace_back(static_cast<const char*>(base), bytes);
+  return RAFB200_OK;
+}
+
+int rafb200_zero_shard_grad(rafb200_zero_t z, int tensor, const void** ptr) {
+  RAFB200_REQUIRE(z && ptr, "rafb200_zero_shard_grad: NULL argument");
+  RAFB200_REQUIRE(z->bound, "rafb200_zero_shard_grad: bind buffers first");
+  RAFB200_REQUIRE(tensor >= 0 && tensor < z->plan.k, "rafb200_zero_shard_grad: no tensor %d", tensor);
+  *ptr = z->shard_g[tensor];
   return RAFB200_OK;
 }
 
@@ -604,7 +662,7 @@ int rafb200_zero_set_update_blocks(rafb200_zero_t z, int max_blocks) {
   RAFB200_REQUIRE(z && max_blocks >= 0, "rafb200_zero_set_update_blocks: bad arguments");
   z->max_update_blocks = max_blocks;
   for (auto& b : z->buckets) {
-    int rc = rafb200_tensor_list_tune(b.list, b.list->window_elems, b.list->slack_items, max_blocks);
+    int rc = rafb200_tensor_list_tune(b.list, b.list->lead_elems, b.list->gap_items, max_blocks);
     if (rc != RAFB200_OK) return rc;
   }
   return RAFB200_OK;
@@ -646,6 +704,9 @@ static int step_impl(rafb200_zero_t z, const rafb200_hyper* h, int step, void* c
   RAFB200_REQUIRE(z && h, "rafb200_zero_step: NULL argument");
   RAFB200_REQUIRE(z->bound, "rafb200_zero_step: bind buffers first");
   RAFB200_REQUIRE(h->optimizer == z->optimizer, "rafb200_zero_step: optimizer differs from the one created");
+  // A barrier of an earlier step gave up: the ranks are no longer in step and every later
+  // barrier would pass without waiting.  Queue nothing more.
+  if (z->host_err && *z->host_err != 0) return wait_expired(*z->host_err);
   cudaStream_t cs = static_cast<cudaStream_t>(compute_stream);
   cudaStream_t ms = static_cast<cudaStream_t>(comm_stream);
   // A mean over ranks is a sum on the wire and a 1/n folded into the update's
@@ -662,10 +723,34 @@ static int step_impl(rafb200_zero_t z, const rafb200_hyper* h, int step, void* c
     RAFB200_CUDA(cudaStreamWaitEvent(z->h2d_stream, z->ev_start, 0));
     RAFB200_CUDA(cudaStreamWaitEvent(z->d2h_stream, z->ev_start, 0));
     for (auto& b : bl) {
-      for (int i : b.tensors)
-        if (z->plan.numel[i])
-          RAFB200_CUDA(cudaMemcpyAsync(z->grads[i], grads_host[i], (size_t)z->plan.numel[i] * gs,
-                                       cudaMemcpyHostToDevice, z->h2d_stream));
+      // Tensors that follow one another in host AND device memory, inside ranges the caller
+      // declared to be single allocations, travel as one copy: a caller that keeps its
+      // gradients (parameters) in one arena per side pays one copy per bucket and direction
+      // instead of one per tensor.  (A copy must not span two allocations, however close.)
+      const char *run_src = nullptr;
+      char* run_dst = nullptr;
+      size_t run = 0;
+      auto flush = [&]() -> int {
+        if (run) RAFB200_CUDA(cudaMemcpyAsync(run_dst, run_src, run, cudaMemcpyHostToDevice, z->h2d_stream));
+        run = 0;
+        return RAFB200_OK;
+      };
+      for (int i : b.tensors) {
+        const size_t bytes = (size_t)z->plan.numel[i] * gs;
+        if (!bytes) continue;
+        const char* src = static_cast<const char*>(grads_host[i]);
+        char* dst = static_cast<char*>(z->grads[i]);
+        if (run && src == run_src + run && dst == run_dst + run && z->in_one_arena(run_src, src + bytes) &&
+            z->in_one_arena(run_dst, dst + bytes)) {
+          run += bytes;
+          continue;
+        }
+        if (int rc = flush()) return rc;
+        run_src = src;
+        run_dst = dst;
+        run = bytes;
+      }
+      if (int rc = flush()) return rc;
       RAFB200_CUDA(cudaEventRecord(b.h2d_done, z->h2d_stream));
     }
   }
@@ -673,11 +758,36 @@ static int step_impl(rafb200_zero_t z, const rafb200_hyper* h, int step, void* c
     if (!host) return RAFB200_OK;
     RAFB200_CUDA(cudaEventRecord(b.out_ready, cs));
     RAFB200_CUDA(cudaStreamWaitEvent(z->d2h_stream, b.out_ready, 0));
-    for (int i : b.tensors)
-      if (z->plan.numel[i])
-        RAFB200_CUDA(cudaMemcpyAsync(params_host[i], z->params[i], (size_t)z->plan.numel[i] * ps,
-                                     cudaMemcpyDeviceToHost, z->d2h_stream));
-    return RAFB200_OK;
+    const char* run_src = nullptr;
+    char* run_dst = nullptr;
+    size_t run = 0;
+    auto flush = [&]() -> int {
+      if (run) RAFB200_CUDA(cudaMemcpyAsync(run_dst, run_src, run, cudaMemcpyDeviceToHost, z->d2h_stream));
+      run = 0;
+      return RAFB200_OK;
+    };
+    for (int i : b.tensors) {
+      // what leaves: the whole parameter, or (host_output 1) the rows this rank owns
+      int64_t lo = 0, hi = z->plan.numel[i];
+      if (z->host_output == 1 && z->n > 1) {
+        lo = std::min<int64_t>(hi, (int64_t)z->rank * z->plan.shard_elems[i]);
+        hi = std::min<int64_t>(hi, lo + z->plan.shard_elems[i]);
+      }
+      const size_t bytes = (size_t)(hi - lo) * ps;
+      if (!bytes) continue;
+      const char* src = static_cast<const char*>(z->params[i]) + (size_t)lo * ps;
+      char* dst = static_cast<char*>(params_host[i]) + (size_t)lo * ps;
+      if (run && src == run_src + run && dst == run_dst + run && z->in_one_arena(run_src, src + bytes) &&
+          z->in_one_arena(run_dst, dst + bytes)) {
+        run += bytes;
+        continue;
+      }
+      if (int rc = flush()) return rc;
+      run_src = src;
+      run_dst = dst;
+      run = bytes;
+    }
+    return flush();
   };
   auto finish = [&]() -> int {  // the compute stream ends the step for the caller
     if (!host) return RAFB200_OK;
@@ -718,7 +828,8 @@ static int step_impl(rafb200_zero_t z, const rafb200_hyper* h, int step, void* c
                                     b.slot_elems, z->g_dtype, "sum", ms);
       if ((z->stage_mask & 2) && z->symmetric) {
         // every rank has packed this bucket -> sum this rank's slot over all ranks, in place
-        rc = symm_barrier(z->sig_peers, z->n, z->rank, 0, ++z->epoch[0], z->dev_err, ms);
+        rc = symm_barrier(z->sig_peers, z->n, z->rank, 0, ++z->epoch[0], z->wait_limit_ns, z->dev_err,
+                          z->host_err_dev, ms);
         if (rc != RAFB200_OK) return rc;
         rc = symm_reduce_scatter(z->g_peers, z->g_mc, z->g_red, b.dev_rs_segs, b.dev_rs_items, b.n_rs_items,
                                  z->g_dtype, z->n, z->comm_blocks, ms);
@@ -744,7 +855,8 @@ static int step_impl(rafb200_zero_t z, const rafb200_hyper* h, int step, void* c
                             z->rank, z->comm_blocks, as);
         if (rc != RAFB200_OK) return rc;
         // every rank's slot has landed here before the unpack reads the buffer
-        rc = symm_barrier(z->sig_peers, z->n, z->rank, 1, ++z->epoch[1], z->dev_err, as);
+        rc = symm_barrier(z->sig_peers, z->n, z->rank, 1, ++z->epoch[1], z->wait_limit_ns, z->dev_err,
+                          z->host_err_dev, as);
       }
       if (rc != RAFB200_OK) return rc;
       RAFB200_CUDA(cudaEventRecord(b.ag_done, as));

@@ -82,17 +82,22 @@ class TensorList:
             ptrs(v, torch.float32), ptrs(out, self.out_dtype), stream_ptr(stream)))
         self._keep = (g, p, m, v, out)  # the device table holds raw pointers
 
-    def tune(self, window_elems=None, slack_items=None, max_blocks=0):
-        lib = _lib.load()
-        # None keeps the value chosen at creation: read it back through a no-op tune is not
-        # possible in the C ABI, so the defaults are restated here.
-        if window_elems is None:
-            window_elems = 32 << 20
-        if slack_items is None:
-            props = torch.cuda.get_device_properties(torch.cuda.current_device())
-            slack_items = 8 * props.multi_processor_count
-        check(lib.rafb200_tensor_list_tune(self.handle, int(window_elems), int(slack_items),
-                                           int(max_blocks)))
+    def tune(self, lead_elems=8 << 20, gap_items=0, max_blocks=0):
+        """Scheduling knobs of the LANS kernel (rafb200_tensor_list_tune); the defaults are
+        the ones a list is created with."""
+        check(_lib.load().rafb200_tensor_list_tune(self.handle, int(lead_elems), int(gap_items),
+                                                   int(max_blocks)))
+
+    def set_wait_limit(self, limit_ms: int):
+        """Bound of every wait inside the LANS kernel (default 2 s)."""
+        check(_lib.load().rafb200_tensor_list_set_wait_limit(self.handle, int(limit_ms)))
+
+    def set_lans_items(self, items):
+        """Replace the LANS work-item table: ``items`` is an (n, 2) uint32 array."""
+        import numpy as np
+
+        a = np.ascontiguousarray(items, np.uint32).reshape(-1, 2)
+        check(_lib.load().rafb200_tensor_list_set_lans_items(self.handle, a.ctypes.data, a.shape[0]))
 
     def lans_workspace(self) -> torch.Tensor:
         if self._ws is None:

@@ -1,5 +1,4 @@
-"""ZeRO plan and step driver bindings, and the parameter-shape tables of the
-benchmark workloads."""
+"""ZeRO plan and step driver bindings."""
 from __future__ import annotations
 
 import ctypes as C
@@ -86,6 +85,18 @@ def make_hyper(optimizer: str, **kw) -> Hyper:
     h.grad_scale = kw.get("grad_scale", 1.0)
     h.average = int(kw.get("average", 1))
     return h
+
+
+class _DevMem:
+    """Exposes a raw device range through __cuda_array_interface__ (no ownership)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+def _device_view(ptr: int, nbytes: int, dtype) -> torch.Tensor:
+    return torch.as_tensor(_DevMem(ptr, nbytes), device="cuda").view(dtype)
 
 
 class ZeroStep:
@@ -176,6 +187,7 @@ class ZeroStep:
             pa([b + p_off for b in bases]), (mc + p_off) if mc else None,
             pa([b + sig_off for b in bases]), int(comm_blocks)))
         self._symm = (buf, handle)  # keeps the mapping alive
+        self.declare_arena(buf)
         self._arena = (g_off, p_off)
         self.multicast = bool(mc)
 
@@ -208,6 +220,31 @@ class ZeroStep:
         """Synchronise the device; raise if a bounded cross-GPU wait of a step ran out."""
         check(_lib.load().rafb200_zero_status(self.handle))
 
+    def set_wait_limit(self, limit_ms: int):
+        """Bound of every cross-GPU wait of the symmetric mode (default 10 s)."""
+        check(_lib.load().rafb200_zero_set_wait_limit(self.handle, int(limit_ms)))
+
+    def declare_arena(self, tensor: torch.Tensor):
+        """Declare the memory of ``tensor`` (host or device) to be one allocation, so that
+        step_host may merge the copies of adjacent tensors inside it."""
+        check(_lib.load().rafb200_zero_declare_arena(self.handle, tensor.data_ptr(),
+                                                     tensor.numel() * tensor.element_size()))
+
+    def set_host_output(self, mode: int):
+        """step_host copies back 0: every parameter in full, 1: this rank's rows only."""
+        check(_lib.load().rafb200_zero_set_host_output(self.handle, int(mode)))
+
+    def shard_grad(self, i: int) -> torch.Tensor:
+        """The gradient block the update of tensor ``i`` reads (this rank's reduced row
+        block when there is more than one rank), as a 1-D view of device memory."""
+        ptr = C.c_void_p()
+        check(_lib.load().rafb200_zero_shard_grad(self.handle, int(i), C.byref(ptr)))
+        n = int(self.plan.shard_elems[i])
+        es = torch.empty((), dtype=self.g_dtype).element_size()
+        if n == 0 or not ptr.value:
+            return torch.empty(0, dtype=self.g_dtype, device="cuda")
+        return _device_view(ptr.value, n * es, self.g_dtype)
+
     def set_stage_mask(self, mask: int):
         """Measurement aid: bit 0 pack, 1 reduce-scatter, 2 update, 3 all-gather, 4 unpack."""
         check(_lib.load().rafb200_zero_set_stage_mask(self.handle, int(mask)))
@@ -226,59 +263,6 @@ class ZeroStep:
             self.close()
         except Exception:
             pass
-
-
-# --------------------------------------------------------------------------- workloads
-def resnet50_shapes() -> List[Tuple[int, ...]]:
-    """161 parameter tensors, 25,557,032 elements: conv weights O x I x k x k, a
-    (gamma, beta) pair after every conv, fc 1000 x 2048 + bias."""
-    shapes: List[Tuple[int, ...]] = []
-
-    def conv_bn(o, i, k):
-        shapes.append((o, i, k, k))
-        shapes.append((o,))
-        shapes.append((o,))
-
-    conv_bn(64, 3, 7)
-    inplanes = 64
-    for planes, blocks in ((64, 3), (128, 4), (256, 6), (512, 3)):
-        for b in range(blocks):
-            conv_bn(planes, inplanes, 1)
-            conv_bn(planes, planes, 3)
-            conv_bn(planes * 4, planes, 1)
-            if b == 0:
-                conv_bn(planes * 4, inplanes, 1)  # downsample
-            inplanes = planes * 4
-    shapes.append((1000, 2048))
-    shapes.append((1000,))
-    return shapes
-
-
-def bert_large_shapes() -> List[Tuple[int, ...]]:
-    """391 tensors, 335,141,888 elements (24 layers, hidden 1024, FFN 4096, vocab 30522)."""
-    h, ffn = 1024, 4096
-    shapes: List[Tuple[int, ...]] = [(30522, h), (512, h), (2, h), (h,), (h,)]
-    for _ in range(24):
-        for _ in range(4):
-            shapes += [(h, h), (h,)]
-        shapes += [(h,), (h,)]
-        shapes += [(ffn, h), (ffn,), (h, ffn), (h,)]
-        shapes += [(h,), (h,)]
-    shapes += [(h, h), (h,)]
-    return shapes
-
-
-def gpt2_medium_shapes() -> List[Tuple[int, ...]]:
-    """292 tensors, 354,823,168 elements (24 layers, d_model 1024, vocab 50257, ctx 1024)."""
-    d = 1024
-    shapes: List[Tuple[int, ...]] = [(50257, d), (1024, d)]
-    for _ in range(24):
-        shapes += [(d,), (d,)]
-        shapes += [(d, 3 * d), (3 * d,), (d, d), (d,)]
-        shapes += [(d,), (d,)]
-        shapes += [(d, 4 * d), (4 * d,), (4 * d, d), (d,)]
-    shapes += [(d,), (d,)]
-    return shapes
 
 
 def numel(shape) -> int:

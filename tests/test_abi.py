@@ -43,7 +43,8 @@ def test_version_and_error_string(lib):
 
 @pytest.mark.parametrize("n_ranks", [1, 2, 4, 8])
 def test_plan_geometry_matches_oracle(n_ranks):
-    from raf_b200.zero import Plan, bert_large_shapes, gpt2_medium_shapes, numel, resnet50_shapes
+    from bench import bert_large_shapes, gpt2_medium_shapes, numel, resnet50_shapes
+    from raf_b200.zero import Plan
 
     for shapes, bucket in ((resnet50_shapes(), 6553600), (bert_large_shapes(), 13107200),
                            (gpt2_medium_shapes(), 13107200), ([(7, 3), (1,), (0, 4), (9,)], 10)):
@@ -63,7 +64,8 @@ def test_plan_geometry_matches_oracle(n_ranks):
 
 
 def test_plan_sizes_of_the_benchmark_configs():
-    from raf_b200.zero import Plan, bert_large_shapes, gpt2_medium_shapes, resnet50_shapes
+    from bench import bert_large_shapes, gpt2_medium_shapes, resnet50_shapes
+    from raf_b200.zero import Plan
 
     rn = Plan(resnet50_shapes(), 8, 0, 6553600)
     assert (rn.k, rn.total_elems, rn.total_padded, rn.num_buckets) == (161, 25557032, 25557032, 5)

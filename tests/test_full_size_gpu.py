@@ -1,12 +1,10 @@
 """Parity at the full sizes of the benchmark configurations.
 
-Config 1 (one flat fp32 tensor of 25,557,032 elements, SGD-momentum, 10 steps) runs always: the
-oracle needs a fraction of a second per step, so every element is compared, bit for bit.
-The BERT-large LANS and GPT-2-medium Adam lists at full size (about 10 GB of host arrays and half
-a minute each) run when RAFB200_FULL_SIZE_TESTS=1.
+Config 1 (one flat fp32 tensor of 25,557,032 elements, SGD-momentum, 10 steps): every element
+is compared, bit for bit.  Config 3 (the BERT-large LANS list, 335,141,888 elements) and config 4
+(the GPT-2-medium Adam list, 354,823,168 elements): one step over the whole list, every element
+compared.  Config 5: one flat tensor of 64 Mi and of 512 Mi elements, windows and strided samples.
 """
-import os
-
 import numpy as np
 import pytest
 import torch
@@ -15,8 +13,6 @@ from oracle import oracle as O
 from tests.util import bits_equal, make_grad, to_numpy, to_torch
 
 pytestmark = pytest.mark.gpu
-FULL = pytest.mark.skipif(os.environ.get("RAFB200_FULL_SIZE_TESTS") != "1",
-                          reason="set RAFB200_FULL_SIZE_TESTS=1 (10 GB of host memory, ~1 minute)")
 
 
 def test_config1_flat_sgd_ten_steps_full_size():
@@ -37,10 +33,9 @@ def test_config1_flat_sgd_ten_steps_full_size():
     assert bits_equal(to_numpy(tv), v)
 
 
-@FULL
 def test_config3_bert_large_lans_one_step_full_size():
     from raf_b200 import op
-    from raf_b200.zero import bert_large_shapes, numel
+    from bench import bert_large_shapes, numel
     from tests.test_kernels_gpu import LANS_HYPER, _run_lans_case
 
     numels = [numel(s) for s in bert_large_shapes()]
@@ -49,10 +44,9 @@ def test_config3_bert_large_lans_one_step_full_size():
     assert worst < 1e-5
 
 
-@FULL
 def test_config4_gpt2_medium_adam_one_step_full_size():
     from raf_b200 import op
-    from raf_b200.zero import gpt2_medium_shapes, numel
+    from bench import gpt2_medium_shapes, numel
 
     numels = [numel(s) for s in gpt2_medium_shapes()]
     assert sum(numels) == 354823168
@@ -77,3 +71,45 @@ def test_config4_gpt2_medium_adam_one_step_full_size():
         assert bits_equal(to_numpy(tvs[i]), vs[i]), i
         assert bits_equal(to_numpy(touts[i]), out), i
     tl.close()
+
+
+@pytest.mark.parametrize("mi", [64, 512])
+def test_config5_flat_adam_one_step_full_size(mi):
+    """One flat fp32 tensor of 64 Mi / 512 Mi elements (the largest is 131,072 work items in one
+    tensor, 2 GiB per array).  Adam is element-wise, so three windows of 4 Mi elements (start,
+    an odd offset in the middle, end) are compared bit for bit with the oracle, and float64
+    sums over strided samples of p, m, v catch anything that went wrong in between."""
+    from raf_b200 import op
+
+    n = mi << 20
+    torch.cuda.empty_cache()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(mi)
+    tp = torch.randn(n, generator=gen, device="cuda") * 0.02
+    tg = torch.randn(n, generator=gen, device="cuda") * 1e-3
+    tm = torch.randn(n, generator=gen, device="cuda") * 1e-4
+    tv = torch.rand(n, generator=gen, device="cuda") * 1e-6
+    win = 4 << 20
+    mid = (n // 2 + 12345) | 1
+    windows = [(0, win), (mid, mid + win), (n - win, n)]
+    stride = 4099  # prime: samples fall on every position of the 4096-element work items
+    before = [[to_numpy(t[lo:hi]) for t in (tg, tp, tm, tv)] for lo, hi in windows]
+    samp = [to_numpy(t[::stride]) for t in (tg, tp, tm, tv)]
+    tl = op.TensorList([n], "float32", "float32")
+    tl.bind([tg], [tp], [tm], [tv], None)
+    op.adam_list_(tl, 3, 1e-4, 0.9, 0.95, 1e-8, 1, 0.1, 1)
+    torch.cuda.synchronize()
+    for (lo, hi), (g, p, m, v) in zip(windows, before):
+        O.adam(g, p, m, v, 3, 1e-4, 0.9, 0.95, 1e-8, 1, 0.1, 1)
+        assert bits_equal(to_numpy(tp[lo:hi]), p), (mi, lo)
+        assert bits_equal(to_numpy(tm[lo:hi]), m), (mi, lo)
+        assert bits_equal(to_numpy(tv[lo:hi]), v), (mi, lo)
+    g, p, m, v = samp
+    O.adam(g, p, m, v, 3, 1e-4, 0.9, 0.95, 1e-8, 1, 0.1, 1)
+    for ours, want in ((tp, p), (tm, m), (tv, v)):
+        got = to_numpy(ours[::stride])
+        assert bits_equal(got, want), mi
+        assert float(got.astype(np.float64).sum()) == float(want.astype(np.float64).sum())
+    tl.close()
+    del tp, tg, tm, tv
+    torch.cuda.empty_cache()

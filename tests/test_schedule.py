@@ -1,6 +1,11 @@
-"""Invariants of the LANS work-item order (host only): every (phase, tensor, chunk) exactly
-once, and every item after all items it waits for - the property that makes the persistent
-kernel's in-kernel waits deadlock-free whatever the number of resident blocks."""
+"""Invariants of the LANS work-item order (host only).
+
+Every unit of work exactly once, every item after all items it waits for, the stage-1 items
+in tensor order and no more parked items per tensor than the grid has room for - together the
+properties that make the persistent kernel's in-kernel waits deadlock-free: an item only
+waits for items with smaller tickets, and the earliest tensor with work outstanding can always
+get a slot, because only parked items of that tensor (fewer than there are slots) and items of
+earlier tensors (which complete without it) can occupy the others."""
 import ctypes as C
 
 import numpy as np
@@ -8,59 +13,79 @@ import pytest
 from hypothesis import given, settings
 from hypothesis import strategies as st
 
-CHUNK = 4096
+ELEMS = 1024
+A_ELEMS = {0: 4096, 1: 7168, 2: 7168}  # per gradient dtype code (f32, f16, bf16)
+KIND_A, KIND_BS, KIND_CS, KIND_BCP = 0, 1, 2, 3
 
 
-def schedule(numels, with_norm, window_elems, slack):
+def schedule(numels, g_dtype, with_norm, slots_total, lead_elems, gap_items):
     from raf_b200 import _lib
 
     lib = _lib.load()
     arr = (C.c_int64 * len(numels))(*numels)
     count = C.c_size_t()
-    _lib.check(lib.rafb200_lans_schedule(len(numels), arr, int(with_norm), window_elems, slack, None, 0,
-                                         C.byref(count)))
+    _lib.check(lib.rafb200_lans_schedule(len(numels), arr, g_dtype, int(with_norm), slots_total, lead_elems,
+                                         gap_items, None, 0, C.byref(count)))
     items = np.zeros((count.value, 2), np.uint32)
-    _lib.check(lib.rafb200_lans_schedule(len(numels), arr, int(with_norm), window_elems, slack,
-                                         items.ctypes.data, count.value, C.byref(count)))
+    _lib.check(lib.rafb200_lans_schedule(len(numels), arr, g_dtype, int(with_norm), slots_total, lead_elems,
+                                         gap_items, items.ctypes.data, count.value, C.byref(count)))
     return items[:, 0] >> 30, items[:, 0] & ((1 << 30) - 1), items[:, 1]
 
 
-def check(numels, with_norm, window_elems, slack):
-    phase, tensor, chunk = schedule(numels, with_norm, window_elems, slack)
-    nchunks = [(n + CHUNK - 1) // CHUNK for n in numels]
-    phases = (0, 1, 2) if with_norm else (1, 2)
-    assert len(phase) == sum(nchunks) * len(phases)
-    seen = set(zip(phase.tolist(), tensor.tolist(), chunk.tolist()))
-    assert len(seen) == len(phase)                       # no item twice
-    for ph in phases:                                    # and every expected item present
-        for t, nc in enumerate(nchunks):
-            assert all((ph, t, c) in seen for c in range(nc))
-    last = {}                                            # position of the last item of (phase, tensor)
-    first = {}
-    for pos, key in enumerate(zip(phase.tolist(), tensor.tolist())):
-        last[key] = pos
-        first.setdefault(key, pos)
-    for t, nc in enumerate(nchunks):
-        if nc == 0:
-            continue
-        if with_norm:
-            assert last[(0, t)] < first[(1, t)]          # moments need the gradient norm
-        assert last[(1, t)] < first[(2, t)]              # the update needs the update norms
+def park_cap(slots_total):
+    return max(0, min(slots_total * 13 // 20, slots_total - 4))
+
+
+def check(numels, g_dtype, with_norm, slots_total, lead_elems, gap_items):
+    kind, tensor, chunk = schedule(numels, g_dtype, with_norm, slots_total, lead_elems, gap_items)
+    n_a = [(n + A_ELEMS[g_dtype] - 1) // A_ELEMS[g_dtype] for n in numels]
+    n_b = [(n + ELEMS - 1) // ELEMS for n in numels]
+    cap = park_cap(slots_total)
+    seen = {}
+    for pos, key in enumerate(zip(kind.tolist(), tensor.tolist(), chunk.tolist())):
+        assert key not in seen, f"item {key} twice"
+        seen[key] = pos
+    stage1_tensors = []
+    for t, n in enumerate(numels):
+        a_pos = [seen[(KIND_A, t, c)] for c in range(n_a[t])] if with_norm else []
+        if not with_norm:
+            assert not any(k == KIND_A for k in kind.tolist())
+        parked = [c for c in range(n_b[t]) if (KIND_BCP, t, c) in seen]
+        streamed = [c for c in range(n_b[t]) if (KIND_BS, t, c) in seen]
+        assert sorted(parked + streamed) == list(range(n_b[t]))      # stage 1 of every chunk, once
+        assert len(parked) <= cap and (len(parked) == min(n_b[t], cap))
+        assert all((KIND_CS, t, c) in seen for c in streamed)        # a streamed chunk is updated later
+        assert not any((KIND_CS, t, c) in seen for c in parked)      # a parked one is not loaded again
+        s1_pos = [seen[(KIND_BS, t, c)] for c in streamed] + [seen[(KIND_BCP, t, c)] for c in parked]
+        if s1_pos:
+            stage1_tensors.append((min(s1_pos), max(s1_pos), t))
+            if a_pos:
+                assert max(a_pos) < min(s1_pos)                      # stage 1 needs the gradient norm
+            for c in streamed:
+                assert seen[(KIND_CS, t, c)] > max(s1_pos)           # stage 2 needs the update norms
+            if parked and streamed:                                  # the parked part is the tail
+                assert max(seen[(KIND_BS, t, c)] for c in streamed) < min(seen[(KIND_BCP, t, c)] for c in parked)
+    assert len(seen) == sum(n_a) * (1 if with_norm else 0) + sum(n_b) + sum(
+        1 for k in kind.tolist() if k == KIND_CS)
+    stage1_tensors.sort()
+    for (lo1, hi1, t1), (lo2, hi2, t2) in zip(stage1_tensors, stage1_tensors[1:]):
+        assert hi1 < lo2 and t1 < t2                                 # stage 1 runs tensor by tensor
 
 
 @pytest.mark.parametrize("with_norm", [True, False])
 def test_schedule_of_the_benchmark_shapes(with_norm):
-    from raf_b200.zero import bert_large_shapes, gpt2_medium_shapes, numel
+    from bench import bert_large_shapes, gpt2_medium_shapes, numel
 
-    for shapes in (bert_large_shapes(), gpt2_medium_shapes()):
-        check([numel(s) for s in shapes], with_norm, 32 << 20, 8 * 148)
+    for shapes, g_dtype in ((bert_large_shapes(), 1), (gpt2_medium_shapes(), 2)):
+        check([numel(s) for s in shapes], g_dtype, with_norm, 148 * 15, 8 << 20, 0)
 
 
 @settings(max_examples=60, deadline=None)
 @given(st.lists(st.one_of(st.integers(0, 5), st.integers(0, 70000), st.integers(0, 3_000_000)), min_size=0, max_size=12),
-       st.booleans(), st.sampled_from([0, 1, CHUNK, 1 << 20, 32 << 20]), st.sampled_from([0, 1, 7, 300, 5000]))
-def test_schedule_invariants_random_lists(numels, with_norm, window_elems, slack):
-    check(numels, with_norm, window_elems, slack)
+       st.sampled_from([0, 1, 2]), st.booleans(), st.sampled_from([1, 3, 13, 15, 91, 2220]),
+       st.sampled_from([0, 1, ELEMS, 1 << 20, 8 << 20]), st.sampled_from([0, 1, 7, 300, 5000]))
+def test_schedule_invariants_random_lists(numels, g_dtype, with_norm, slots_total, lead_elems, gap_items):
+    check(numels, g_dtype, with_norm, slots_total, lead_elems, gap_items)
 
 
 def test_schedule_rejects_bad_arguments():
@@ -69,8 +94,10 @@ def test_schedule_rejects_bad_arguments():
     lib = _lib.load()
     count = C.c_size_t()
     neg = (C.c_int64 * 1)(-1)
-    assert lib.rafb200_lans_schedule(1, neg, 1, 0, 0, None, 0, C.byref(count)) == 1
+    assert lib.rafb200_lans_schedule(1, neg, 0, 1, 15, 0, 0, None, 0, C.byref(count)) == 1
     one = (C.c_int64 * 1)(10000)
+    assert lib.rafb200_lans_schedule(1, one, 0, 1, 0, 0, 0, None, 0, C.byref(count)) == 1  # no slots
     small = (C.c_uint32 * 2)()
-    assert lib.rafb200_lans_schedule(1, one, 1, 0, 0, small, 1, C.byref(count)) == 1  # 9 items, room for 1
-    assert count.value == 9
+    # 3 gradient-norm items of 4096 + 10 chunks of 1024, 9 of them parked, 1 streamed twice
+    assert lib.rafb200_lans_schedule(1, one, 0, 1, 15, 0, 0, small, 1, C.byref(count)) == 1
+    assert count.value == 3 + 10 + 1

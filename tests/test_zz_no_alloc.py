@@ -1,10 +1,11 @@
 """rafb200_lans_tensor_static: the one-tensor LANS entry point that allocates nothing.
 
 Called through the C ABI with raw device pointers and compared with the existing
-entry point (rafb200_lans on a one-tensor list) on the same inputs, for two calls in
-a row - the second call finds the shared static array as the first one left it.
-Tolerance: 1e-5 relative, the LANS bar of this suite (the two entry points run the
-same kernel, so in practice they agree far more closely).
+entry point (rafb200_lans on a one-tensor list) AND with the CPU oracle on the same
+inputs, for two calls in a row - the second call finds the shared static array as the
+first one left it.  Tolerance: 1e-5 relative, the LANS bar of this suite (the two entry
+points run the same kernel, so in practice they agree far more closely).  The free
+device memory reported by the driver must be the same before and after the calls.
 
 The file name sorts last on purpose: this test must pass both alone and after every
 other GPU test has used the library in the same process.
@@ -13,7 +14,8 @@ import numpy as np
 import pytest
 import torch
 
-from tests.util import TORCH, make_grad, rel_err, to_numpy, to_torch
+from oracle import oracle as O
+from tests.util import CODES, TORCH, make_grad, rel_err, to_numpy, to_torch
 
 pytestmark = pytest.mark.gpu
 
@@ -55,21 +57,36 @@ def test_static_entry_matches_list_entry_twice(n, g_dtype, out_dtype, mode, norm
 
     pa, ma, va, oa = state()   # existing entry point
     pb, mb, vb, ob = state()   # static-scratch entry point
+    po, mo, vo = p0.copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)  # CPU oracle
     tl = op.TensorList([n], g_dtype, out_dtype or "float32")
+    grads = [make_grad(np.random.default_rng(100 + step), n, g_dtype, loss_scale=1.0 / scale)
+             for step in (1, 2)]
+    tgrads = [to_torch(g, g_dtype) for g in grads]
+    # the first call on a device resolves the address of the static array: make it here, then
+    # compare the driver's free-memory figure right before and right after each call under test
+    # (nothing of torch allocates in between)
+    _lib.check(_static_call(lib, tgrads[0], *state()[:3], None, 1, mode, normalize_grad, scale))
+    torch.cuda.synchronize()
     try:
         for step in (1, 2):
-            g = to_torch(make_grad(np.random.default_rng(100 + step), n, g_dtype,
-                                   loss_scale=1.0 / scale), g_dtype)
+            g = tgrads[step - 1]
             tl.bind([g], [pa], [ma], [va], [oa] if oa is not None else None)
             op.lans_list_(tl, step, HYPER["learning_rate"], HYPER["beta1"], HYPER["beta2"],
                           HYPER["eps"], HYPER["bias_correction"], HYPER["weight_decay"],
                           HYPER["grad_averaging"], mode, normalize_grad, grad_scale=scale)
             op.lans_status(tl)
+            free_mid = torch.cuda.mem_get_info()[0]
             _lib.check(_static_call(lib, g, pb, mb, vb, ob, step, mode, normalize_grad, scale))
             torch.cuda.synchronize()
-            for a, b, name in ((pa, pb, "p"), (ma, mb, "m"), (va, vb, "v")):
+            assert torch.cuda.mem_get_info()[0] == free_mid, "the call changed the free device memory"
+            O.lans([grads[step - 1]], [po], [mo], [vo], step, HYPER["learning_rate"], HYPER["beta1"],
+                   HYPER["beta2"], HYPER["eps"], HYPER["bias_correction"], HYPER["weight_decay"],
+                   HYPER["grad_averaging"], mode, int(normalize_grad), scale)
+            for a, b, ref, name in ((pa, pb, po, "p"), (ma, mb, mo, "m"), (va, vb, vo, "v")):
                 err = rel_err(to_numpy(b), to_numpy(a))
                 assert err < 1e-5, (name, step, err)
+                err = rel_err(to_numpy(b), ref)
+                assert err < 1e-5, ("against the oracle", name, step, err)
             if oa is not None:
                 err = rel_err(to_numpy(ob.float()), to_numpy(oa.float()))
                 assert err < (1e-5 if out_dtype == "float32" else 1e-2), ("out", step, err)
