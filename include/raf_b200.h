@@ -47,7 +47,11 @@ typedef enum {
 
 /* Element types.  The reference's DType codes for the same types are
  * kDLFloat/32, kDLFloat/16 and kDLBfloat/16 (include/raf/device.h:27-36). */
-typedef enum { RAFB200_F32 = 0, RAFB200_F16 = 1, RAFB200_BF16 = 2 } rafb200_dtype;
+typedef enum {
+  RAFB200_F32 = 0, RAFB200_F16 = 1, RAFB200_BF16 = 2,
+  /* collectives only (the NCCL type map of src/op/dialect/nccl/communication_utils.h:31-48): */
+  RAFB200_F64 = 3, RAFB200_I8 = 4, RAFB200_U8 = 5, RAFB200_I64 = 6
+} rafb200_dtype;
 
 RAFB200_API const char* rafb200_last_error(void);
 RAFB200_API int rafb200_version(void);
@@ -137,8 +141,9 @@ RAFB200_API int rafb200_sgd_list(rafb200_tensor_list_t list, float learning_rate
  *    kernels src/op/dialect/cuda/kernels/multi_tensor_lans.cu:95-450).
  * Same argument meaning and per-element formulas.  Differences, all deliberate:
  *   - one persistent launch instead of about fifty.  A chunk of a tensor is
- *     loaded into shared memory once and stays there while the tensor-wide
- *     norms stage 2 needs are completed by the other thread blocks, so every
+ *     loaded into shared memory once and its intermediate results stay on chip
+ *     (in tensor memory) while the tensor-wide norms stage 2 needs are
+ *     completed by the other thread blocks, so every
  *     array is read once and written once; only the part of a tensor that
  *     exceeds what the grid can hold on chip is read a second time.  Per-tensor
  *     norms are reduced warp-shuffle-then-block in the same kernel and summed
@@ -182,15 +187,15 @@ RAFB200_API int rafb200_lans(rafb200_tensor_list_t list, int step, const float* 
  * kind-0 item of their tensor (only with normalize_grad); kind 2 and the second
  * half of kind 3 wait for every kind-1 and kind-3 item of their tensor.  An item
  * only waits for items that come earlier in the order, and at most
- * two thirds of the grid's shared-memory slots (slots_total = blocks x 15 slots
- * for 16-bit gradients, x 13 for fp32) ever hold parked items of one tensor, so a
- * running block only ever waits for items that running blocks hold.  The
+ * four fifths of the grid's parking places (cells_total = blocks x 21 cells of
+ * tensor memory) ever hold parked items of one tensor, so a running block only
+ * ever waits for items that running blocks hold.  The
  * reference has no such object: its six passes are separate launches
  * (multi_tensor_lans.cu:401-450).  lead_elems and gap_items as in
- * rafb200_tensor_list_tune (gap_items 0 = slots_total).
+ * rafb200_tensor_list_tune (gap_items 0 = cells_total).
  * items may be NULL to query *count alone; capacity counts items. */
 RAFB200_API int rafb200_lans_schedule(int k, const int64_t* numel, int g_dtype, int with_norm_phase,
-                                      int slots_total, int64_t lead_elems, int gap_items,
+                                      int cells_total, int64_t lead_elems, int gap_items,
                                       uint32_t* items, size_t capacity, size_t* count);
 /* Synchronises `stream`, then reports whether the last rafb200_lans on this
  * workspace completed (RAFB200_OK) or a bounded device wait expired.
@@ -314,6 +319,19 @@ RAFB200_API int rafb200_comm_destroy(rafb200_comm_t comm);
  * free, set-up-time operation. */
 RAFB200_API int rafb200_comm_alloc(rafb200_comm_t comm, size_t bytes, void** ptr);
 RAFB200_API int rafb200_comm_free(rafb200_comm_t comm, void* ptr);
+/*
+ * Sub-communicators: the `rank_list` argument of raf.op._allreduce / _allgather /
+ * _reduce_scatter (def_schema.py:699-738) - a list of groups of ranks of the global
+ * communicator.  Replaces Communicator::InitSubCommunicator and CommunicatorPool
+ * (src/distributed/common/communicator.cc:21-84, include/raf/communicator.h:104-147):
+ * the result is the communicator of the group that names this rank (rank inside the
+ * group = position in it), or a world of one when no group names it, cached under
+ * the rank list and owned by `comm` (do not destroy it).  group_sizes[n_groups],
+ * ranks[] = the groups one after another.  n_groups 0 returns `comm` itself.  Every
+ * rank of `comm` must make the same call (NCCL splits the communicator collectively).
+ */
+RAFB200_API int rafb200_comm_sub(rafb200_comm_t comm, int n_groups, const int* group_sizes,
+                                 const int* ranks, rafb200_comm_t* sub);
 RAFB200_API int rafb200_comm_size(rafb200_comm_t comm);
 RAFB200_API int rafb200_comm_rank(rafb200_comm_t comm);
 /* Polls NCCL's asynchronous error state (the reference never does). */
@@ -324,8 +342,9 @@ RAFB200_API int rafb200_comm_check(rafb200_comm_t comm);
  * _group_allgather (schemas scripts/src_codegen/def_schema.py:699-738; NCCL
  * dialect src/op/dialect/nccl/nccl.cc:40-399).  `computation` is one of
  * "sum", "prod", "min", "max", "avg" as in nccl.cc:57-72.  Counts are in
- * elements.  dtype may be any rafb200_dtype (bf16 is an addition: the
- * reference's map, communication_utils.h:31-48, has none).
+ * elements.  dtype may be any rafb200_dtype: the six types of the reference's
+ * map (communication_utils.h:31-48) and bf16, which it lacks.  `comm` may be a
+ * sub-communicator from rafb200_comm_sub (the schema's rank_list).
  * reduce_scatter: recvcount elements per rank, rank r receives block r of
  * sendbuf (dim 0 split, src/op/declare/collective_comm.cc:112-158); in place
  * when recvbuf == sendbuf + rank*recvcount.  allgather: in place when
@@ -346,6 +365,34 @@ RAFB200_API int rafb200_allgather(rafb200_comm_t comm, const void* sendbuf, void
 RAFB200_API int rafb200_group_allgather(rafb200_comm_t comm, int k, const void* const* sendbuf,
                                         void* const* recvbuf, const int64_t* sendcount, int dtype,
                                         void* stream);
+
+/*
+ * DistConfig (include/raf/dist_config.h:17-48): the process-wide object the
+ * reference's passes read - same fields and defaults.
+ */
+typedef struct {
+  int scheduling_param;
+  int iteration;
+  int enable_data_parallel;
+  int zero_opt_level;
+  int enable_auto_dp_profiling;
+  int auto_dp_profiling_start_iter;   /* default 2 */
+  int auto_dp_profiling_end_iter;     /* default 4 */
+  int64_t group_bucket_size;          /* default 5,000,000,000 elements */
+} rafb200_dist_config;
+RAFB200_API int rafb200_dist_config_get(rafb200_dist_config* out);
+RAFB200_API int rafb200_dist_config_set(const rafb200_dist_config* in);
+
+/*
+ * Streams by tag (Stream::Get(device, tag, index), src/impl/stream_pool.cc:53-98;
+ * tags of include/raf/stream_pool.h: compute 1, host-to-device 2, device-to-host 3,
+ * communication 4, fuse 5, defuse 6).  Created on first use, one per (device, tag,
+ * index), non-blocking; the same call returns the same stream.  rafb200_zero_step
+ * takes its streams from here when the caller passes NULL (compute: tag 1 index 0,
+ * communication: tag 4 index 0).
+ */
+RAFB200_API int rafb200_stream_get(int device, int tag, int index, void** stream);
+RAFB200_API int rafb200_stream_release_all(void);
 
 /* ------------------------------------------------------------------------- */
 /* ZeRO plan: shard geometry and buckets                                      */

@@ -72,6 +72,11 @@ SIGNATURES = {
     "rafb200_comm_destroy": (_i, [_vp]),
     "rafb200_comm_alloc": (_i, [_vp, _sz, _P(_vp)]),
     "rafb200_comm_free": (_i, [_vp, _vp]),
+    "rafb200_comm_sub": (_i, [_vp, _i, _vp, _vp, _P(_vp)]),
+    "rafb200_dist_config_get": (_i, [_vp]),
+    "rafb200_dist_config_set": (_i, [_vp]),
+    "rafb200_stream_get": (_i, [_i, _i, _i, _P(_vp)]),
+    "rafb200_stream_release_all": (_i, []),
     "rafb200_comm_size": (_i, [_vp]),
     "rafb200_comm_rank": (_i, [_vp]),
     "rafb200_comm_check": (_i, [_vp]),

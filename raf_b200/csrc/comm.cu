@@ -39,6 +39,10 @@ struct rafb200_comm_s {
   };
   std::map<void*, Reg> regs;
   std::string store_file;  // file this rank published (removed on destroy)
+  // sub-communicators by rank list (the reference's CommunicatorPool,
+  // include/raf/communicator.h:104-147), owned by the global communicator
+  std::map<std::vector<int>, rafb200_comm_s*> subs;
+  int timeout_ms = 60000;
 };
 
 namespace rafb200 {
@@ -55,13 +59,26 @@ static int nccl_fail(ncclResult_t r, const char* what) {
     if (r__ != ncclSuccess) return nccl_fail(r__, #expr); \
   } while (0)
 
+// src/op/dialect/nccl/communication_utils.h:31-48 (int8, int64, uint8, f16, f32, f64), plus bf16
 static int to_nccl_dtype(int dtype, ncclDataType_t* out) {
   switch (dtype) {
     case RAFB200_F32: *out = ncclFloat32; return RAFB200_OK;
     case RAFB200_F16: *out = ncclFloat16; return RAFB200_OK;
     case RAFB200_BF16: *out = ncclBfloat16; return RAFB200_OK;
+    case RAFB200_F64: *out = ncclFloat64; return RAFB200_OK;
+    case RAFB200_I8: *out = ncclInt8; return RAFB200_OK;
+    case RAFB200_U8: *out = ncclUint8; return RAFB200_OK;
+    case RAFB200_I64: *out = ncclInt64; return RAFB200_OK;
   }
-  return set_error(RAFB200_INVALID_ARGUMENT, "unsupported dtype %d", dtype);
+  return set_error(RAFB200_INVALID_ARGUMENT, "NotImplementedError: no NCCL type for dtype %d", dtype);
+}
+static size_t comm_dtype_size(int dtype) {
+  switch (dtype) {
+    case RAFB200_F16: case RAFB200_BF16: return 2;
+    case RAFB200_F64: case RAFB200_I64: return 8;
+    case RAFB200_I8: case RAFB200_U8: return 1;
+    default: return 4;
+  }
 }
 
 // "sum" | "prod" | "min" | "max" | "avg"  (src/op/dialect/nccl/nccl.cc:57-72)
@@ -119,38 +136,38 @@ static int store_fetch(const std::string& file, void* data, size_t n, int timeou
   }
 }
 
-// ncclCommInitRank blocks until every rank has joined.  It runs on a helper
-// thread so that a peer that never arrives costs `timeout_ms`, not forever; a
-// helper that is still blocked at the deadline is left behind (it owns its
-// state through the shared_ptr) and the caller gets RAFB200_TIMEOUT.
-struct InitState {
-  std::mutex mu;
-  std::condition_variable cv;
-  bool done = false;
-  ncclResult_t result = ncclSuccess;
-  ncclComm_t comm = nullptr;
-};
+// Communicator creation with a deadline: a non-blocking communicator
+// (ncclCommInitRankConfig, blocking = 0) is polled with ncclCommGetAsyncError until
+// it is ready; a peer that never arrives costs `timeout_ms`, after which the
+// half-built communicator is released with ncclCommAbort and the caller gets
+// RAFB200_TIMEOUT.  (The reference calls the blocking ncclCommInitRank and waits forever,
+// src/distributed/cuda/nccl_communicator.cc:113.)
+static int wait_ready(ncclComm_t comm, int timeout_ms, const char* what) {
+  const auto deadline = Clock::now() + std::chrono::milliseconds(timeout_ms);
+  while (true) {
+    ncclResult_t st = ncclSuccess;
+    ncclResult_t r = ncclCommGetAsyncError(comm, &st);
+    if (r != ncclSuccess) return nccl_fail(r, "ncclCommGetAsyncError");
+    if (st == ncclSuccess) return RAFB200_OK;
+    if (st != ncclInProgress) return nccl_fail(st, what);
+    if (Clock::now() > deadline) return set_error(RAFB200_TIMEOUT, "%s: not every rank joined within %d ms", what, timeout_ms);
+    std::this_thread::sleep_for(std::chrono::milliseconds(2));
+  }
+}
 
 static int init_rank(rafb200_comm_s* c, const ncclUniqueId& id, int timeout_ms) {
-  auto st = std::make_shared<InitState>();
-  const int size = c->size, rank = c->rank, device = c->device;
-  std::thread([st, id, size, rank, device]() {
-    ncclComm_t comm = nullptr;
-    ncclResult_t r = ncclSuccess;
-    if (cudaSetDevice(device) != cudaSuccess) r = ncclUnhandledCudaError;
-    if (r == ncclSuccess) r = ncclCommInitRank(&comm, size, id, rank);
-    std::lock_guard<std::mutex> lk(st->mu);
-    st->result = r;
-    st->comm = comm;
-    st->done = true;
-    st->cv.notify_all();
-  }).detach();
-  std::unique_lock<std::mutex> lk(st->mu);
-  if (!st->cv.wait_for(lk, std::chrono::milliseconds(timeout_ms), [&] { return st->done; }))
-    return set_error(RAFB200_TIMEOUT, "ncclCommInitRank: not every rank joined within %d ms",
-                     timeout_ms);
-  if (st->result != ncclSuccess) return nccl_fail(st->result, "ncclCommInitRank");
-  c->nccl = st->comm;
+  RAFB200_CUDA(cudaSetDevice(c->device));
+  ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+  cfg.blocking = 0;
+  ncclComm_t comm = nullptr;
+  ncclResult_t r = ncclCommInitRankConfig(&comm, c->size, id, c->rank, &cfg);
+  if (r != ncclSuccess && r != ncclInProgress) return nccl_fail(r, "ncclCommInitRankConfig");
+  int rc = wait_ready(comm, timeout_ms, "ncclCommInitRankConfig");
+  if (rc != RAFB200_OK) {
+    if (comm) ncclCommAbort(comm);
+    return rc;
+  }
+  c->nccl = comm;
   return RAFB200_OK;
 }
 
@@ -190,6 +207,7 @@ int rafb200_comm_create_with_id(int world_size, int rank, int device, const void
     c->is_void = false;
     ncclUniqueId id;
     memcpy(&id, id128, sizeof(id));
+    c->timeout_ms = timeout_ms;
     int rc = init_rank(c, id, timeout_ms);
     if (rc != RAFB200_OK) {
       delete c;
@@ -271,6 +289,8 @@ int rafb200_comm_destroy(rafb200_comm_t c) {
   int rc = RAFB200_OK;
   // Buffers the caller forgot to hand back: deregister and free them with the communicator.
   while (!c->regs.empty()) rafb200_comm_free(c, c->regs.begin()->first);
+  for (auto& kv : c->subs) rafb200_comm_destroy(kv.second);
+  c->subs.clear();
   if (c->nccl && !c->borrowed) {
     ncclResult_t r = ncclCommDestroy(c->nccl);
     if (r != ncclSuccess) rc = nccl_fail(r, "ncclCommDestroy");
@@ -315,6 +335,131 @@ int rafb200_comm_free(rafb200_comm_t c, void* ptr) {
   return rc;
 }
 
+int rafb200_comm_sub(rafb200_comm_t c, int n_groups, const int* group_sizes, const int* ranks,
+                     rafb200_comm_t* sub) {
+  RAFB200_REQUIRE(c && sub, "rafb200_comm_sub: NULL argument");
+  *sub = nullptr;
+  if (n_groups == 0) {  // no rank_list: the global communicator itself
+    *sub = c;
+    return RAFB200_OK;
+  }
+  RAFB200_REQUIRE(n_groups > 0 && group_sizes && ranks, "rafb200_comm_sub: bad rank list");
+  // key of the pool: the rank list, flattened with separators
+  std::vector<int> key;
+  int total = 0, my_group = -1, my_rank = -1;
+  for (int g = 0; g < n_groups; ++g) {
+    RAFB200_REQUIRE(group_sizes[g] > 0, "rafb200_comm_sub: empty group %d", g);
+    for (int i = 0; i < group_sizes[g]; ++i) {
+      const int r = ranks[total + i];
+      RAFB200_REQUIRE(r >= 0 && r < c->size, "rafb200_comm_sub: rank %d outside the communicator of %d", r, c->size);
+      if (r == c->rank && my_group < 0) {  // communicator.cc:38-46: the first group that names this rank
+        my_group = g;
+        my_rank = i;
+      }
+      key.push_back(r);
+    }
+    key.push_back(-1);
+    total += group_sizes[g];
+  }
+  auto it = c->subs.find(key);
+  if (it != c->subs.end()) {
+    *sub = it->second;
+    return RAFB200_OK;
+  }
+  auto* s = new rafb200_comm_s();
+  s->device = c->device;
+  s->timeout_ms = c->timeout_ms;
+  if (my_group >= 0) {
+    s->size = group_sizes[my_group];
+    s->rank = my_rank;
+  }  // else: a world of one (communicator.cc:48-58)
+  if (!c->is_void) {
+    // Every rank of the parent takes part in the split; ranks outside every group get no
+    // communicator.  (The reference exchanges one id per group and calls ncclCommInitRank,
+    // nccl_communicator.cc:115-158; ncclCommSplit needs no exchange.)
+    ncclComm_t split = nullptr;
+    ncclResult_t r = ncclCommSplit(c->nccl, my_group >= 0 ? my_group : NCCL_SPLIT_NOCOLOR, my_rank >= 0 ? my_rank : 0,
+                                   &split, nullptr);
+    if (r != ncclSuccess && r != ncclInProgress) {
+      delete s;
+      return nccl_fail(r, "ncclCommSplit");
+    }
+    if (split) {
+      int rc = wait_ready(split, c->timeout_ms, "ncclCommSplit");
+      if (rc != RAFB200_OK) {
+        ncclCommAbort(split);
+        delete s;
+        return rc;
+      }
+    }
+    if (my_group >= 0 && s->size > 1) {
+      s->is_void = false;
+      s->nccl = split;
+    } else if (split) {
+      ncclCommDestroy(split);  // a group of one needs no NCCL underneath
+    }
+  }
+  c->subs[key] = s;
+  *sub = s;
+  return RAFB200_OK;
+}
+
+// ---- DistConfig (include/raf/dist_config.h:17-48): one process-wide object ----------
+static rafb200_dist_config g_dist_config = {0, 0, 0, 0, 0, 2, 4, 5000000000ll};
+
+int rafb200_dist_config_get(rafb200_dist_config* out) {
+  RAFB200_REQUIRE(out, "rafb200_dist_config_get: NULL argument");
+  *out = g_dist_config;
+  return RAFB200_OK;
+}
+
+int rafb200_dist_config_set(const rafb200_dist_config* in) {
+  RAFB200_REQUIRE(in, "rafb200_dist_config_set: NULL argument");
+  RAFB200_REQUIRE(in->zero_opt_level >= 0 && in->zero_opt_level <= 3, "rafb200_dist_config_set: zero_opt_level %d",
+                  in->zero_opt_level);
+  RAFB200_REQUIRE(in->group_bucket_size > 0, "rafb200_dist_config_set: group_bucket_size must be positive");
+  g_dist_config = *in;
+  return RAFB200_OK;
+}
+
+// ---- streams by tag (src/impl/stream_pool.cc:53-98) ---------------------------------
+namespace {
+struct StreamKey {
+  int device, tag, index;
+  bool operator<(const StreamKey& o) const {
+    return device != o.device ? device < o.device : tag != o.tag ? tag < o.tag : index < o.index;
+  }
+};
+std::mutex g_stream_mu;
+std::map<StreamKey, cudaStream_t> g_streams;
+}  // namespace
+
+int rafb200_stream_get(int device, int tag, int index, void** stream) {
+  RAFB200_REQUIRE(stream && device >= 0 && tag >= 0 && index >= 0, "rafb200_stream_get: bad arguments");
+  std::lock_guard<std::mutex> lk(g_stream_mu);
+  const StreamKey key{device, tag, index};
+  auto it = g_streams.find(key);
+  if (it == g_streams.end()) {
+    int prev = 0;
+    RAFB200_CUDA(cudaGetDevice(&prev));
+    RAFB200_CUDA(cudaSetDevice(device));
+    cudaStream_t s = nullptr;
+    cudaError_t e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
+    cudaSetDevice(prev);
+    if (e != cudaSuccess) return set_error(RAFB200_CUDA_ERROR, "cudaStreamCreate: %s", cudaGetErrorString(e));
+    it = g_streams.emplace(key, s).first;
+  }
+  *stream = it->second;
+  return RAFB200_OK;
+}
+
+int rafb200_stream_release_all(void) {
+  std::lock_guard<std::mutex> lk(g_stream_mu);
+  for (auto& kv : g_streams) cudaStreamDestroy(kv.second);
+  g_streams.clear();
+  return RAFB200_OK;
+}
+
 int rafb200_comm_size(rafb200_comm_t c) { return c ? c->size : 0; }
 int rafb200_comm_rank(rafb200_comm_t c) { return c ? c->rank : -1; }
 
@@ -343,7 +488,7 @@ int rafb200_allreduce(rafb200_comm_t c, const void* sendbuf, void* recvbuf, int6
   if (rc == RAFB200_OK) rc = to_nccl_op(computation, &op);
   if (rc != RAFB200_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (c->is_void) return local_copy(sendbuf, recvbuf, (size_t)count * dtype_size(dtype), s);
+  if (c->is_void) return local_copy(sendbuf, recvbuf, (size_t)count * comm_dtype_size(dtype), s);
   RAFB200_NCCL(c, ncclAllReduce(sendbuf, recvbuf, (size_t)count, dt, op, c->nccl, s));
   return RAFB200_OK;
 }
@@ -361,7 +506,7 @@ int rafb200_group_reduce_scatter(rafb200_comm_t c, int k, const void* const* sen
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (c->is_void) {
     for (int i = 0; i < k; ++i) {
-      rc = local_copy(sendbuf[i], recvbuf[i], (size_t)recvcount[i] * dtype_size(dtype), s);
+      rc = local_copy(sendbuf[i], recvbuf[i], (size_t)recvcount[i] * comm_dtype_size(dtype), s);
       if (rc != RAFB200_OK) return rc;
     }
     return RAFB200_OK;
@@ -396,7 +541,7 @@ int rafb200_group_allgather(rafb200_comm_t c, int k, const void* const* sendbuf,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (c->is_void) {
     for (int i = 0; i < k; ++i) {
-      rc = local_copy(sendbuf[i], recvbuf[i], (size_t)sendcount[i] * dtype_size(dtype), s);
+      rc = local_copy(sendbuf[i], recvbuf[i], (size_t)sendcount[i] * comm_dtype_size(dtype), s);
       if (rc != RAFB200_OK) return rc;
     }
     return RAFB200_OK;

@@ -67,11 +67,14 @@ constexpr int kBlockThreads = 256;
 //   Cs   stage 1 again and stage 2 of the same chunk, stores everything
 //   BCp  both on a chunk that stays in shared memory in between ("parked")
 constexpr uint32_t kKindA = 0, kKindBs = 1, kKindCs = 2, kKindBCp = 3;
-constexpr int kLansElems = 1024;      // elements per Bs / Cs / BCp item = one shared-memory slot
-constexpr int kLansAElems16 = 7168;   // gradient elements per A item (what a slot holds), 16-bit g
-constexpr int kLansAElems32 = 4096;   // the same for fp32 gradients
-constexpr int kLansSlots16 = 15;      // slots per block (one block per SM): 15 x 14 KB, 16-bit g
-constexpr int kLansSlots32 = 13;      // 13 x 16 KB, fp32 g
+constexpr int kLansVecs = 2;          // 4-element vectors a consumer thread holds per array per item
+constexpr int kLansElems = 128 * 4 * kLansVecs;  // elements per Bs / Cs / BCp item = one slot (1024)
+constexpr int kLansAElems16 = kLansElems * 7;    // gradient elements per A item (what a slot holds), 16-bit g
+constexpr int kLansAElems32 = kLansElems * 4;    // the same for fp32 gradients
+constexpr int kLansSlots16 = 215040 / (kLansElems * 14);  // slots per block (one block per SM), 16-bit g: 15 x 14 KB
+constexpr int kLansSlots32 = 215040 / (kLansElems * 16);  // fp32 g: 13 x 16 KB
+constexpr int kLansCells = 512 / (12 * kLansVecs);        // parked chunks per block: 21 x 24 columns of tensor memory
+constexpr int kLansNBits = 14;        // bits of an element count inside an item (<= 14336)
 
 // Per-tensor control words of the LANS kernel (zeroed at the start of every call).
 // A norm word is "final" when its top bit is set: the publisher stores the bits of

@@ -58,7 +58,7 @@ constexpr unsigned kErrWaitG = 1, kErrWaitN = 2, kErrRing = 3, kErrData = 4, kEr
 
 struct LansParams {
   const TensorDesc* descs;
-  const uint32_t* block_off;  // block b runs items[block_off[b] .. block_off[b + 1])
+  const uint32_t* block_off;  // list h (2b: even slots of block b, 2b + 1: odd) = items[block_off[h] .. block_off[h + 1])
   const Item* items;
   LansHeader* hdr;
   LansCtl* ctl;
@@ -172,6 +172,45 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// ---- tensor memory as a scratchpad ------------------------------------------------------
+// 32x32b accesses: the 32 threads of a warp address the 32 lanes of the warp's own quarter
+// of tensor memory (lanes 32 * (warp % 4) ...); thread t reads / writes eight consecutive
+// 32-bit columns of lane t.  `taddr` = (first lane of the quarter << 16) | first column.
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const F4& a, const F4& b) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr),
+               "r"(__float_as_uint(a.x[0])), "r"(__float_as_uint(a.x[1])), "r"(__float_as_uint(a.x[2])),
+               "r"(__float_as_uint(a.x[3])), "r"(__float_as_uint(b.x[0])), "r"(__float_as_uint(b.x[1])),
+               "r"(__float_as_uint(b.x[2])), "r"(__float_as_uint(b.x[3]))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, F4& a, F4& b) {
+  uint32_t r0, r1, r2, r3, r4, r5, r6, r7;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3), "=r"(r4), "=r"(r5), "=r"(r6), "=r"(r7)
+               : "r"(taddr)
+               : "memory");
+  a.x[0] = __uint_as_float(r0);
+  a.x[1] = __uint_as_float(r1);
+  a.x[2] = __uint_as_float(r2);
+  a.x[3] = __uint_as_float(r3);
+  b.x[0] = __uint_as_float(r4);
+  b.x[1] = __uint_as_float(r5);
+  b.x[2] = __uint_as_float(r6);
+  b.x[3] = __uint_as_float(r7);
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// kLansVecs vectors of four values each, to / from 4 * kLansVecs consecutive columns
+__device__ __forceinline__ void tmem_st_vecs(uint32_t taddr, const F4 (&a)[kLansVecs]) {
+#pragma unroll
+  for (int i = 0; i < kLansVecs; i += 2) tmem_st8(taddr + 4 * i, a[i], a[i + 1]);
+}
+__device__ __forceinline__ void tmem_ld_vecs(uint32_t taddr, F4 (&a)[kLansVecs]) {
+#pragma unroll
+  for (int i = 0; i < kLansVecs; i += 2) tmem_ld8(taddr + 4 * i, a[i], a[i + 1]);
+}
+constexpr uint32_t kCellColumns = 12 * kLansVecs;  // p, update_m, update_g of a thread's elements
+
 // Bounded wait on an mbarrier that also gives up as soon as any block has reported an
 // error; a timeout reports `code` itself.
 __device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, LansHeader* hdr,
@@ -216,12 +255,15 @@ __device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, LansHea
 constexpr int kGroups = 4;                       // consumer groups per block
 constexpr int kGroupThreads = 128;               // four warps
 constexpr int kConsumerWarps = kGroups * 4;      // 16
-constexpr int kPrefWarp = kConsumerWarps;        // 16: resolves the block's items ahead of their use
-constexpr int kParkWarp = kConsumerWarps + 1;    // 17: finishes parked chunks, serves idle slots
-constexpr int kPubWarp = kConsumerWarps + 2;     // 18: adds partial sums to the tensors' accumulators
-constexpr int kLansThreads = (kConsumerWarps + 3) * 32;  // 608
-constexpr int kQueueDepth = 8;                   // >= 2 x slots per group: never overflows
-constexpr int kRing = 32;                        // resolved items waiting for a slot
+constexpr int kPrefWarp = kConsumerWarps;        // 16, 17: resolve the block's items ahead of their use
+constexpr int kParkWarp = kConsumerWarps + 2;    // 18: finishes parked chunks
+constexpr int kPubWarp = kConsumerWarps + 3;     // 19: adds partial sums to the tensors' accumulators
+constexpr int kLansThreads = (kConsumerWarps + 4) * 32;  // 640
+constexpr int kQueueDepth = 32;                  // > slots per group + parked cells + end marker
+constexpr int kRing = 64;                        // mailboxes: kMailboxes per slot
+constexpr uint32_t kMailboxes = 4;
+constexpr uint32_t kMbEmpty = 0, kMbFull = 1, kMbTaking = 2, kMbIdle = 3;
+constexpr uint32_t kSeqBits = 11, kSeqMask = (1u << kSeqBits) - 1u;  // see partition_lans_items
 constexpr int kBVecs = kLansElems / (kGroupThreads * kVec);  // 2 vectors per thread per chunk
 static_assert(kBVecs * kGroupThreads * kVec == kLansElems, "a chunk is whole passes of a group");
 
@@ -233,7 +275,8 @@ struct __align__(16) SlotMeta {
   float* m;
   float* v;
   void* out;
-  uint32_t n_nbulk;    // low half: elements; high half: leading elements delivered by bulk copy
+  uint32_t n_nbulk;    // bits 12..0 elements; 25..13 leading elements delivered by bulk copy;
+                       // 31..26 tensor-memory cell of a parked item
   uint32_t tensor_op;  // bits 29..0 tensor, bits 31..30 first operation (kOpA, kOpB, kOpBP, kOpC)
   uint32_t nparts;     // arrivals that complete the norm(s) this item adds to
   float cs;            // gradient multiplier  grad_scale / (||g|| + eps)
@@ -257,11 +300,27 @@ struct LansCtrl {
   uint32_t head;        // next ring entry to claim
   uint32_t consumed;    // ring entries copied out (their ring slot may be rewritten)
   uint32_t done_items;  // items of this block that have finished
-  uint32_t free_mask;   // slots without an item that nobody is refilling
+  uint32_t cell_seq;    // parked items that were given a cell so far (they get theirs in list order)
+  uint32_t mb_state[64]; // mailbox kMailboxes * slot + round % kMailboxes, see kMb*
   uint32_t parked_mask; // slots whose chunk waits for its tensor's norms
   uint32_t tail[kGroups];
   uint32_t item_cnt[16], pub_cnt[16], op_cnt[16];  // per slot: parities of its barriers
+  uint32_t cell_free;    // tensor-memory cells nobody holds
+  uint32_t cell_parked;  // cells whose chunk waits for its tensor's norms
+  uint32_t tmem_base;    // address the allocation returned
+  uint32_t cellop_cnt[32], cell_grp[32];  // per cell: parity of its barrier, group that parked it
+  uint32_t stat[8];  // development counters (LANS_TRACE builds)
 };
+
+// What the second half of a parked item needs: where p and the parameter copy go.
+struct __align__(16) CellMeta {
+  float* p;
+  void* out;
+  uint32_t n_nbulk;
+  uint32_t tensor;
+  uint32_t pad_[2];
+};
+static_assert(sizeof(CellMeta) == 32, "CellMeta is 32 bytes");
 
 template <typename GT>
 struct LansGeo {
@@ -271,15 +330,16 @@ struct LansGeo {
   static constexpr int kAElems = sizeof(GT) == 2 ? kLansAElems16 : kLansAElems32;
   static constexpr int kSlots = sizeof(GT) == 2 ? kLansSlots16 : kLansSlots32;
   static_assert(kAElems * (int)sizeof(GT) <= kSlotBytes, "an A item fits a slot");
-  static_assert(kSlots <= 16 && kSlots <= kGroups * (kQueueDepth / 2), "per-slot tables hold 16");
+  static_assert(kSlots <= 16 && kLansVecs % 2 == 0 && kLansCells <= 32, "per-slot tables hold 16");
   static constexpr int kMetaOff = kSlots * kSlotBytes;
   static constexpr int kRingOff = kMetaOff + kSlots * (int)sizeof(SlotMeta);
   static constexpr int kRedOff = kRingOff + kRing * (int)sizeof(SlotMeta);
   static constexpr int kQueueOff = kRedOff + kSlots * (int)sizeof(RedSlot);
-  static constexpr int kCtrlOff = kQueueOff + kGroups * kQueueDepth * 16;
+  static constexpr int kCellOff = kQueueOff + kGroups * kQueueDepth * 16;
+  static constexpr int kCtrlOff = kCellOff + kLansCells * (int)sizeof(CellMeta);
   static constexpr int kBarOff = (kCtrlOff + (int)sizeof(LansCtrl) + 15) & ~15;
-  // barriers: data, done, redfull, redempty per slot; queue entries; end of consumers
-  static constexpr int kNumBars = 4 * kSlots + kGroups * kQueueDepth + 1;
+  // barriers: data, done, redfull, redempty per slot; queue entries; end of consumers; per cell
+  static constexpr int kNumBars = 4 * kSlots + kGroups * kQueueDepth + 1 + kLansCells;
   static constexpr int kTotal = kBarOff + kNumBars * 8;
   static_assert(kTotal <= 232448, "fits the 227 KB of shared memory a block may use");
 };
@@ -304,13 +364,15 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
   const uint32_t bar_redempty = bar_redfull + S * 8;
   const uint32_t bar_queue = bar_redempty + S * 8;
   const uint32_t bar_end = bar_queue + kGroups * kQueueDepth * 8;
+  const uint32_t bar_cell = bar_end + 8;
   const uint32_t data_base = smem_u32(smem);
+  CellMeta* s_cell = reinterpret_cast<CellMeta*>(smem + L::kCellOff);
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const uint32_t list_lo = P.block_off[blockIdx.x], list_hi = P.block_off[blockIdx.x + 1];
-  const uint32_t n_list = list_hi - list_lo;
+  // two lists per block: the entries of its even slots and of its odd slots
+  const uint32_t n_list = P.block_off[2 * blockIdx.x + 2] - P.block_off[2 * blockIdx.x];
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(bar_data + 8 * s, 1);      // whoever starts the item (+ transaction bytes)
@@ -320,11 +382,25 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
     }
     for (int q = 0; q < kGroups * kQueueDepth; ++q) mbar_init(bar_queue + 8 * q, 1);
     mbar_init(bar_end, kConsumerWarps);
+    for (int c = 0; c < kLansCells; ++c) mbar_init(bar_cell + 8 * c, 4);
     memset(ctrl, 0, sizeof(LansCtrl));
-    ctrl->free_mask = (1u << S) - 1u;
+    for (int q = 0; q < S; ++q) ctrl->mb_state[kMailboxes * q] = kMbIdle;  // every slot waits for its first item
+    ctrl->cell_free = (1u << kLansCells) - 1u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  // Tensor memory (256 KB per SM, otherwise unused by this kernel) holds the parked chunks.
+  // The parker warp allocates all 512 columns and gives them back before it leaves.
+  if (warp == kParkWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&ctrl->tmem_base)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = ctrl->tmem_base;
 
   LansStage1 s1 = P.s1;
   if (P.step_dev != nullptr) {  // bias corrections were computed on the device, see above
@@ -334,26 +410,24 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
   const uint64_t pol_keep = make_policy_keep(), pol_stream = make_policy_stream();
 
   // Hands one entry of a group's queue to that group.  Called by a single thread.
+  // `slot` is a shared-memory slot, or - for kOpCP - a tensor-memory cell.
   auto push_op = [&](uint32_t slot, uint32_t op, uint32_t dpar, uint32_t rpar, float cs, float rm, float rg) {
-    const uint32_t grp = slot & 3u;
-    const uint32_t opar = atomicAdd(&ctrl->op_cnt[slot], 1u) & 1u;
+    const uint32_t grp = (op == kOpCP) ? ld_shared_volatile(&ctrl->cell_grp[slot]) : (slot & 3u);
+    const uint32_t opar = atomicAdd(op == kOpCP ? &ctrl->cellop_cnt[slot] : &ctrl->op_cnt[slot], 1u) & 1u;
     const uint32_t tail = atomicAdd(&ctrl->tail[grp], 1u);
     const uint32_t qi = grp * kQueueDepth + (tail % kQueueDepth);
     s_queue[qi] = make_uint4(op | (slot << 3) | (dpar << 8) | (rpar << 9) | (opar << 10), __float_as_uint(cs),
                              __float_as_uint(rm), __float_as_uint(rg));
     mbar_arrive(bar_queue + 8 * qi);
   };
-  // Claims the oldest published ring entry for the (empty) slot `slot`: copies it into the
-  // slot's description, starts the bulk copies and queues the item's first operation.
-  // Returns false when the ring is empty.  Called by a single thread that owns the slot.
-  auto start_next = [&](uint32_t slot) -> bool {
-    if (atomicSub(&ctrl->avail, 1) <= 0) {
-      atomicAdd(&ctrl->avail, 1);
-      return false;
-    }
-    const uint32_t h = atomicAdd(&ctrl->head, 1u) % kRing;
-    __threadfence_block();
-    const uint4* src = reinterpret_cast<const uint4*>(&s_ring[h]);
+  // Every slot has two mailboxes for its next items (rounds of the slot alternate between
+  // them), filled by the prefetcher.  A mailbox is EMPTY, FULL, being TAKEN, or the slot sits
+  // IDLE in front of it: then whoever fills it starts the item himself.
+  //
+  // Starts the item in mailbox `h` of slot `slot`: copies it into the slot's description,
+  // issues the bulk copies and queues the item's first operation.  Called by a single thread.
+  auto start_from_mailbox = [&](uint32_t slot, uint32_t h) {
+    const uint4* src = reinterpret_cast<const uint4*>(&s_ring[kMailboxes * slot + h]);
     uint4* dst = reinterpret_cast<uint4*>(&s_meta[slot]);
     const uint4 e0 = src[0], e1 = src[1], e2 = src[2], e3 = src[3];
     dst[0] = e0;
@@ -361,8 +435,8 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
     dst[2] = e2;
     dst[3] = e3;
     __threadfence_block();
-    atomicAdd(&ctrl->consumed, 1u);
-    const uint32_t op = e2.w >> 30, nbulk = e2.z >> 16;
+    *reinterpret_cast<volatile uint32_t*>(&ctrl->mb_state[kMailboxes * slot + h]) = kMbEmpty;
+    const uint32_t op = e2.w >> 30, nbulk = (e2.z >> kLansNBits) & ((1u << kLansNBits) - 1u);
     const uint32_t dpar = atomicAdd(&ctrl->item_cnt[slot], 1u) & 1u;
     const uint32_t my_data = bar_data + 8 * slot;
     if (nbulk > 0) {
@@ -387,26 +461,50 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
     }
     uint32_t rpar = 0;
     if (op != kOpC) rpar = atomicAdd(&ctrl->pub_cnt[slot], 1u) & 1u;
+    if (op == kOpBP) rpar |= (atomicAdd(&ctrl->cellop_cnt[e2.z >> (2 * kLansNBits)], 1u) & 1u) << 2;  // lands in bit 11
     LANS_TRACE(1u, slot, op);
     push_op(slot, op, dpar, rpar, __uint_as_float(e3.y), __uint_as_float(e3.z), __uint_as_float(e3.w));
-    return true;
+  };
+  // The slot has run empty: take its next item if the prefetcher has it ready, else leave
+  // word that the slot is idle.  Called by a single thread that owns the slot.
+  auto take_next = [&](uint32_t slot) {
+    const uint32_t h = ld_shared_volatile(&ctrl->item_cnt[slot]) % kMailboxes;
+    uint32_t* stp = &ctrl->mb_state[kMailboxes * slot + h];
+    uint32_t old = atomicCAS(stp, kMbFull, kMbTaking);
+    if (old != kMbFull) {
+      old = atomicCAS(stp, kMbEmpty, kMbIdle);
+      if (old == kMbFull) old = atomicCAS(stp, kMbFull, kMbTaking);
+    }
+    if (old == kMbFull) start_from_mailbox(slot, h);
   };
 
-  if (warp == kPrefWarp) {
+  if (warp == kPrefWarp || warp == kPrefWarp + 1) {
     // =============================== prefetcher ===============================
-    // Lane j resolves the entries j, j + 32, ... of the block's list: item -> descriptor of
-    // its tensor (kept while the tensor stays the same) -> the norms the item's first
-    // operation needs, final -> ring.  Entries are published in list order.
-    enum : uint32_t { F_ITEM, F_DESC, F_NORM, F_WRITE, F_PUB, F_DONE };
-    uint32_t e = (uint32_t)lane;
-    uint32_t st = e < n_list ? (uint32_t)F_ITEM : (uint32_t)F_DONE;
-    uint32_t tp = 0, chunk = 0, my_t = 0xffffffffu, pub_next = 0;
+    // The even slots of a block share one list, the odd slots another; the j-th slot of a
+    // parity with S_h slots runs the entries j, j + S_h, j + 2 S_h, ... of its list.  Four lanes
+    // prepare them in turn (round r goes to mailbox r % 4): item -> descriptor of its tensor (kept
+    // while the tensor stays the same) -> the norms the item's first operation needs are
+    // final -> a tensor-memory cell if the item parks -> the slot's mailbox.
+    enum : uint32_t { F_ITEM, F_DESC, F_NORM, F_CELL, F_WRITE, F_DONE };
+    // Two warps: warp w serves the slots s with s % 2 == w, four lanes (mailboxes) per slot,
+    // and hands out its own half of the tensor-memory cells.
+    const uint32_t pw = (uint32_t)(warp - kPrefWarp);
+    const uint32_t slot = 2u * ((uint32_t)lane & 7u) + pw, half = (uint32_t)lane >> 3;
+    const uint32_t my_cells = pw == 0 ? ((1u << ((kLansCells + 1) / 2)) - 1u)
+                                      : (((1u << kLansCells) - 1u) & ~((1u << ((kLansCells + 1) / 2)) - 1u));
+    const uint32_t list_lo = P.block_off[2 * blockIdx.x + pw];
+    const uint32_t my_n = P.block_off[2 * blockIdx.x + pw + 1] - list_lo;
+    const uint32_t S_h = ((uint32_t)S + 1u - pw) / 2u;  // slots of my parity
+    uint32_t e = ((uint32_t)lane & 7u) + S_h * half;    // my entry of the list
+    uint32_t st = (slot < (uint32_t)S && e < my_n) ? (uint32_t)F_ITEM : (uint32_t)F_DONE;
+    uint32_t tp = 0, chunk = 0, seq = 0, my_t = 0xffffffffu, my_cell = 0;
     uint4 d0 = make_uint4(0, 0, 0, 0), d1 = d0, d2 = d0, d3 = d0, nrm = d0;
     bool have_g = false, have_n = false;
     float cs = s1.gscale, rm = 0.f, rg = 0.f;
     uint64_t t_enter = 0;
     const bool normalize = s1.normalize != 0;
     int failed = 0;
+    uint32_t g_base = 0, g_mask = 0;
     for (uint32_t iter = 1;; ++iter) {
       const uint32_t st_in = st;
       // ---- global requests of this iteration, all issued before any is used ----
@@ -447,7 +545,8 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
       }
       if (st_in == F_ITEM) {
         tp = it.x;
-        chunk = it.y;
+        chunk = it.y & ((1u << (32 - kSeqBits)) - 1u);
+        seq = it.y >> (32 - kSeqBits);
         const uint32_t t = tp & kTensorMask;
         if (t != my_t) {
           my_t = t;
@@ -464,86 +563,140 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
       if (st == F_NORM) {
         const bool need_g = normalize && kind != kKindA;
         const bool need_n = kind == kKindCs;
-        if ((!need_g || have_g) && (!need_n || have_n)) st = F_WRITE;
+        if ((!need_g || have_g) && (!need_n || have_n)) st = (kind == kKindBCp) ? (uint32_t)F_CELL : (uint32_t)F_WRITE;
       }
-      if (st == F_WRITE && e < ld_shared_volatile(&ctrl->consumed) + kRing) {
-        const char* dg = reinterpret_cast<const char*>(((uint64_t)d0.y << 32) | d0.x);
-        float* dp = reinterpret_cast<float*>(((uint64_t)d0.w << 32) | d0.z);
-        float* dm = reinterpret_cast<float*>(((uint64_t)d1.y << 32) | d1.x);
-        float* dv = reinterpret_cast<float*>(((uint64_t)d1.w << 32) | d1.z);
-        char* dout = reinterpret_cast<char*>(((uint64_t)d2.y << 32) | d2.x);
-        const int64_t numel = (int64_t)(((uint64_t)d2.w << 32) | d2.z);
-        const uint32_t flags = d3.z;
-        const int per = (kind == kKindA) ? L::kAElems : kLansElems;
-        const int64_t start = (int64_t)chunk * per;
-        const int64_t left = numel - start;
-        const int n = left < per ? (int)left : per;
-        constexpr int gran = 16 / (int)sizeof(GT);  // elements per 16 bytes of gradient
-        const int nbulk = (flags & kFlagBulk) ? (n / gran) * gran : 0;
-        const uint32_t op = kind == kKindA ? kOpA : kind == kKindBs ? kOpB : kind == kKindCs ? kOpC : kOpBP;
-        SlotMeta& mt = s_ring[e % kRing];
-        mt.g = dg + start * (int64_t)sizeof(GT);
-        mt.p = dp + start;
-        mt.m = dm + start;
-        mt.v = dv + start;
-        mt.out = dout ? dout + start * (int64_t)sizeof(OT) : nullptr;
-        mt.n_nbulk = (uint32_t)n | ((uint32_t)nbulk << 16);
-        mt.tensor_op = my_t | (op << 30);
-        mt.nparts = (uint32_t)((numel + per - 1) / per);
-        mt.cs = (op == kOpA) ? s1.gscale : cs;
-        mt.ratio_m = rm;
-        mt.ratio_g = rg;
-        st = F_PUB;
-      }
-      // ---- publish in list order ----
-      const unsigned written = __ballot_sync(0xffffffffu, st == F_PUB);
-      const uint32_t l0 = pub_next & 31u;
-      const unsigned rot = __funnelshift_r(written, written, l0);  // bit i = lane (l0 + i) % 32
-      const int npub = (rot == 0xffffffffu) ? 32 : __ffs(~rot) - 1;
-      if (npub > 0) {
-        __threadfence_block();
-        if (lane == 0) LANS_TRACE(7u, (uint32_t)npub, pub_next);
-        if (lane == 0) atomicAdd(&ctrl->avail, npub);
-        if ((((uint32_t)lane - l0) & 31u) < (uint32_t)npub) {
-          e += kRing;
-          st = e < n_list ? (uint32_t)F_ITEM : (uint32_t)F_DONE;
+      // ---- tensor-memory cells ----
+      // `seq` numbers the parked items of this block in list order.  An item may take a cell
+      // out of turn as long as a free cell remains for every earlier item that has none yet:
+      // then no item ever holds a cell that an earlier one is waiting for.  g_base = lowest
+      // number without a cell, bit i of g_mask = number g_base + i has one (warp-uniform).
+      {
+        const uint32_t off = (seq - g_base) & kSeqMask;
+        const bool asks = st == F_CELL && off < 32u;
+        uint32_t cand = asks ? (1u << off) : 0u;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) cand |= __shfl_xor_sync(0xffffffffu, cand, o);
+        uint32_t free_cells = 0;
+        if (lane == 0) free_cells = ld_shared_volatile(&ctrl->cell_free) & my_cells;
+        free_cells = __shfl_sync(0xffffffffu, free_cells, 0);
+        uint32_t nfree = (uint32_t)__popc(free_cells), newly = 0;
+        for (uint32_t c = cand; c != 0 && nfree > 0; c &= c - 1u) {
+          const uint32_t o = (uint32_t)__ffs(c) - 1u;
+          const uint32_t earlier_without = o - (uint32_t)__popc((g_mask | newly) & ((1u << o) - 1u));
+          if (nfree - 1u < earlier_without) break;  // later numbers have at least as many before them
+          newly |= 1u << o;
+          --nfree;
         }
-        pub_next += (uint32_t)npub;
+        if (newly) {
+          if (asks && ((newly >> off) & 1u)) {
+            my_cell = __fns(free_cells, 0, __popc(newly & ((1u << off) - 1u)) + 1);
+            st = F_WRITE;
+          }
+          uint32_t taken = (st == F_WRITE && asks && ((newly >> off) & 1u)) ? (1u << my_cell) : 0u;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) taken |= __shfl_xor_sync(0xffffffffu, taken, o);
+          if (lane == 0) atomicAnd(&ctrl->cell_free, ~taken);
+          g_mask |= newly;
+          while (g_mask & 1u) {
+            g_mask >>= 1;
+            ++g_base;
+          }
+          __syncwarp();
+        }
       }
+      // ---- hand the item to its slot ----
+      if (st == F_WRITE) {
+        const uint32_t mb = kMailboxes * slot + half;
+        const uint32_t mbs = ld_shared_volatile(&ctrl->mb_state[mb]);
+        if (mbs == kMbEmpty || mbs == kMbIdle) {
+          const char* dg = reinterpret_cast<const char*>(((uint64_t)d0.y << 32) | d0.x);
+          float* dp = reinterpret_cast<float*>(((uint64_t)d0.w << 32) | d0.z);
+          float* dm = reinterpret_cast<float*>(((uint64_t)d1.y << 32) | d1.x);
+          float* dv = reinterpret_cast<float*>(((uint64_t)d1.w << 32) | d1.z);
+          char* dout = reinterpret_cast<char*>(((uint64_t)d2.y << 32) | d2.x);
+          const int64_t numel = (int64_t)(((uint64_t)d2.w << 32) | d2.z);
+          const uint32_t flags = d3.z;
+          const int per = (kind == kKindA) ? L::kAElems : kLansElems;
+          const int64_t start = (int64_t)chunk * per;
+          const int64_t left = numel - start;
+          const int n = left < per ? (int)left : per;
+          constexpr int gran = 16 / (int)sizeof(GT);  // elements per 16 bytes of gradient
+          const int nbulk = (flags & kFlagBulk) ? (n / gran) * gran : 0;
+          const uint32_t op = kind == kKindA ? kOpA : kind == kKindBs ? kOpB : kind == kKindCs ? kOpC : kOpBP;
+          SlotMeta& mt = s_ring[mb];
+          mt.g = dg + start * (int64_t)sizeof(GT);
+          mt.p = dp + start;
+          mt.m = dm + start;
+          mt.v = dv + start;
+          mt.out = dout ? dout + start * (int64_t)sizeof(OT) : nullptr;
+          mt.n_nbulk = (uint32_t)n | ((uint32_t)nbulk << kLansNBits) | ((op == kOpBP ? my_cell : 0u) << (2 * kLansNBits));
+          mt.tensor_op = my_t | (op << 30);
+          mt.nparts = (uint32_t)((numel + per - 1) / per);
+          mt.cs = (op == kOpA) ? s1.gscale : cs;
+          mt.ratio_m = rm;
+          mt.ratio_g = rg;
+          if (op == kOpBP) {
+            CellMeta& cm = s_cell[my_cell];
+            cm.p = dp + start;
+            cm.out = mt.out;
+            cm.n_nbulk = (uint32_t)n | ((uint32_t)nbulk << kLansNBits);
+            cm.tensor = my_t;
+          }
+          __threadfence_block();
+          if (atomicCAS(&ctrl->mb_state[mb], kMbEmpty, kMbFull) == kMbIdle) {
+            // the slot has been waiting for this item: start it from here
+            *reinterpret_cast<volatile uint32_t*>(&ctrl->mb_state[mb]) = kMbTaking;
+            start_from_mailbox(slot, half);
+          }
+          e += kMailboxes * S_h;
+          st = e < my_n ? (uint32_t)F_ITEM : (uint32_t)F_DONE;
+        }
+      }
+#ifdef RAFB200_LANS_TRACE
+      {
+        unsigned cnt[6];
+        for (uint32_t x = 0; x < 6; ++x) cnt[x] = __popc(__ballot_sync(0xffffffffu, st == x));
+        if (lane == 0) {
+          for (uint32_t x = 0; x < 6; ++x) ctrl->stat[x] += cnt[x];
+          ctrl->stat[6] += 1;
+          ctrl->stat[7] += __popc(ld_shared_volatile(&ctrl->cell_free));
+        }
+      }
+#endif
       if (st != st_in) t_enter = 0;
       // ---- bounded waits, errors, end ----
       if ((iter & 31u) == 0) {
         const uint64_t now = global_ns();
-        if (st == F_NORM) {
+        if (st == F_NORM || st == F_CELL) {
           if (t_enter == 0) {
             t_enter = now;
           } else if (now - t_enter > P.wait_ns) {
-            if (atomicCAS(&P.hdr->error, 0u, kind == kKindCs ? kErrWaitN : kErrWaitG) == 0u)
+            if (atomicCAS(&P.hdr->error, 0u, (kind == kKindCs || st == F_CELL) ? kErrWaitN : kErrWaitG) == 0u)
               P.hdr->error_item = list_lo + e;
           }
         }
         if (*reinterpret_cast<volatile unsigned*>(&P.hdr->error) != 0) failed = 1;
       }
       if (__all_sync(0xffffffffu, st == F_DONE) || __any_sync(0xffffffffu, failed != 0)) break;
-      if (npub == 0 && !__any_sync(0xffffffffu, st != st_in)) __nanosleep(100);
+      if (!__any_sync(0xffffffffu, st != st_in)) __nanosleep(100);
     }
-    if (blockIdx.x == 0 && lane == 0) P.hdr->sched_iters = pub_next;
     return;
   }
 
   if (warp == kParkWarp) {
     // ================================= parker =================================
-    // Lane s looks after slot s: finishes its parked chunk when the tensor's norms are final,
-    // and refills it when it ran empty while the ring had nothing to offer.
+    // Lane c looks after tensor-memory cell c: queues the second half of the chunk parked
+    // there when the tensor's norms are final.  Lane s < S also refills slot s when it ran
+    // empty while the ring had nothing to offer.
     const bool active = lane < S;
     const uint32_t bit = 1u << lane;
     uint64_t t_parked = 0;
     int failed = 0;
     for (uint32_t iter = 1;; ++iter) {
-      const uint32_t parked_mask = ld_shared_volatile(&ctrl->parked_mask);
-      const bool parked = active && (parked_mask & bit);
+      const uint32_t parked_mask = ld_shared_volatile(&ctrl->cell_parked);
+      const bool parked = lane < kLansCells && (parked_mask & bit);
       uint32_t my_t = 0x80000000u | (uint32_t)lane;
-      if (parked) my_t = s_meta[lane].tensor_op & kTensorMask;
+      if (parked) my_t = s_cell[lane].tensor;
       const unsigned same_t = __match_any_sync(0xffffffffu, my_t);
       const int leader = __ffs(same_t) - 1;
       uint4 nrm = make_uint4(0, 0, 0, 0);
@@ -555,14 +708,10 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
         const float pn = norm_value(nrm.y), umn = norm_value(nrm.z), ugn = norm_value(nrm.w);
         const float a = (umn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, umn)) : P.lr;
         const float b2 = (ugn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, ugn)) : P.lr;
-        atomicAnd(&ctrl->parked_mask, ~bit);
+        atomicAnd(&ctrl->cell_parked, ~bit);
         LANS_TRACE(6u, (uint32_t)lane, my_t);
         push_op((uint32_t)lane, kOpCP, 0, 0, 0.f, -mul(a, s1.beta1), -mul(b2, s1.beta3));
         t_parked = 0;
-      }
-      if (active && (ld_shared_volatile(&ctrl->free_mask) & bit) && !failed) {
-        atomicAnd(&ctrl->free_mask, ~bit);
-        if (!start_next((uint32_t)lane)) atomicOr(&ctrl->free_mask, bit);
       }
       __syncwarp();
       const bool all_done = ld_shared_volatile(&ctrl->done_items) >= n_list;
@@ -592,6 +741,16 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
       const uint32_t items = ld_shared_volatile(&ctrl->item_cnt[lane]);
       if (items > 0) ring_wait(bar_data + 8 * lane, (items - 1u) & 1u, P.hdr, kErrData, (uint32_t)lane, P.wait_ns);
     }
+#ifdef RAFB200_LANS_TRACE
+    if (blockIdx.x == 5 && lane < 8) {
+      long long* o = reinterpret_cast<long long*>(static_cast<char*>(P.trace) + 16 + 16 * 16000) + 16 * 8;
+      o[lane] = ctrl->stat[lane];
+    }
+#endif
+    // every consumer warp has left (or the bounded wait above gave up): give the tensor
+    // memory back
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
     return;
   }
 
@@ -691,18 +850,30 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
     LANS_TICK(c_queue);
     const uint4 ent = s_queue[qi];
     const uint32_t op = ent.x & 7u, slot = (ent.x >> 3) & 31u, dpar = (ent.x >> 8) & 1u, rpar = (ent.x >> 9) & 1u,
-                   opar = (ent.x >> 10) & 1u;
+                   opar = (ent.x >> 10) & 1u, cpar = (ent.x >> 11) & 1u;
     if (op == kOpEnd) break;
     const float cs = __uint_as_float(ent.y), ratio_m = __uint_as_float(ent.z), ratio_g = __uint_as_float(ent.w);
-    const SlotMeta mt = s_meta[slot];
-    const int n = (int)(mt.n_nbulk & 0xffffu), nbulk = (int)(mt.n_nbulk >> 16);
+    // kOpCP names a tensor-memory cell, every other operation a shared-memory slot
+    SlotMeta mt = s_meta[op == kOpCP ? 0u : slot];
+    uint32_t cell = mt.n_nbulk >> (2 * kLansNBits);
+    if (op == kOpCP) {
+      const CellMeta cm = s_cell[slot];
+      mt.p = cm.p;
+      mt.out = cm.out;
+      mt.n_nbulk = cm.n_nbulk;
+      cell = slot;
+    }
+    const int n = (int)(mt.n_nbulk & ((1u << kLansNBits) - 1u)),
+              nbulk = (int)((mt.n_nbulk >> kLansNBits) & ((1u << kLansNBits) - 1u));
     const GT* gg = static_cast<const GT*>(mt.g);
     float* gp = mt.p;
     float* gm = mt.m;
     float* gv = mt.v;
     OT* gout = static_cast<OT*>(mt.out);
     unsigned char* sbase = smem + slot * L::kSlotBytes;
-    const uint32_t my_done = bar_done + 8 * slot;
+    const uint32_t my_done = (op == kOpCP) ? bar_cell + 8 * slot : bar_done + 8 * slot;
+    // this warp's quarter of the cell: lanes 32 * wig ..., columns 24 * cell ...
+    const uint32_t taddr = tmem_base + ((uint32_t)(32 * wig) << 16) + kCellColumns * cell;
     if (op != kOpCP) {  // first use of the slot's data: wait for the copies
       ok = ring_wait(bar_data + 8 * slot, dpar, P.hdr, kErrData, slot, P.wait_ns);
       if (!__all_sync(0xffffffffu, ok)) break;
@@ -711,7 +882,116 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
     bool publishes = false;
     LANS_TICK(c_data);
 
-    if (op == kOpA) {
+    // The common case - every element of the item arrived by bulk copy - runs as straight-line
+    // code without per-vector tests; ragged or unaligned items take the general code below.
+    // Both add an element's square into the same accumulator in the same order.
+    const bool whole = nbulk == ((op == kOpA) ? L::kAElems : kLansElems);
+    if (whole && op == kOpA) {
+      constexpr int kPasses = L::kAElems / (kGroupThreads * kVec);
+      constexpr int kBatch = kPasses % 7 == 0 ? 7 : 8;  // vectors in flight per thread
+      static_assert(kPasses % kBatch == 0, "an A item is whole batches of passes");
+      for (int q0 = 0; q0 < kPasses; q0 += kBatch) {
+        F4 r[kBatch];
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q)
+          r[q] = Elem<GT>::smem4(sbase + ((q0 + q) * (kGroupThreads * kVec) + gtid * kVec) * sizeof(GT));
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q)
+#pragma unroll
+          for (int j = 0; j < kVec; ++j) {
+            const float x = r[q].x[j] * s1.gscale;
+            acc0 = fmaf(x, x, acc0);
+          }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(my_done);
+      publishes = true;
+    } else if (whole && op == kOpCP) {
+      F4 rp[kBVecs], um[kBVecs], ug[kBVecs];
+      tmem_ld_vecs(taddr, rp);
+      tmem_ld_vecs(taddr + 4 * kLansVecs, um);
+      tmem_ld_vecs(taddr + 8 * kLansVecs, ug);
+      tmem_wait_ld();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(my_done);  // the cell may be given to another chunk
+#pragma unroll
+      for (int q = 0; q < kBVecs; ++q) {
+        const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+#pragma unroll
+        for (int j = 0; j < kVec; ++j)
+          rp[q].x[j] = fmaf(ratio_g, ug[q].x[j], fmaf(ratio_m, um[q].x[j], rp[q].x[j]));
+        Elem<float>::template store4<kStream>(gp + e, rp[q], pol);
+      }
+      if (gout) {
+#pragma unroll
+        for (int q = 0; q < kBVecs; ++q)
+          Elem<OT>::template store4<kStream>(gout + q * (kGroupThreads * kVec) + gtid * kVec, rp[q], pol);
+      }
+    } else if (whole) {
+      F4 rg[kBVecs], rp[kBVecs], rm[kBVecs], rv[kBVecs], ua[kBVecs], ub[kBVecs];
+#pragma unroll
+      for (int q = 0; q < kBVecs; ++q) {
+        const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+        rg[q] = Elem<GT>::smem4(sbase + e * sizeof(GT));
+        rp[q] = Elem<float>::smem4(sbase + L::kGBytes + e * 4);
+        rm[q] = Elem<float>::smem4(sbase + L::kGBytes + L::kFBytes + e * 4);
+        rv[q] = Elem<float>::smem4(sbase + L::kGBytes + 2 * L::kFBytes + e * 4);
+      }
+      __syncwarp();  // values are in registers: the slot can be refilled
+      if (lane == 0) mbar_arrive(my_done);
+      auto stage1 = [&](auto mode_tag) {
+        constexpr int kMode = decltype(mode_tag)::value;
+#pragma unroll
+        for (int q = 0; q < kBVecs; ++q)
+#pragma unroll
+          for (int j = 0; j < kVec; ++j)
+            s1.template apply<kMode>(rg[q].x[j], rp[q].x[j], rm[q].x[j], rv[q].x[j], cs, ua[q].x[j], ub[q].x[j]);
+      };
+      if (s1.mode == 0) stage1(std::integral_constant<int, 0>{});
+      else stage1(std::integral_constant<int, 1>{});
+      if (op == kOpC) {
+#pragma unroll
+        for (int q = 0; q < kBVecs; ++q) {
+          const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+#pragma unroll
+          for (int j = 0; j < kVec; ++j)
+            rp[q].x[j] = fmaf(ratio_g, ub[q].x[j], fmaf(ratio_m, ua[q].x[j], rp[q].x[j]));
+          Elem<float>::template store4<kStream>(gp + e, rp[q], pol);
+          Elem<float>::template store4<kStream>(gm + e, rm[q], pol);
+          Elem<float>::template store4<kStream>(gv + e, rv[q], pol);
+        }
+        if (gout) {
+#pragma unroll
+          for (int q = 0; q < kBVecs; ++q)
+            Elem<OT>::template store4<kStream>(gout + q * (kGroupThreads * kVec) + gtid * kVec, rp[q], pol);
+        }
+      } else {
+        publishes = true;
+#pragma unroll
+        for (int q = 0; q < kBVecs; ++q)
+#pragma unroll
+          for (int j = 0; j < kVec; ++j) {
+            acc0 = fmaf(rp[q].x[j], rp[q].x[j], acc0);
+            acc1 = fmaf(ua[q].x[j], ua[q].x[j], acc1);
+            acc2 = fmaf(ub[q].x[j], ub[q].x[j], acc2);
+          }
+        if (op == kOpBP) {
+          // m and v are final; p, update_m and update_g wait in tensor memory for the norms
+          tmem_st_vecs(taddr, rp);
+          tmem_st_vecs(taddr + 4 * kLansVecs, ua);
+          tmem_st_vecs(taddr + 8 * kLansVecs, ub);
+#pragma unroll
+          for (int q = 0; q < kBVecs; ++q) {
+            const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+            Elem<float>::template store4<kStream>(gm + e, rm[q], pol);
+            Elem<float>::template store4<kStream>(gv + e, rv[q], pol);
+          }
+          tmem_wait_st();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_cell + 8 * cell);  // this warp's part is parked
+        }
+      }
+    } else if (op == kOpA) {
       constexpr int kPasses = L::kAElems / (kGroupThreads * kVec);
 #pragma unroll 2
       for (int q = 0; q < kPasses; ++q) {
@@ -729,21 +1009,16 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
           acc0 = fmaf(x, x, acc0);
         }
       }
-      fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(my_done);
       publishes = true;
     } else if (op == kOpCP) {
-      // stage 2 from the parked chunk: p, update_m, update_g are in the slot
+      // stage 2 from the parked chunk: p, update_m, update_g are in tensor memory
       F4 rp[kBVecs], um[kBVecs], ug[kBVecs];
-#pragma unroll
-      for (int q = 0; q < kBVecs; ++q) {
-        const int e = q * (kGroupThreads * kVec) + gtid * kVec;
-        rp[q] = Elem<float>::smem4(sbase + L::kGBytes + e * 4);
-        um[q] = Elem<float>::smem4(sbase + L::kGBytes + L::kFBytes + e * 4);
-        ug[q] = Elem<float>::smem4(sbase + L::kGBytes + 2 * L::kFBytes + e * 4);
-      }
-      fence_proxy_async_smem();  // the next bulk copy into this slot comes after these accesses
+      tmem_ld_vecs(taddr, rp);
+      tmem_ld_vecs(taddr + 4 * kLansVecs, um);
+      tmem_ld_vecs(taddr + 8 * kLansVecs, ug);
+      tmem_wait_ld();
       __syncwarp();
       if (lane == 0) mbar_arrive(my_done);
 #pragma unroll
@@ -786,22 +1061,28 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
           }
         }
       }
-      if (op != kOpBP) {  // values are in registers: the slot can be refilled
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(my_done);
-      }
+      __syncwarp();  // values are in registers: the slot can be refilled
+      if (lane == 0) mbar_arrive(my_done);
+      // stage 1 of the thread's eight elements, `mode` resolved once
+      F4 ua[kBVecs], ub[kBVecs];
+      auto stage1 = [&](auto mode_tag) {
+        constexpr int kMode = decltype(mode_tag)::value;
+#pragma unroll
+        for (int q = 0; q < kBVecs; ++q)
+#pragma unroll
+          for (int j = 0; j < kVec; ++j)
+            s1.template apply<kMode>(rg[q].x[j], rp[q].x[j], rm[q].x[j], rv[q].x[j], cs, ua[q].x[j], ub[q].x[j]);
+      };
+      if (s1.mode == 0) stage1(std::integral_constant<int, 0>{});
+      else stage1(std::integral_constant<int, 1>{});
       if (op == kOpC) {
 #pragma unroll
         for (int q = 0; q < kBVecs; ++q) {
           const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+          // p - ratio_m*update_m - ratio_g*update_g  (:385; the ratios carry the minus sign)
 #pragma unroll
-          for (int j = 0; j < kVec; ++j) {
-            float a, b;
-            s1(rg[q].x[j], rp[q].x[j], rm[q].x[j], rv[q].x[j], cs, a, b);
-            // p - ratio_m*update_m - ratio_g*update_g  (:385; the ratios carry the minus sign)
-            rp[q].x[j] = fmaf(ratio_g, b, fmaf(ratio_m, a, rp[q].x[j]));
-          }
+          for (int j = 0; j < kVec; ++j)
+            rp[q].x[j] = fmaf(ratio_g, ub[q].x[j], fmaf(ratio_m, ua[q].x[j], rp[q].x[j]));
           if (e < nbulk) {  // aligned: 16-byte stores
             Elem<float>::template store4<kStream>(gp + e, rp[q], pol);
             Elem<float>::template store4<kStream>(gm + e, rm[q], pol);
@@ -823,27 +1104,17 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
 #pragma unroll
         for (int q = 0; q < kBVecs; ++q) {
           const int e = q * (kGroupThreads * kVec) + gtid * kVec;
-          F4 a, b;
 #pragma unroll
           for (int j = 0; j < kVec; ++j) {
-            const float pp = rp[q].x[j];
-            s1(rg[q].x[j], pp, rm[q].x[j], rv[q].x[j], cs, a.x[j], b.x[j]);
-            acc0 = fmaf(pp, pp, acc0);
-            acc1 = fmaf(a.x[j], a.x[j], acc1);
-            acc2 = fmaf(b.x[j], b.x[j], acc2);
+            acc0 = fmaf(rp[q].x[j], rp[q].x[j], acc0);
+            acc1 = fmaf(ua[q].x[j], ua[q].x[j], acc1);
+            acc2 = fmaf(ub[q].x[j], ub[q].x[j], acc2);
           }
-          if (op == kOpBP) {
-            // m and v are final; p, update_m and update_g wait in the slot for the norms
-            float4* sp = reinterpret_cast<float4*>(sbase + L::kGBytes + e * 4);
-            float4* sm = reinterpret_cast<float4*>(sbase + L::kGBytes + L::kFBytes + e * 4);
-            float4* sv = reinterpret_cast<float4*>(sbase + L::kGBytes + 2 * L::kFBytes + e * 4);
-            *sm = make_float4(a.x[0], a.x[1], a.x[2], a.x[3]);
-            *sv = make_float4(b.x[0], b.x[1], b.x[2], b.x[3]);
+          if (op == kOpBP) {  // m and v are final
             if (e < nbulk) {
               Elem<float>::template store4<kStream>(gm + e, rm[q], pol);
               Elem<float>::template store4<kStream>(gv + e, rv[q], pol);
             } else {
-              *sp = make_float4(rp[q].x[0], rp[q].x[1], rp[q].x[2], rp[q].x[3]);
 #pragma unroll
               for (int j = 0; j < kVec; ++j)
                 if (e + j < n) {
@@ -854,8 +1125,13 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
           }
         }
         if (op == kOpBP) {
+          // p, update_m and update_g wait in tensor memory for the norms
+          tmem_st_vecs(taddr, rp);
+          tmem_st_vecs(taddr + 4 * kLansVecs, ua);
+          tmem_st_vecs(taddr + 8 * kLansVecs, ub);
+          tmem_wait_st();
           __syncwarp();
-          if (lane == 0) mbar_arrive(my_done);
+          if (lane == 0) mbar_arrive(bar_cell + 8 * cell);
         }
       }
     }
@@ -863,24 +1139,28 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
     LANS_TICK(c_op);
     // The bookkeeping after an operation goes to a different warp of the group each time.
     const bool duty = (uint32_t)wig == (i & 3u);
-    if (op == kOpBP) {
-      // every warp of the group has parked its part: the parker may finish the chunk as soon
-      // as the norms are final (which needs this chunk's sums, handed over below)
-      if (duty) {
-        if (lane == 0) {
-          ok = ring_wait(my_done, opar, P.hdr, kErrDone, slot, P.wait_ns);
-          if (ok) atomicOr(&ctrl->parked_mask, 1u << slot);
-        }
-        if (!__shfl_sync(0xffffffffu, ok, 0)) break;
-      }
-    } else if (duty) {
-      // The item is finished.  When the other three warps have let go of the slot too,
-      // the next item of the ring starts in it; with the ring empty the parker takes over.
+    if (duty) {
       if (lane == 0) {
         ok = ring_wait(my_done, opar, P.hdr, kErrDone, slot, P.wait_ns);
-        if (ok) {
+        if (ok && op == kOpCP) {
+          // the parked chunk is in registers: its cell is free again, the item is finished
+          atomicOr(&ctrl->cell_free, 1u << cell);
           atomicAdd(&ctrl->done_items, 1u);
-          if (!start_next(slot)) atomicOr(&ctrl->free_mask, 1u << slot);
+        } else if (ok) {
+          // The other three warps have let go of the slot too: the next item of the ring
+          // starts in it; with the ring empty the parker takes over.
+          if (op != kOpBP) atomicAdd(&ctrl->done_items, 1u);
+          take_next(slot);
+          if (op == kOpBP) {
+            // every warp of the group has parked its part: the parker may queue the second
+            // half as soon as the norms are final (which needs this chunk's sums, below)
+            ok = ring_wait(bar_cell + 8 * cell, cpar, P.hdr, kErrDone, 0x100u | cell, P.wait_ns);
+            if (ok) {
+              ctrl->cell_grp[cell] = (uint32_t)grp;
+              __threadfence_block();
+              atomicOr(&ctrl->cell_parked, 1u << cell);
+            }
+          }
         }
       }
       if (!__shfl_sync(0xffffffffu, ok, 0)) break;
@@ -932,24 +1212,38 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
 // item i of that order goes to block i % grid.
 __global__ void lans_static_init_kernel(unsigned char* ws, size_t ctl_off, size_t desc_off, size_t off_off,
                                         size_t items_off, TensorDesc d, uint32_t n_a, uint32_t n_b,
-                                        uint32_t n_park, uint32_t grid) {
+                                        uint32_t n_park, uint32_t grid, uint32_t slots) {
   const uint32_t n_stream = n_b - n_park;
   const uint32_t total = n_a + n_b + n_stream;
   Item* items = reinterpret_cast<Item*>(ws + items_off);
   uint32_t* off = reinterpret_cast<uint32_t*>(ws + off_off);
-  // block b owns the global positions b, b + grid, ...: (total - b + grid - 1) / grid of them
+  // Same dealing as partition_lans_items, with one tensor and every item in one sequence:
+  // block b owns the global positions b, b + grid, ...; its r-th item goes to the list of
+  // its even slots when (r % slots) is even, else to the list of its odd slots.
   auto first_of = [&](uint32_t b) {  // entries of blocks 0 .. b-1
     const uint32_t q = total / grid, r = total % grid;
     return b * q + (b < r ? b : r);
   };
-  for (uint32_t b = threadIdx.x; b <= grid; b += blockDim.x) off[b] = first_of(b);
+  auto in_half = [&](uint32_t r, uint32_t odd) {  // items 0 .. r-1 of a block that go to that list
+    const uint32_t full = r / slots, rem = r % slots;
+    return odd ? full * (slots / 2) + rem / 2 : full * ((slots + 1) / 2) + (rem + 1) / 2;
+  };
+  for (uint32_t b = threadIdx.x; b <= grid; b += blockDim.x) {
+    off[2 * b] = first_of(b);
+    if (b < grid) off[2 * b + 1] = first_of(b) + in_half(first_of(b + 1) - first_of(b), 0);
+  }
   for (uint32_t i = threadIdx.x; i < total; i += blockDim.x) {
+    const uint32_t b = i % grid, r = i / grid, odd = (r % slots) & 1u;
     Item it;
     if (i < n_a) it = Item{kKindA << kPhaseShift, i};
     else if (i < n_a + n_stream) it = Item{kKindBs << kPhaseShift, i - n_a};
-    else if (i < n_a + n_b) it = Item{kKindBCp << kPhaseShift, i - n_a};
-    else it = Item{kKindCs << kPhaseShift, i - n_a - n_b};
-    items[first_of(i % grid) + i / grid] = it;
+    else if (i < n_a + n_b) {
+      // running number among the parked items of the same list
+      const uint32_t lo = n_a + n_stream;
+      const uint32_t r_lo = lo > b ? (lo - b + grid - 1) / grid : 0u;
+      it = Item{kKindBCp << kPhaseShift, (i - n_a) | (((in_half(r, odd) - in_half(r_lo, odd)) & 2047u) << 21)};
+    } else it = Item{kKindCs << kPhaseShift, i - n_a - n_b};
+    items[first_of(b) + (odd ? in_half(first_of(b + 1) - first_of(b), 0) : 0u) + in_half(r, odd)] = it;
   }
   uint32_t* head = reinterpret_cast<uint32_t*>(ws);
   for (uint32_t i = threadIdx.x; i < (ctl_off + sizeof(LansCtl)) / 4; i += blockDim.x) head[i] = 0u;
@@ -962,11 +1256,11 @@ int lans_slots(int g_dtype) { return g_dtype == RAFB200_F32 ? kLansSlots32 : kLa
 int lans_a_elems(int g_dtype) { return g_dtype == RAFB200_F32 ? kLansAElems32 : kLansAElems16; }
 
 // How many chunks of one tensor may wait on chip at the same time, for a grid with
-// `slots_total` slots: about two thirds, and always at least four slots fewer than there are.
-uint32_t lans_park_cap(int64_t slots_total) {
-  int64_t cap = slots_total * 13 / 20;
-  if (const char* e = getenv("RAFB200_PARK_PCT")) cap = slots_total * atoi(e) / 100;  // EXPERIMENT
-  if (cap > slots_total - 4) cap = slots_total - 4;
+// `cells_total` tensor-memory cells (blocks x kLansCells): four fifths, so that every block -
+// the parked items are dealt out evenly - keeps cells for the tensors before and after it.
+uint32_t lans_park_cap(int64_t cells_total) {
+  int64_t cap = cells_total * 4 / 5;
+  if (const char* e = getenv("RAFB200_PARK_PCT")) cap = cells_total * atoi(e) / 100;  // EXPERIMENT
   return (uint32_t)(cap < 0 ? 0 : cap);
 }
 
@@ -1042,27 +1336,41 @@ std::vector<Item> build_lans_schedule(const std::vector<int64_t>& numel, int a_e
 // Deals the items of a schedule out to `grid` blocks, each block keeping the global order.
 // Stage-1 items (Bs, BCp) are dealt in turn among themselves, the other items among
 // themselves, so that a tensor's parked items spread evenly over the blocks whatever they
-// are interleaved with.  Result: off[0 .. grid] followed (8-byte aligned) by the items.
-std::vector<uint32_t> partition_lans_items(const std::vector<Item>& sched, int grid) {
-  std::vector<std::vector<Item>> per(grid);
+// are interleaved with.  Inside a block the r-th item of either sort goes to the list of
+// the even slots when (r % slots) is even, else to the list of the odd slots: the two lists
+// get work in proportion to their slots, and of any 17 consecutive parked items at most 10
+// land in the even list (11 cells) and 9 in the odd one (10 cells).
+// Result: off[0 .. 2 * grid] (list 2b = even slots of block b, 2b + 1 = odd slots),
+// followed (8-byte aligned) by the items.
+std::vector<uint32_t> partition_lans_items(const std::vector<Item>& sched, int grid, int slots) {
+  std::vector<std::vector<Item>> per(2 * (size_t)grid);
   uint64_t rr_b = 0, rr_o = 0;
   for (const Item& it : sched) {
     const uint32_t kind = it.tensor_phase >> kPhaseShift;
     const bool stage1 = kind == kKindBs || kind == kKindBCp;
-    per[(stage1 ? rr_b++ : rr_o++) % (uint64_t)grid].push_back(it);
+    const uint64_t r = stage1 ? rr_b++ : rr_o++;
+    const uint64_t b = r % (uint64_t)grid, round = r / (uint64_t)grid;
+    per[2 * b + ((round % (uint64_t)slots) & 1u)].push_back(it);
   }
-  const size_t head = ((size_t)grid + 1 + 1) & ~(size_t)1;  // uint32 words before the items
+  const size_t head = (2 * (size_t)grid + 1 + 1) & ~(size_t)1;  // uint32 words before the items
   std::vector<uint32_t> out(head + 2 * sched.size());
   uint32_t at = 0;
-  for (int b = 0; b < grid; ++b) {
-    out[b] = at;
-    for (const Item& it : per[b]) {
+  for (int hb = 0; hb < 2 * grid; ++hb) {
+    out[hb] = at;
+    // Each list has its own prefetcher warp and its own half of the block's tensor-memory
+    // cells.  Its parked items carry their running number among them (modulo 2^11, far more
+    // than are ever in flight) in the top bits of the chunk word; chunk indices stay below
+    // 2^21.  Cells are handed out by these numbers.
+    uint32_t seq = 0;
+    for (const Item& it : per[hb]) {
+      uint32_t chunk = it.chunk;
+      if ((it.tensor_phase >> kPhaseShift) == kKindBCp) chunk |= (seq++ & 2047u) << 21;
       out[head + 2 * (size_t)at] = it.tensor_phase;
-      out[head + 2 * (size_t)at + 1] = it.chunk;
+      out[head + 2 * (size_t)at + 1] = chunk;
       ++at;
     }
   }
-  out[grid] = at;
+  out[2 * grid] = at;
   return out;
 }
 
@@ -1143,8 +1451,8 @@ using namespace rafb200;
 // kStaticMaxElems elements, as a statically allocated device array: every GPU that
 // loads this library holds these 76 KB until the process exits.
 constexpr int64_t kStaticMaxElems = 4ll << 20;  // 4,194,304 elements
-constexpr uint32_t kStaticMaxB = (uint32_t)(kStaticMaxElems / kLansElems);                         // 4096
-constexpr uint32_t kStaticMaxA = (uint32_t)((kStaticMaxElems + kLansAElems32 - 1) / kLansAElems32);  // 1024
+constexpr uint32_t kStaticMaxB = (uint32_t)(kStaticMaxElems / kLansElems);
+constexpr uint32_t kStaticMaxA = (uint32_t)((kStaticMaxElems + kLansAElems32 - 1) / kLansAElems32);
 constexpr size_t kStaticCtlOff = 128, kStaticDescOff = 256, kStaticOffOff = 512, kStaticItemsOff = 2048;
 constexpr int kStaticMaxGrid = (int)((kStaticItemsOff - kStaticOffOff) / 4) - 1;  // 383 blocks
 constexpr size_t kStaticBytes = kStaticItemsOff + (size_t)(kStaticMaxA + 2 * kStaticMaxB) * sizeof(Item);
@@ -1182,7 +1490,7 @@ int rafb200_lans(rafb200_tensor_list_t list, int step, const float* step_dev, fl
   LansParams P;
   P.descs = list->dev_desc;
   const uint32_t* table = normalize_grad ? list->dev_lans_lists : list->dev_lans_lists_nonorm;
-  const size_t head = ((size_t)list->lans_grid + 1 + 1) & ~(size_t)1;
+  const size_t head = (2 * (size_t)list->lans_grid + 1 + 1) & ~(size_t)1;
   P.block_off = table;
   P.items = reinterpret_cast<const Item*>(table + head);
   char* ws = static_cast<char*>(workspace);
@@ -1257,7 +1565,7 @@ int rafb200_lans_tensor_static(const void* g, int g_dtype, float* p, float* m, f
   const int a_elems = lans_a_elems(g_dtype);
   const uint32_t n_a = normalize_grad ? (uint32_t)((numel + a_elems - 1) / a_elems) : 0u;
   const uint32_t n_b = (uint32_t)((numel + kLansElems - 1) / kLansElems);
-  const uint32_t cap = lans_park_cap((int64_t)grid * lans_slots(g_dtype));
+  const uint32_t cap = lans_park_cap((int64_t)grid * kLansCells);
   const uint32_t n_park = n_b < cap ? n_b : cap;
 
   LansParams P;
@@ -1277,16 +1585,16 @@ int rafb200_lans_tensor_static(const void* g, int g_dtype, float* p, float* m, f
   // words and writes this call's descriptor and item table; nothing is copied from host
   // memory and nothing is allocated, on the device or on the host.
   lans_static_init_kernel<<<1, 256, 0, s>>>(ws, kStaticCtlOff, kStaticDescOff, kStaticOffOff, kStaticItemsOff, d,
-                                            n_a, n_b, n_park, (uint32_t)grid);
+                                            n_a, n_b, n_park, (uint32_t)grid, (uint32_t)lans_slots(g_dtype));
   RAFB200_CUDA(cudaGetLastError());
   return launch_lans(device, grid, g_dtype, out_dtype, P, s);
 }
 
-int rafb200_lans_schedule(int k, const int64_t* numel, int g_dtype, int with_norm_phase, int slots_total,
+int rafb200_lans_schedule(int k, const int64_t* numel, int g_dtype, int with_norm_phase, int cells_total,
                           int64_t lead_elems, int gap_items, uint32_t* items, size_t capacity,
                           size_t* count) {
   RAFB200_REQUIRE(k >= 0 && (k == 0 || numel) && count && lead_elems >= 0 && gap_items >= 0 &&
-                      slots_total >= 1 && dtype_valid(g_dtype),
+                      cells_total >= 1 && dtype_valid(g_dtype),
                   "rafb200_lans_schedule: bad arguments");
   std::vector<int64_t> n(k);
   for (int i = 0; i < k; ++i) {
@@ -1294,7 +1602,8 @@ int rafb200_lans_schedule(int k, const int64_t* numel, int g_dtype, int with_nor
     n[i] = numel[i];
   }
   const std::vector<Item> sched = build_lans_schedule(n, lans_a_elems(g_dtype), with_norm_phase != 0,
-                                                      lans_park_cap(slots_total), lead_elems, gap_items);
+                                                      lans_park_cap(cells_total), lead_elems,
+                                                      gap_items > 0 ? gap_items : cells_total);
   *count = sched.size();
   if (items) {
     RAFB200_REQUIRE(capacity >= sched.size(), "rafb200_lans_schedule: %zu items, room for %zu", sched.size(),

@@ -20,9 +20,9 @@ std::vector<Item> build_lans_schedule(const std::vector<int64_t>& numel, int a_e
                                       uint32_t park_cap, int64_t lead_elems, int64_t gap_items);
 int lans_slots(int g_dtype);
 int lans_a_elems(int g_dtype);
-uint32_t lans_park_cap(int64_t slots_total);
+uint32_t lans_park_cap(int64_t cells_total);
 int lans_grid(int sm_count, int max_blocks);
-std::vector<uint32_t> partition_lans_items(const std::vector<Item>& sched, int grid);
+std::vector<uint32_t> partition_lans_items(const std::vector<Item>& sched, int grid, int slots);
 bool pointers_aligned(const void* g, int g_dtype, const void* p, const void* m, const void* v,
                       const void* out, int out_dtype);
 
@@ -38,12 +38,12 @@ static int upload_items(const std::vector<Item>& items, Item** dev, uint32_t* n)
   return RAFB200_OK;
 }
 
-static int upload_lists(const std::vector<Item>& sched, int grid, uint32_t** dev) {
+static int upload_lists(const std::vector<Item>& sched, int grid, int slots, uint32_t** dev) {
   if (*dev) {
     cudaFree(*dev);
     *dev = nullptr;
   }
-  const std::vector<uint32_t> table = partition_lans_items(sched, grid);
+  const std::vector<uint32_t> table = partition_lans_items(sched, grid, slots);
   RAFB200_CUDA(cudaMalloc(reinterpret_cast<void**>(dev), table.size() * sizeof(uint32_t)));
   RAFB200_CUDA(cudaMemcpy(*dev, table.data(), table.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
   return RAFB200_OK;
@@ -52,14 +52,14 @@ static int upload_lists(const std::vector<Item>& sched, int grid, uint32_t** dev
 static int rebuild_lans_schedule(rafb200_tensor_list_s* l) {
   l->lans_grid = lans_grid(l->sm_count, l->max_blocks);
   const int64_t slots_total = (int64_t)l->lans_grid * lans_slots(l->g_dtype);
-  const uint32_t cap = lans_park_cap(slots_total);
+  const uint32_t cap = lans_park_cap((int64_t)l->lans_grid * kLansCells);
   const int64_t gap = l->gap_items > 0 ? l->gap_items : slots_total;
   const int a_elems = lans_a_elems(l->g_dtype);
   l->custom_items = false;
-  int rc = upload_lists(build_lans_schedule(l->numel, a_elems, true, cap, l->lead_elems, gap), l->lans_grid,
+  int rc = upload_lists(build_lans_schedule(l->numel, a_elems, true, cap, l->lead_elems, gap), l->lans_grid, lans_slots(l->g_dtype),
                         &l->dev_lans_lists);
   if (rc != RAFB200_OK) return rc;
-  return upload_lists(build_lans_schedule(l->numel, a_elems, false, cap, l->lead_elems, gap), l->lans_grid,
+  return upload_lists(build_lans_schedule(l->numel, a_elems, false, cap, l->lead_elems, gap), l->lans_grid, lans_slots(l->g_dtype),
                       &l->dev_lans_lists_nonorm);
 }
 
@@ -89,9 +89,10 @@ int rafb200_tensor_list_create(int k, const int64_t* numel, int g_dtype, int out
   l->host_desc.resize(k);
   uint64_t chunks = 0;
   for (int i = 0; i < k; ++i) {
-    if (numel[i] < 0) {
+    if (numel[i] < 0 || numel[i] >= (1ll << 31)) {
       delete l;
-      return set_error(RAFB200_INVALID_ARGUMENT, "rafb200_tensor_list_create: numel[%d] < 0", i);
+      return set_error(RAFB200_INVALID_ARGUMENT,
+                       "rafb200_tensor_list_create: numel[%d] must be in [0, 2^31)", i);
     }
     TensorDesc& d = l->host_desc[i];
     memset(&d, 0, sizeof(d));
@@ -231,9 +232,9 @@ int rafb200_tensor_list_set_lans_items(rafb200_tensor_list_t l, const uint32_t* 
                     "rafb200_tensor_list_set_lans_items: item %zu is past the end of tensor %u", i, t);
   }
   RAFB200_CUDA(cudaDeviceSynchronize());  // the old tables may still be read by a kernel in flight
-  int rc = upload_lists(v, l->lans_grid, &l->dev_lans_lists);
+  int rc = upload_lists(v, l->lans_grid, lans_slots(l->g_dtype), &l->dev_lans_lists);
   if (rc != RAFB200_OK) return rc;
-  rc = upload_lists(v, l->lans_grid, &l->dev_lans_lists_nonorm);
+  rc = upload_lists(v, l->lans_grid, lans_slots(l->g_dtype), &l->dev_lans_lists_nonorm);
   l->custom_items = true;
   return rc;
 }

@@ -78,11 +78,15 @@ struct LansStage1 {
     if (normalize && gnorm != 0.0f) return gscale * fdiv(1.0f, add(gnorm, eps));
     return gscale;
   }
-  // in: g (raw), p, m, v, cs = grad_multiplier   out: m, v updated; um, ug
-  __device__ __forceinline__ void operator()(float g, float p, float& m, float& v, float cs,
-                                             float& um, float& ug) const {
+  // in: g (raw), p, m, v, cs = grad_multiplier   out: m, v updated; um, ug.
+  // MODE is the `mode` argument (0 = L2, 1 = decoupled weight decay) as a compile-time
+  // constant: with the choice made once per chunk, the arithmetic of the elements a thread
+  // holds is one straight line of code that the compiler can interleave.
+  template <int MODE>
+  __device__ __forceinline__ void apply(float g, float p, float& m, float& v, float cs, float& um,
+                                        float& ug) const {
     float sg = g * cs;
-    if (mode == 0) {
+    if (MODE == 0) {
       sg = fmaf(wd, p, sg);
       m = fmaf(beta3, sg, m * beta1);
       v = fmaf(one_minus_beta2 * sg, sg, v * beta2);

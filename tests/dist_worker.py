@@ -85,6 +85,31 @@ def check_collectives(comm):
             dist.group_allgather(shards, 0, outs, stream=s)
             for k, o in zip((1, 2, 5), outs):
                 assert torch.equal(o[:, 0].float().cpu(), torch.arange(1, n + 1).repeat_interleave(k).float())
+        # rank_list: every group reduces / gathers among its own ranks; a rank that no group
+        # names works alone (test_collective_communication.py:124-227, communicator.cc:21-84)
+        groups = [[0], list(range(1, n))] if n > 2 else [[0], [1]]
+        mine = groups[0] if r == 0 else groups[1]
+        x = torch.full((4, 4), float(r + 1), device="cuda")
+        dist.allreduce(x, "sum", rank_list=groups, stream=s)
+        assert torch.all(x == float(sum(q + 1 for q in mine))), x
+        y = dist.allgather(torch.full((2, 3), float(r + 1), device="cuda"), 0, rank_list=groups, stream=s)
+        assert torch.equal(y[:, 0].cpu(), torch.tensor([q + 1.0 for q in mine]).repeat_interleave(2))
+        x = torch.full((len(mine) * 2, 2), float(r + 1), device="cuda")
+        y = dist.reduce_scatter(x, "sum", rank_list=groups, stream=s)
+        assert y.shape == (2, 2) and torch.all(y == float(sum(q + 1 for q in mine)))
+        x = torch.full((3,), float(r + 1), device="cuda")
+        dist.allreduce(x, "sum", rank_list=[[0]], stream=s)  # ranks other than 0 are named nowhere
+        assert torch.all(x == float(r + 1))
+        x = torch.full((3,), float(r + 1), device="cuda")
+        dist.allreduce(x, "sum", rank_list=groups, stream=s)  # the same list again: the cached group
+        assert torch.all(x == float(sum(q + 1 for q in mine)))
+        # the integer and double types of the reference's NCCL type map
+        for dtype in (torch.int64, torch.uint8, torch.int8, torch.float64):
+            x = torch.full((5,), r + 1, dtype=dtype, device="cuda")
+            dist.allreduce(x, "sum", stream=s)
+            assert torch.all(x == n * (n + 1) // 2), (dtype, x)
+            y = dist.allgather(torch.full((2,), r + 1, dtype=dtype, device="cuda"), 0, stream=s)
+            assert torch.equal(y.cpu().double(), torch.arange(1, n + 1).repeat_interleave(2).double())
         try:
             dist.reduce_scatter(torch.zeros(n + 1, 2, device="cuda"), "sum", stream=s)
             raise AssertionError("reduce_scatter accepted a dim 0 that does not divide")
