@@ -387,9 +387,10 @@ RAFB200_API int rafb200_dist_config_set(const rafb200_dist_config* in);
  * Streams by tag (Stream::Get(device, tag, index), src/impl/stream_pool.cc:53-98;
  * tags of include/raf/stream_pool.h: compute 1, host-to-device 2, device-to-host 3,
  * communication 4, fuse 5, defuse 6).  Created on first use, one per (device, tag,
- * index), non-blocking; the same call returns the same stream.  rafb200_zero_step
- * takes its streams from here when the caller passes NULL (compute: tag 1 index 0,
- * communication: tag 4 index 0).
+ * index), non-blocking; the same call returns the same stream.  A caller without
+ * an executor of its own takes the two streams of rafb200_zero_step from here
+ * (compute: tag 1 index 0, communication: tag 4 index 0), as the Python mirror
+ * does; a NULL stream argument keeps its CUDA meaning, the default stream.
  */
 RAFB200_API int rafb200_stream_get(int device, int tag, int index, void** stream);
 RAFB200_API int rafb200_stream_release_all(void);

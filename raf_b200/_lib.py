@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.environ.get("RAFB200_LIB") or os.path.join(HERE, "libraf_b200.so")
+LIB_PATH = os.environ.get("RAFB200_LIB") or os.path.join(HERE, "libraf_b200.so")  # an installed copy elsewhere
 
 F32, F16, BF16 = 0, 1, 2
 OPT_SGD, OPT_ADAM, OPT_LANS = 0, 1, 2

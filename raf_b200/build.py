@@ -58,15 +58,6 @@ def _headers_mtime() -> float:
 
 
 def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> str:
-    global OBJ, LIB
-    # Development aid: extra nvcc flags (e.g. -DRAFB200_LANS_UNROLL=2) build a variant
-    # library beside the default one; RAFB200_LIB selects it at load time.
-    extra = os.environ.get("RAFB200_NVCC_EXTRA", "").split()
-    if extra:
-        tag = "".join(c if c.isalnum() else "_" for c in "_".join(extra))
-        OBJ = os.path.join(HERE, "_obj", tag)
-        LIB = os.path.join(HERE, f"libraf_b200{tag}.so")
-        force = force or not os.path.exists(LIB)
     nvcc = _nvcc()
     os.makedirs(OBJ, exist_ok=True)
     srcs = _sources()
@@ -78,7 +69,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
         objs.append(o)
         stale = force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr_m)
         if stale:
-            cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if ptxas_info else []) + ["-x", "cu", "-c", s, "-o", o]
+            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + ["-x", "cu", "-c", s, "-o", o]
             jobs.append(cmd)
 
     def run(cmd):

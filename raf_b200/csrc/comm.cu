@@ -435,7 +435,8 @@ std::map<StreamKey, cudaStream_t> g_streams;
 }  // namespace
 
 int rafb200_stream_get(int device, int tag, int index, void** stream) {
-  RAFB200_REQUIRE(stream && device >= 0 && tag >= 0 && index >= 0, "rafb200_stream_get: bad arguments");
+  RAFB200_REQUIRE(stream && device >= 0 && tag >= 1 && tag <= 6 && index >= 0,
+                  "rafb200_stream_get: bad arguments (tags are 1 .. 6)");
   std::lock_guard<std::mutex> lk(g_stream_mu);
   const StreamKey key{device, tag, index};
   auto it = g_streams.find(key);

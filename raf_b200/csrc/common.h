@@ -74,7 +74,10 @@ constexpr int kLansAElems32 = kLansElems * 4;    // the same for fp32 gradients
 constexpr int kLansSlots16 = 215040 / (kLansElems * 14);  // slots per block (one block per SM), 16-bit g: 15 x 14 KB
 constexpr int kLansSlots32 = 215040 / (kLansElems * 16);  // fp32 g: 13 x 16 KB
 constexpr int kLansCells = 512 / (12 * kLansVecs);        // parked chunks per block: 21 x 24 columns of tensor memory
-constexpr int kLansNBits = 14;        // bits of an element count inside an item (<= 14336)
+constexpr int kLansNBits = kLansVecs == 2 ? 13 : 14;  // bits of an element count inside an item
+static_assert(kLansAElems16 < (1 << kLansNBits) && kLansAElems32 < (1 << kLansNBits) &&
+                  kLansCells <= (1 << (32 - 2 * kLansNBits)),
+              "count, bulk count and cell number of an item share one 32-bit word");
 
 // Per-tensor control words of the LANS kernel (zeroed at the start of every call).
 // A norm word is "final" when its top bit is set: the publisher stores the bits of
@@ -105,7 +108,7 @@ struct LansHeader {
   unsigned int ticket;   // next work item to hand out
   unsigned int error;    // 0, or the code of the bounded wait that expired
   unsigned int error_item;
-  unsigned int sched_iters;  // polling iterations of block 0's scheduler warp (a cheap health figure)
+  unsigned int pad1_;
   float inv_bc1;         // reciprocal bias corrections when `step` lives on the device
   float inv_bc2;
 };

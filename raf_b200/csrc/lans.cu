@@ -67,7 +67,6 @@ struct LansParams {
   const float* step_dev;
   int bias_correction;
   uint64_t wait_ns;  // bound of every wait inside the kernel
-  void* trace;       // development aid, see LANS_TRACE
 };
 
 __device__ __forceinline__ uint64_t global_ns() {
@@ -230,26 +229,6 @@ __device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, LansHea
   return true;
 }
 
-#ifdef RAFB200_LANS_TRACE
-// Development aid (not built by default): block 0 logs (event, a, b, time) records behind
-// the control words of the workspace.
-#define LANS_TRACE(ev, a, b)                                                                      \
-  do {                                                                                            \
-    if (blockIdx.x == 0) {                                                                        \
-      unsigned* tb__ = reinterpret_cast<unsigned*>(P.trace);                                      \
-      const unsigned i__ = atomicAdd(tb__, 1u);                                                   \
-      if (i__ < 16000u) {                                                                         \
-        const uint64_t t__ = global_ns();                                                         \
-        tb__[4 + 4 * i__] = (ev);                                                                 \
-        tb__[5 + 4 * i__] = (a);                                                                  \
-        tb__[6 + 4 * i__] = (b);                                                                  \
-        tb__[7 + 4 * i__] = (unsigned)(t__ & 0xffffffffu);                                        \
-      }                                                                                           \
-    }                                                                                             \
-  } while (0)
-#else
-#define LANS_TRACE(ev, a, b) do { } while (0)
-#endif
 
 // ---- kernel geometry ---------------------------------------------------------------
 constexpr int kGroups = 4;                       // consumer groups per block
@@ -309,7 +288,6 @@ struct LansCtrl {
   uint32_t cell_parked;  // cells whose chunk waits for its tensor's norms
   uint32_t tmem_base;    // address the allocation returned
   uint32_t cellop_cnt[32], cell_grp[32];  // per cell: parity of its barrier, group that parked it
-  uint32_t stat[8];  // development counters (LANS_TRACE builds)
 };
 
 // What the second half of a parked item needs: where p and the parameter copy go.
@@ -462,7 +440,6 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
     uint32_t rpar = 0;
     if (op != kOpC) rpar = atomicAdd(&ctrl->pub_cnt[slot], 1u) & 1u;
     if (op == kOpBP) rpar |= (atomicAdd(&ctrl->cellop_cnt[e2.z >> (2 * kLansNBits)], 1u) & 1u) << 2;  // lands in bit 11
-    LANS_TRACE(1u, slot, op);
     push_op(slot, op, dpar, rpar, __uint_as_float(e3.y), __uint_as_float(e3.z), __uint_as_float(e3.w));
   };
   // The slot has run empty: take its next item if the prefetcher has it ready, else leave
@@ -652,17 +629,6 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
           st = e < my_n ? (uint32_t)F_ITEM : (uint32_t)F_DONE;
         }
       }
-#ifdef RAFB200_LANS_TRACE
-      {
-        unsigned cnt[6];
-        for (uint32_t x = 0; x < 6; ++x) cnt[x] = __popc(__ballot_sync(0xffffffffu, st == x));
-        if (lane == 0) {
-          for (uint32_t x = 0; x < 6; ++x) ctrl->stat[x] += cnt[x];
-          ctrl->stat[6] += 1;
-          ctrl->stat[7] += __popc(ld_shared_volatile(&ctrl->cell_free));
-        }
-      }
-#endif
       if (st != st_in) t_enter = 0;
       // ---- bounded waits, errors, end ----
       if ((iter & 31u) == 0) {
@@ -709,7 +675,6 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
         const float a = (umn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, umn)) : P.lr;
         const float b2 = (ugn != 0.0f && pn != 0.0f) ? mul(P.lr, fdiv(pn, ugn)) : P.lr;
         atomicAnd(&ctrl->cell_parked, ~bit);
-        LANS_TRACE(6u, (uint32_t)lane, my_t);
         push_op((uint32_t)lane, kOpCP, 0, 0, 0.f, -mul(a, s1.beta1), -mul(b2, s1.beta3));
         t_parked = 0;
       }
@@ -741,12 +706,6 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
       const uint32_t items = ld_shared_volatile(&ctrl->item_cnt[lane]);
       if (items > 0) ring_wait(bar_data + 8 * lane, (items - 1u) & 1u, P.hdr, kErrData, (uint32_t)lane, P.wait_ns);
     }
-#ifdef RAFB200_LANS_TRACE
-    if (blockIdx.x == 5 && lane < 8) {
-      long long* o = reinterpret_cast<long long*>(static_cast<char*>(P.trace) + 16 + 16 * 16000) + 16 * 8;
-      o[lane] = ctrl->stat[lane];
-    }
-#endif
     // every consumer warp has left (or the bounded wait above gave up): give the tensor
     // memory back
     __syncwarp();
@@ -783,7 +742,6 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
       // update of the tensor's accumulators (the lowest of their lanes does it), and all such
       // groups go out at the same time: one pair of round trips to L2 per look, however many
       // tensors the block has chunks of.
-      if (lane == 0) LANS_TRACE(4u, pending, 0u);
       const unsigned same = __match_any_sync(0xffffffffu, ready ? key : (0x80000000u | (uint32_t)lane));
       const bool leads = ready && (__ffs(same) - 1) == lane;
       double a0 = 0.0, a1 = 0.0, a2 = 0.0;
@@ -810,7 +768,6 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
         __threadfence();
         const unsigned cnt = (unsigned)__popc(same);
         const unsigned old = atomicAdd(is_a ? &ctl->arrived_a : &ctl->arrived_b, cnt);
-        LANS_TRACE(5u, key, old + cnt == nparts);
         if (old + cnt == nparts) {
           // Every part of the tensor has been added: publish the norm(s), value and
           // "final" bit in one word each.
@@ -836,18 +793,11 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
   const int grp = warp >> 2, wig = warp & 3, gtid = tid & (kGroupThreads - 1);
   Policies pol;
   pol.init();
-#ifdef RAFB200_LANS_TRACE
-  long long c_queue = 0, c_data = 0, c_op = 0, c_duty = 0, c_pub = 0, c_t = clock64(), c_n = 0;
-#define LANS_TICK(acc) do { const long long n__ = clock64(); acc += n__ - c_t; c_t = n__; } while (0)
-#else
-#define LANS_TICK(acc) do { } while (0)
-#endif
   for (uint32_t i = 0;; ++i) {
     const uint32_t qi = (uint32_t)grp * kQueueDepth + (i % kQueueDepth);
     bool ok = ring_wait(bar_queue + 8 * qi, (i / kQueueDepth) & 1u, P.hdr, kErrRing, 0x1000u | (uint32_t)grp,
                         P.wait_ns);
     if (!__all_sync(0xffffffffu, ok)) break;  // every lane of the warp leaves, or none
-    LANS_TICK(c_queue);
     const uint4 ent = s_queue[qi];
     const uint32_t op = ent.x & 7u, slot = (ent.x >> 3) & 31u, dpar = (ent.x >> 8) & 1u, rpar = (ent.x >> 9) & 1u,
                    opar = (ent.x >> 10) & 1u, cpar = (ent.x >> 11) & 1u;
@@ -880,7 +830,6 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
     }
     float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f;
     bool publishes = false;
-    LANS_TICK(c_data);
 
     // The common case - every element of the item arrived by bulk copy - runs as straight-line
     // code without per-vector tests; ragged or unaligned items take the general code below.
@@ -1135,8 +1084,6 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
         }
       }
     }
-
-    LANS_TICK(c_op);
     // The bookkeeping after an operation goes to a different warp of the group each time.
     const bool duty = (uint32_t)wig == (i & 3u);
     if (duty) {
@@ -1165,8 +1112,6 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
       }
       if (!__shfl_sync(0xffffffffu, ok, 0)) break;
     }
-
-    LANS_TICK(c_duty);
     if (publishes) {
       const float v0 = warp_sum(acc0);
       float v1 = 0.f, v2 = 0.f;
@@ -1190,17 +1135,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
         mbar_arrive(bar_redfull + 8 * slot);
       }
     }
-    LANS_TICK(c_pub);
-#ifdef RAFB200_LANS_TRACE
-    ++c_n;
-#endif
   }
-#ifdef RAFB200_LANS_TRACE
-  if (blockIdx.x == 5 && lane == 0) {
-    long long* o = reinterpret_cast<long long*>(static_cast<char*>(P.trace) + 16 + 16 * 16000) + warp * 8;
-    o[0] = c_queue; o[1] = c_data; o[2] = c_op; o[3] = c_duty; o[4] = c_pub; o[5] = c_n;
-  }
-#endif
   // No more work (or a wait expired): tell the publisher and the parker that this warp has left.
   __syncwarp();
   if (lane == 0) mbar_arrive(bar_end);
@@ -1260,7 +1195,6 @@ int lans_a_elems(int g_dtype) { return g_dtype == RAFB200_F32 ? kLansAElems32 : 
 // the parked items are dealt out evenly - keeps cells for the tensors before and after it.
 uint32_t lans_park_cap(int64_t cells_total) {
   int64_t cap = cells_total * 4 / 5;
-  if (const char* e = getenv("RAFB200_PARK_PCT")) cap = cells_total * atoi(e) / 100;  // EXPERIMENT
   return (uint32_t)(cap < 0 ? 0 : cap);
 }
 
@@ -1376,11 +1310,7 @@ std::vector<uint32_t> partition_lans_items(const std::vector<Item>& sched, int g
 
 size_t lans_ctl_bytes(int k) { return 128 + sizeof(LansCtl) * (size_t)k; }
 
-#ifdef RAFB200_LANS_TRACE
-size_t lans_workspace_bytes(int k) { return ((lans_ctl_bytes(k) + 255) & ~(size_t)255) + 16 + 16 * 16000 + 2048; }
-#else
 size_t lans_workspace_bytes(int k) { return (lans_ctl_bytes(k) + 255) & ~(size_t)255; }
-#endif
 
 // The persistent grid: one block per SM, or fewer when a cap leaves SMs to a concurrent
 // collective.  The schedule of a list is built for this number of blocks.
@@ -1500,11 +1430,6 @@ int rafb200_lans(rafb200_tensor_list_t list, int step, const float* step_dev, fl
               grad_averaging, mode, normalize_grad, grad_scale);
   P.step_dev = step_dev;
   P.wait_ns = list->wait_ns;
-  P.trace = nullptr;
-#ifdef RAFB200_LANS_TRACE
-  P.trace = ws + ((lans_ctl_bytes(list->k) + 255) & ~(size_t)255);
-  RAFB200_CUDA(cudaMemsetAsync(P.trace, 0, 16, s));
-#endif
 
   RAFB200_CUDA(cudaMemsetAsync(workspace, 0, lans_ctl_bytes(list->k), s));
   if (step_dev) {
@@ -1578,7 +1503,6 @@ int rafb200_lans_tensor_static(const void* g, int g_dtype, float* p, float* m, f
               mode, normalize_grad, grad_scale);
   P.step_dev = nullptr;
   P.wait_ns = 2000000000ull;
-  P.trace = nullptr;
 
   // The array keeps whatever the previous call left in it.  A small kernel on the same
   // stream zeroes the ticket counter, the error word, the arrival counters, sums and norm

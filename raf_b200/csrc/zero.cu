@@ -167,6 +167,7 @@ struct rafb200_zero_s {
   // barrier kernel stores to when it gives up, read at the top of every step.
   volatile unsigned int* host_err = nullptr;
   unsigned int* host_err_dev = nullptr;  // device address of *host_err
+  int device = 0;                        // the device current at creation
   uint64_t wait_limit_ns = 10000000000ull;
   int host_output = 0;               // 0: full parameters to the host, 1: this rank's row blocks
   std::vector<const void*> shard_g;  // per tensor: where the update reads its gradient block
@@ -323,6 +324,7 @@ int rafb200_zero_create(rafb200_plan_t plan, rafb200_comm_t comm, int g_dtype, i
       rc = set_error(RAFB200_CUDA_ERROR, "rafb200_zero_create: no usable CUDA device");
       break;
     }
+    z->device = dev;
     // With a single rank there is nothing to overlap: one bucket, one launch.
     const int nb = (z->n == 1) ? (k > 0 ? 1 : 0) : plan->nbuckets;
     z->buckets.resize(nb);

@@ -26,7 +26,8 @@ def dtype_code(dtype) -> int:
 
 
 class _CDistConfig(C.Structure):
-    _fields_ = [("enable_data_parallel", C.c_int), ("zero_opt_level", C.c_int),
+    _fields_ = [("scheduling_param", C.c_int), ("iteration", C.c_int),
+                ("enable_data_parallel", C.c_int), ("zero_opt_level", C.c_int),
                 ("enable_auto_dp_profiling", C.c_int), ("auto_dp_profiling_start_iter", C.c_int),
                 ("auto_dp_profiling_end_iter", C.c_int), ("group_bucket_size", C.c_int64)]
 

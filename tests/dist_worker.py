@@ -122,10 +122,17 @@ def check_collectives(comm):
 # collectives by NCCL / own kernels with / without multicast / own kernels on gradients and
 # parameters that live inside the symmetric buffer (no pack and unpack copies)
 MODES = ["nccl", "multimem", "peer", "view"]
+# ... and each of them again with all steps queued back to back: no host synchronisation and no
+# status read between steps, so the values also cover the ordering ACROSS steps (the fence at the
+# start of a step, barrier epochs, the all-gather of step s overlapping the reduce-scatter of
+# step s + 1, gradients rewritten inside the symmetric buffer)
+MODES = MODES + [m + "_q" for m in MODES]
 
 
-def run_zero(comm, out_dir, mode):
+def run_zero(comm, out_dir, tag):
     n, r = comm.size, comm.rank
+    queued = tag.endswith("_q")
+    mode = tag[:-2] if queued else tag
     for case, (optimizer, g_dtype, p_dtype) in enumerate(CASES):
         plan = Plan(SHAPES, n, r, BUCKET)
         z = ZeroStep(plan, comm, g_dtype, p_dtype, optimizer)
@@ -155,8 +162,10 @@ def run_zero(comm, out_dir, mode):
                            beta1=0.9, beta2=0.999, eps=1e-6, weight_decay=0.01, grad_scale=scale,
                            average=1)
         saved = {}
+        keep = []  # the library's streams read the gradients: they stay allocated until the last status
         for step in range(1, STEPS + 1):
             grads = [local_grad(r, step, i, numel(s), g_dtype, 1 / scale).cuda() for i, s in enumerate(SHAPES)]
+            keep.append(list(grads))
             if gviews is not None:  # "backward" writes straight into the symmetric buffer
                 for i, gv in enumerate(gviews):
                     if gv is not None:
@@ -164,11 +173,14 @@ def run_zero(comm, out_dir, mode):
                         grads[i] = gv.reshape(-1)
             z.bind(grads, params, tp, tm, tv)
             z.step(hyper, step)
+            if queued:
+                continue
             z.status()
             if step == 1:  # the caller's gradients are inputs only: the step must not modify them
                 for i, s in enumerate(SHAPES):
                     again = local_grad(r, step, i, numel(s), g_dtype, 1 / scale)
                     assert torch.equal(grads[i].cpu(), again), ("gradient modified", i)
+        z.status()
         for i in range(len(SHAPES)):
             saved[f"p_{i}"] = tp[i].cpu().numpy()
             saved[f"m_{i}"] = tm[i].cpu().numpy()
@@ -178,7 +190,7 @@ def run_zero(comm, out_dir, mode):
         if mode == "view":
             assert kernels <= 7 * plan.num_buckets
         saved["counts"] = np.array([kernels, collectives, plan.num_buckets])
-        np.savez(os.path.join(out_dir, f"case{case}_{mode}_rank{r}.npz"), **saved)
+        np.savez(os.path.join(out_dir, f"case{case}_{tag}_rank{r}.npz"), **saved)
         z.close()
         plan.close()
 

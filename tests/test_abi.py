@@ -178,3 +178,33 @@ def test_plan_geometry_random_shapes_vs_oracle():
             plan.close()
 
     run()
+
+
+def test_dist_config_lives_in_the_library():
+    """include/raf/dist_config.h:17-48: same fields and defaults; the Python object and the C
+    entry points read and write one process-wide record."""
+    import ctypes as C
+
+    from raf_b200 import _lib
+    from raf_b200 import distributed as dist
+
+    cfg = dist.get_config()
+    before = cfg.dumps()
+    try:
+        assert before["auto_dp_profiling_start_iter"] == 2 and before["auto_dp_profiling_end_iter"] == 4
+        assert before["group_bucket_size"] == 5000000000 and before["zero_opt_level"] in (0, 1, 2, 3)
+        cfg.zero_opt_level = 2
+        cfg.enable_data_parallel = True
+        raw = dist._CDistConfig()
+        _lib.check(_lib.load().rafb200_dist_config_get(C.byref(raw)))
+        assert raw.zero_opt_level == 2 and raw.enable_data_parallel == 1
+        assert cfg.enable_data_parallel is True and cfg.zero_opt_level == 2
+        with pytest.raises(_lib.RafB200Error):
+            cfg.zero_opt_level = 7
+        with pytest.raises(KeyError):
+            cfg.loads({"no_such_field": 1})
+        with pytest.raises(AttributeError):
+            cfg.no_such_field = 1
+    finally:
+        cfg.loads(before)
+    assert cfg.dumps() == before
