@@ -328,7 +328,7 @@ RAFB200_API int rafb200_comm_free(rafb200_comm_t comm, void* ptr);
  * group = position in it), or a world of one when no group names it, cached under
  * the rank list and owned by `comm` (do not destroy it).  group_sizes[n_groups],
  * ranks[] = the groups one after another.  n_groups 0 returns `comm` itself.  Every
- * rank of `comm` must make the same call (NCCL splits the communicator collectively).
+ * rank of `comm` must make the same call: the groups' ids travel in one all-gather over `comm`.
  */
 RAFB200_API int rafb200_comm_sub(rafb200_comm_t comm, int n_groups, const int* group_sizes,
                                  const int* ranks, rafb200_comm_t* sub);

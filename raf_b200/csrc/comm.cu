@@ -53,10 +53,16 @@ static int nccl_fail(ncclResult_t r, const char* what) {
   return set_error(RAFB200_NCCL_ERROR, "%s: %s", what, ncclGetErrorString(r));
 }
 
-#define RAFB200_NCCL(comm, expr)                       \
-  do {                                                 \
-    ncclResult_t r__ = (expr);                         \
-    if (r__ != ncclSuccess) return nccl_fail(r__, #expr); \
+// The communicators are non-blocking (their creation has a deadline, see init_rank), so a call
+// may answer ncclInProgress: the work is then being queued by NCCL's own thread, and nothing
+// that relies on it being on the stream may follow before ncclCommGetAsyncError reports
+// ncclSuccess.  Every entry point therefore waits for that (bounded by the communicator's
+// timeout) before it returns; inside a group only the closing ncclGroupEnd does.
+static int finish_call(rafb200_comm_s* c, ncclResult_t r, const char* what);
+#define RAFB200_NCCL(comm, expr)                            \
+  do {                                                      \
+    int rc__ = finish_call((comm), (expr), #expr);          \
+    if (rc__ != RAFB200_OK) return rc__;                    \
   } while (0)
 
 // src/op/dialect/nccl/communication_utils.h:31-48 (int8, int64, uint8, f16, f32, f64), plus bf16
@@ -152,6 +158,21 @@ static int wait_ready(ncclComm_t comm, int timeout_ms, const char* what) {
     if (st != ncclInProgress) return nccl_fail(st, what);
     if (Clock::now() > deadline) return set_error(RAFB200_TIMEOUT, "%s: not every rank joined within %d ms", what, timeout_ms);
     std::this_thread::sleep_for(std::chrono::milliseconds(2));
+  }
+}
+
+static int finish_call(rafb200_comm_s* c, ncclResult_t r, const char* what) {
+  if (r == ncclSuccess) return RAFB200_OK;
+  if (r != ncclInProgress || !c || !c->nccl) return nccl_fail(r, what);
+  const auto deadline = Clock::now() + std::chrono::milliseconds(c->timeout_ms > 0 ? c->timeout_ms : 60000);
+  while (true) {
+    ncclResult_t st = ncclSuccess;
+    ncclResult_t q = ncclCommGetAsyncError(c->nccl, &st);
+    if (q != ncclSuccess) return nccl_fail(q, "ncclCommGetAsyncError");
+    if (st == ncclSuccess) return RAFB200_OK;
+    if (st != ncclInProgress) return nccl_fail(st, what);
+    if (Clock::now() > deadline) return set_error(RAFB200_TIMEOUT, "%s: still in progress after %d ms", what, c->timeout_ms);
+    std::this_thread::yield();
   }
 }
 
@@ -292,8 +313,11 @@ int rafb200_comm_destroy(rafb200_comm_t c) {
   for (auto& kv : c->subs) rafb200_comm_destroy(kv.second);
   c->subs.clear();
   if (c->nccl && !c->borrowed) {
+    // a non-blocking communicator is finalised first (that may still be in progress when the
+    // call returns), then destroyed
+    rc = finish_call(c, ncclCommFinalize(c->nccl), "ncclCommFinalize");
     ncclResult_t r = ncclCommDestroy(c->nccl);
-    if (r != ncclSuccess) rc = nccl_fail(r, "ncclCommDestroy");
+    if (r != ncclSuccess && rc == RAFB200_OK) rc = nccl_fail(r, "ncclCommDestroy");
   }
   if (!c->store_file.empty()) ::unlink(c->store_file.c_str());
   delete c;
@@ -309,7 +333,8 @@ int rafb200_comm_alloc(rafb200_comm_t c, size_t bytes, void** ptr) {
   void* p = nullptr;
   if (want && ncclMemAlloc(&p, bytes) == ncclSuccess && p) {
     reg.nccl_mem = true;
-    if (ncclCommRegister(c->nccl, p, bytes, &reg.handle) != ncclSuccess) reg.handle = nullptr;
+    if (finish_call(c, ncclCommRegister(c->nccl, p, bytes, &reg.handle), "ncclCommRegister") != RAFB200_OK)
+      reg.handle = nullptr;
   } else {
     p = nullptr;
     RAFB200_CUDA(cudaMalloc(&p, bytes));
@@ -324,8 +349,7 @@ int rafb200_comm_free(rafb200_comm_t c, void* ptr) {
   auto it = c->regs.find(ptr);
   RAFB200_REQUIRE(it != c->regs.end(), "rafb200_comm_free: pointer was not allocated by rafb200_comm_alloc");
   int rc = RAFB200_OK;
-  if (it->second.handle && ncclCommDeregister(c->nccl, it->second.handle) != ncclSuccess)
-    rc = set_error(RAFB200_NCCL_ERROR, "ncclCommDeregister failed");
+  if (it->second.handle) rc = finish_call(c, ncclCommDeregister(c->nccl, it->second.handle), "ncclCommDeregister");
   if (it->second.nccl_mem) {
     if (ncclMemFree(ptr) != ncclSuccess) rc = set_error(RAFB200_NCCL_ERROR, "ncclMemFree failed");
   } else {
@@ -373,30 +397,74 @@ int rafb200_comm_sub(rafb200_comm_t c, int n_groups, const int* group_sizes, con
     s->size = group_sizes[my_group];
     s->rank = my_rank;
   }  // else: a world of one (communicator.cc:48-58)
-  if (!c->is_void) {
-    // Every rank of the parent takes part in the split; ranks outside every group get no
-    // communicator.  (The reference exchanges one id per group and calls ncclCommInitRank,
-    // nccl_communicator.cc:115-158; ncclCommSplit needs no exchange.)
-    ncclComm_t split = nullptr;
-    ncclResult_t r = ncclCommSplit(c->nccl, my_group >= 0 ? my_group : NCCL_SPLIT_NOCOLOR, my_rank >= 0 ? my_rank : 0,
-                                   &split, nullptr);
-    if (r != ncclSuccess && r != ncclInProgress) {
-      delete s;
-      return nccl_fail(r, "ncclCommSplit");
-    }
-    if (split) {
-      int rc = wait_ready(split, c->timeout_ms, "ncclCommSplit");
-      if (rc != RAFB200_OK) {
-        ncclCommAbort(split);
+  bool any_group = false;  // a group of two or more ranks: only then is NCCL needed at all
+  for (int g = 0; g < n_groups; ++g) any_group = any_group || group_sizes[g] > 1;
+  if (!c->is_void && any_group) {
+    // As the reference does (nccl_communicator.cc:115-158), every group gets a communicator of
+    // its own from an id that its first rank draws.  The ids travel over the parent: one
+    // all-gather of a 128-byte record per rank, which every rank of the parent takes part in -
+    // also those that no group names.  (No file store is needed, so this works for adopted
+    // communicators too.)
+    const int n = c->size;
+    ncclUniqueId mine;
+    memset(&mine, 0, sizeof(mine));
+    const bool needs_nccl = my_group >= 0 && s->size > 1;
+    if (needs_nccl && my_rank == 0) {
+      ncclResult_t r = ncclGetUniqueId(&mine);
+      if (r != ncclSuccess) {
         delete s;
-        return rc;
+        return nccl_fail(r, "ncclGetUniqueId");
       }
     }
-    if (my_group >= 0 && s->size > 1) {
+    std::vector<ncclUniqueId> all((size_t)n);
+    unsigned char* dbuf = nullptr;
+    cudaStream_t xs = nullptr;
+    cudaEvent_t done = nullptr;
+    int rc = RAFB200_OK;
+    auto cuda_ok = [&](cudaError_t e, const char* what) {
+      if (e != cudaSuccess && rc == RAFB200_OK) rc = set_error(RAFB200_CUDA_ERROR, "%s: %s", what, cudaGetErrorString(e));
+      return e == cudaSuccess;
+    };
+    if (cuda_ok(cudaMalloc(reinterpret_cast<void**>(&dbuf), sizeof(mine) * ((size_t)n + 1)), "cudaMalloc") &&
+        cuda_ok(cudaStreamCreateWithFlags(&xs, cudaStreamNonBlocking), "cudaStreamCreate") &&
+        cuda_ok(cudaEventCreateWithFlags(&done, cudaEventDisableTiming), "cudaEventCreate") &&
+        cuda_ok(cudaMemcpyAsync(dbuf, &mine, sizeof(mine), cudaMemcpyHostToDevice, xs), "cudaMemcpyAsync")) {
+      rc = finish_call(c, ncclAllGather(dbuf, dbuf + sizeof(mine), sizeof(mine), ncclUint8, c->nccl, xs), "ncclAllGather");
+      if (rc == RAFB200_OK &&
+          cuda_ok(cudaMemcpyAsync(all.data(), dbuf + sizeof(mine), sizeof(mine) * (size_t)n, cudaMemcpyDeviceToHost, xs),
+                  "cudaMemcpyAsync") &&
+          cuda_ok(cudaEventRecord(done, xs), "cudaEventRecord")) {
+        // a rank of the parent that never makes this call must not hang the others for ever
+        const auto deadline = Clock::now() + std::chrono::milliseconds(c->timeout_ms > 0 ? c->timeout_ms : 60000);
+        while (true) {
+          cudaError_t q = cudaEventQuery(done);
+          if (q == cudaSuccess) break;
+          if (q != cudaErrorNotReady) {
+            cuda_ok(q, "cudaEventQuery");
+            break;
+          }
+          if (Clock::now() > deadline) {
+            rc = set_error(RAFB200_TIMEOUT, "rafb200_comm_sub: not every rank joined within %d ms", c->timeout_ms);
+            break;
+          }
+          std::this_thread::sleep_for(std::chrono::microseconds(200));
+        }
+      }
+    }
+    if (rc != RAFB200_TIMEOUT) {  // after a timeout the copy may still be pending: leak rather than fault
+      if (done) cudaEventDestroy(done);
+      if (xs) cudaStreamDestroy(xs);
+      if (dbuf) cudaFree(dbuf);
+    }
+    if (rc == RAFB200_OK && needs_nccl) {
+      const int* grp = ranks;
+      for (int g = 0; g < my_group; ++g) grp += group_sizes[g];
       s->is_void = false;
-      s->nccl = split;
-    } else if (split) {
-      ncclCommDestroy(split);  // a group of one needs no NCCL underneath
+      rc = init_rank(s, all[(size_t)grp[0]], c->timeout_ms);
+    }
+    if (rc != RAFB200_OK) {
+      delete s;
+      return rc;
     }
   }
   c->subs[key] = s;
@@ -516,7 +584,7 @@ int rafb200_group_reduce_scatter(rafb200_comm_t c, int k, const void* const* sen
   RAFB200_NCCL(c, ncclGroupStart());
   for (int i = 0; i < k; ++i) {
     ncclResult_t r = ncclReduceScatter(sendbuf[i], recvbuf[i], (size_t)recvcount[i], dt, op, c->nccl, s);
-    if (r != ncclSuccess) {
+    if (r != ncclSuccess && r != ncclInProgress) {
       ncclGroupEnd();
       return nccl_fail(r, "ncclReduceScatter");
     }
@@ -551,7 +619,7 @@ int rafb200_group_allgather(rafb200_comm_t c, int k, const void* const* sendbuf,
   RAFB200_NCCL(c, ncclGroupStart());
   for (int i = 0; i < k; ++i) {
     ncclResult_t r = ncclAllGather(sendbuf[i], recvbuf[i], (size_t)sendcount[i], dt, c->nccl, s);
-    if (r != ncclSuccess) {
+    if (r != ncclSuccess && r != ncclInProgress) {
       ncclGroupEnd();
       return nccl_fail(r, "ncclAllGather");
     }

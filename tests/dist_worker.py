@@ -103,6 +103,12 @@ def check_collectives(comm):
         x = torch.full((3,), float(r + 1), device="cuda")
         dist.allreduce(x, "sum", rank_list=groups, stream=s)  # the same list again: the cached group
         assert torch.all(x == float(sum(q + 1 for q in mine)))
+        whole = [list(range(n))]  # one group of every rank: a communicator split off the global one
+        x = torch.full((3,), float(r + 1), device="cuda")
+        dist.allreduce(x, "sum", rank_list=whole, stream=s)
+        assert torch.all(x == n * (n + 1) / 2)
+        y = dist.allgather(torch.full((1, 2), float(r + 1), device="cuda"), 0, rank_list=whole, stream=s)
+        assert torch.equal(y[:, 0].cpu(), torch.arange(1, n + 1).float())
         # the integer and double types of the reference's NCCL type map
         for dtype in (torch.int64, torch.uint8, torch.int8, torch.float64):
             x = torch.full((5,), r + 1, dtype=dtype, device="cuda")
