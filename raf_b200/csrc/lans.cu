@@ -429,10 +429,13 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
         tma_load_1d(dstaddr, gsrc, gb, my_data, pol_keep);  // stage 1 reads it again soon
       } else {
         mbar_arrive_expect_tx(my_data, gb + 3u * fb);
-        tma_load_1d(dstaddr, gsrc, gb, my_data, pol_stream);
-        tma_load_1d(dstaddr + L::kGBytes, psrc, fb, my_data, pol_stream);
-        tma_load_1d(dstaddr + L::kGBytes + L::kFBytes, msrc, fb, my_data, pol_stream);
-        tma_load_1d(dstaddr + L::kGBytes + 2 * L::kFBytes, vsrc, fb, my_data, pol_stream);
+        // a streamed chunk is read once more by its update item soon after: keep it in L2;
+        // a parked chunk and the update item's own reads are the last use of the lines
+        const uint64_t pol = (op == kOpB) ? pol_keep : pol_stream;
+        tma_load_1d(dstaddr, gsrc, gb, my_data, pol);
+        tma_load_1d(dstaddr + L::kGBytes, psrc, fb, my_data, pol);
+        tma_load_1d(dstaddr + L::kGBytes + L::kFBytes, msrc, fb, my_data, pol);
+        tma_load_1d(dstaddr + L::kGBytes + 2 * L::kFBytes, vsrc, fb, my_data, pol);
       }
     } else {
       mbar_arrive(my_data);
