@@ -182,14 +182,16 @@ RAFB200_API int rafb200_lans(rafb200_tensor_list_t list, int step, const float* 
  *      update_g only;
  *   2  "streamed" update of 1024 elements: stage 1 again, then stage 2, stores;
  *   3  "parked": stage 1 and, once the tensor's norms are final, stage 2 of 1024
- *      elements that stay in shared memory in between.
- * Blocks draw items in this order from one counter.  Kinds 1 and 3 wait for every
+ *      elements that stay on chip in between (in a cell of the SM's tensor memory
+ *      or of its shared memory).
+ * The items are dealt out to the blocks of the persistent grid in turn, in this
+ * order; a block works through its share in order.  Kinds 1 and 3 wait for every
  * kind-0 item of their tensor (only with normalize_grad); kind 2 and the second
  * half of kind 3 wait for every kind-1 and kind-3 item of their tensor.  An item
- * only waits for items that come earlier in the order, and at most
- * four fifths of the grid's parking places (cells_total = blocks x 21 cells of
- * tensor memory) ever hold parked items of one tensor, so a running block only
- * ever waits for items that running blocks hold.  The
+ * only waits for items that come earlier in the order, and at most five eighths
+ * of the grid's parking places (cells_total = blocks x 29 cells) ever hold
+ * parked items of one tensor, so no block ever waits for a cell that an item
+ * behind it holds.  The
  * reference has no such object: its six passes are separate launches
  * (multi_tensor_lans.cu:401-450).  lead_elems and gap_items as in
  * rafb200_tensor_list_tune (gap_items 0 = cells_total).

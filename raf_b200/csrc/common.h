@@ -71,10 +71,16 @@ constexpr int kLansVecs = 2;          // 4-element vectors a consumer thread hol
 constexpr int kLansElems = 128 * 4 * kLansVecs;  // elements per Bs / Cs / BCp item = one slot (1024)
 constexpr int kLansAElems16 = kLansElems * 7;    // gradient elements per A item (what a slot holds), 16-bit g
 constexpr int kLansAElems32 = kLansElems * 4;    // the same for fp32 gradients
-constexpr int kLansSlots16 = 215040 / (kLansElems * 14);  // slots per block (one block per SM), 16-bit g: 15 x 14 KB
-constexpr int kLansSlots32 = 215040 / (kLansElems * 16);  // fp32 g: 13 x 16 KB
-constexpr int kLansCells = 512 / (12 * kLansVecs);        // parked chunks per block: 21 x 24 columns of tensor memory
-constexpr int kLansNBits = kLansVecs == 2 ? 13 : 14;  // bits of an element count inside an item
+// One block per SM.  Its shared memory holds the slots (chunks on their way in: 14 KB each with
+// 16-bit gradients, 16 KB with fp32 ones) and eight cells for parked chunks (12 KB each: p,
+// update_m, update_g); 21 more cells of 24 columns each live in the SM's tensor memory.
+constexpr int kLansSlots16 = 8;
+constexpr int kLansSlots32 = 6;
+constexpr int kLansTmemCells = 512 / (12 * kLansVecs);  // 21
+constexpr int kLansSmemCells = 8;
+constexpr int kLansCells = kLansTmemCells + kLansSmemCells;  // parked chunks per block: 29
+constexpr int kLansNBits = 13;  // bits of an element count inside an item (<= 7168)
+static_assert(kLansVecs == 2, "slot, cell and queue sizes below are for chunks of 1024 elements");
 static_assert(kLansAElems16 < (1 << kLansNBits) && kLansAElems32 < (1 << kLansNBits) &&
                   kLansCells <= (1 << (32 - 2 * kLansNBits)),
               "count, bulk count and cell number of an item share one 32-bit word");

@@ -210,6 +210,45 @@ __device__ __forceinline__ void tmem_ld_vecs(uint32_t taddr, F4 (&a)[kLansVecs])
 }
 constexpr uint32_t kCellColumns = 12 * kLansVecs;  // p, update_m, update_g of a thread's elements
 
+// A parked chunk waits either in tensor memory (cells 0 .. kLansTmemCells-1; `taddr` = this
+// warp's lanes, the cell's columns) or in a shared-memory cell (`scell`, three arrays of
+// kLansElems floats; thread t of the group owns the 16 bytes at element q*512 + 4*t).
+__device__ __forceinline__ void park_store(bool in_tmem, uint32_t taddr, unsigned char* scell, int gtid,
+                                           const F4 (&rp)[kLansVecs], const F4 (&ua)[kLansVecs],
+                                           const F4 (&ub)[kLansVecs]) {
+  if (in_tmem) {
+    tmem_st_vecs(taddr, rp);
+    tmem_st_vecs(taddr + 4 * kLansVecs, ua);
+    tmem_st_vecs(taddr + 8 * kLansVecs, ub);
+  } else {
+#pragma unroll
+    for (int q = 0; q < kLansVecs; ++q) {
+      float4* d = reinterpret_cast<float4*>(scell + (q * 512 + gtid * 4) * 4);
+      d[0] = make_float4(rp[q].x[0], rp[q].x[1], rp[q].x[2], rp[q].x[3]);
+      d[kLansElems / 4] = make_float4(ua[q].x[0], ua[q].x[1], ua[q].x[2], ua[q].x[3]);
+      d[2 * (kLansElems / 4)] = make_float4(ub[q].x[0], ub[q].x[1], ub[q].x[2], ub[q].x[3]);
+    }
+  }
+}
+__device__ __forceinline__ void park_load(bool in_tmem, uint32_t taddr, const unsigned char* scell, int gtid,
+                                          F4 (&rp)[kLansVecs], F4 (&ua)[kLansVecs], F4 (&ub)[kLansVecs]) {
+  if (in_tmem) {
+    tmem_ld_vecs(taddr, rp);
+    tmem_ld_vecs(taddr + 4 * kLansVecs, ua);
+    tmem_ld_vecs(taddr + 8 * kLansVecs, ub);
+    tmem_wait_ld();
+  } else {
+#pragma unroll
+    for (int q = 0; q < kLansVecs; ++q) {
+      const float4* d = reinterpret_cast<const float4*>(scell + (q * 512 + gtid * 4) * 4);
+      const float4 a = d[0], b = d[kLansElems / 4], c = d[2 * (kLansElems / 4)];
+      rp[q].x[0] = a.x; rp[q].x[1] = a.y; rp[q].x[2] = a.z; rp[q].x[3] = a.w;
+      ua[q].x[0] = b.x; ua[q].x[1] = b.y; ua[q].x[2] = b.z; ua[q].x[3] = b.w;
+      ub[q].x[0] = c.x; ub[q].x[1] = c.y; ub[q].x[2] = c.z; ub[q].x[3] = c.w;
+    }
+  }
+}
+
 // Bounded wait on an mbarrier that also gives up as soon as any block has reported an
 // error; a timeout reports `code` itself.
 __device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, LansHeader* hdr,
@@ -238,9 +277,8 @@ constexpr int kPrefWarp = kConsumerWarps;        // 16, 17: resolve the block's 
 constexpr int kParkWarp = kConsumerWarps + 2;    // 18: finishes parked chunks
 constexpr int kPubWarp = kConsumerWarps + 3;     // 19: adds partial sums to the tensors' accumulators
 constexpr int kLansThreads = (kConsumerWarps + 4) * 32;  // 640
-constexpr int kQueueDepth = 32;                  // > slots per group + parked cells + end marker
+constexpr int kQueueDepth = 64;                  // > slots per group + parked cells + end marker
 constexpr int kRing = 64;                        // mailboxes: kMailboxes per slot
-constexpr uint32_t kMailboxes = 4;
 constexpr uint32_t kMbEmpty = 0, kMbFull = 1, kMbTaking = 2, kMbIdle = 3;
 constexpr uint32_t kSeqBits = 11, kSeqMask = (1u << kSeqBits) - 1u;  // see partition_lans_items
 constexpr int kBVecs = kLansElems / (kGroupThreads * kVec);  // 2 vectors per thread per chunk
@@ -308,8 +346,14 @@ struct LansGeo {
   static constexpr int kAElems = sizeof(GT) == 2 ? kLansAElems16 : kLansAElems32;
   static constexpr int kSlots = sizeof(GT) == 2 ? kLansSlots16 : kLansSlots32;
   static_assert(kAElems * (int)sizeof(GT) <= kSlotBytes, "an A item fits a slot");
-  static_assert(kSlots <= 16 && kLansVecs % 2 == 0 && kLansCells <= 32, "per-slot tables hold 16");
-  static constexpr int kMetaOff = kSlots * kSlotBytes;
+  // a prefetcher warp gives each slot of its parity 32 / (slots of a parity, rounded up to a
+  // power of two) lanes = mailboxes
+  static constexpr int kJBits = kSlots <= 8 ? 2 : 3;
+  static constexpr uint32_t kMailboxes = 32u >> kJBits;
+  static_assert(kSlots <= 16 && kSlots * (int)kMailboxes <= kRing && kLansCells <= 31, "per-slot tables and masks");
+  static constexpr int kSmemCellBytes = 3 * kFBytes;  // p, update_m, update_g
+  static constexpr int kSmemCellOff = kSlots * kSlotBytes;
+  static constexpr int kMetaOff = kSmemCellOff + kLansSmemCells * kSmemCellBytes;
   static constexpr int kRingOff = kMetaOff + kSlots * (int)sizeof(SlotMeta);
   static constexpr int kRedOff = kRingOff + kRing * (int)sizeof(SlotMeta);
   static constexpr int kQueueOff = kRedOff + kSlots * (int)sizeof(RedSlot);
@@ -331,6 +375,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
   extern __shared__ __align__(128) unsigned char smem[];
   using L = LansGeo<GT>;
   constexpr int S = L::kSlots;
+  constexpr uint32_t kMailboxes = L::kMailboxes;
   SlotMeta* s_meta = reinterpret_cast<SlotMeta*>(smem + L::kMetaOff);
   SlotMeta* s_ring = reinterpret_cast<SlotMeta*>(smem + L::kRingOff);
   RedSlot* s_red = reinterpret_cast<RedSlot*>(smem + L::kRedOff);
@@ -461,21 +506,22 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
   if (warp == kPrefWarp || warp == kPrefWarp + 1) {
     // =============================== prefetcher ===============================
     // The even slots of a block share one list, the odd slots another; the j-th slot of a
-    // parity with S_h slots runs the entries j, j + S_h, j + 2 S_h, ... of its list.  Four lanes
-    // prepare them in turn (round r goes to mailbox r % 4): item -> descriptor of its tensor (kept
+    // parity with S_h slots runs the entries j, j + S_h, j + 2 S_h, ... of its list.  Eight lanes
+    // prepare them in turn (round r goes to mailbox r % 8): item -> descriptor of its tensor (kept
     // while the tensor stays the same) -> the norms the item's first operation needs are
     // final -> a tensor-memory cell if the item parks -> the slot's mailbox.
     enum : uint32_t { F_ITEM, F_DESC, F_NORM, F_CELL, F_WRITE, F_DONE };
-    // Two warps: warp w serves the slots s with s % 2 == w, four lanes (mailboxes) per slot,
+    // Two warps: warp w serves the slots s with s % 2 == w, kMailboxes lanes per slot,
     // and hands out its own half of the tensor-memory cells.
     const uint32_t pw = (uint32_t)(warp - kPrefWarp);
-    const uint32_t slot = 2u * ((uint32_t)lane & 7u) + pw, half = (uint32_t)lane >> 3;
+    constexpr uint32_t kJMask = (1u << L::kJBits) - 1u;
+    const uint32_t slot = 2u * ((uint32_t)lane & kJMask) + pw, half = (uint32_t)lane >> L::kJBits;
     const uint32_t my_cells = pw == 0 ? ((1u << ((kLansCells + 1) / 2)) - 1u)
                                       : (((1u << kLansCells) - 1u) & ~((1u << ((kLansCells + 1) / 2)) - 1u));
     const uint32_t list_lo = P.block_off[2 * blockIdx.x + pw];
     const uint32_t my_n = P.block_off[2 * blockIdx.x + pw + 1] - list_lo;
     const uint32_t S_h = ((uint32_t)S + 1u - pw) / 2u;  // slots of my parity
-    uint32_t e = ((uint32_t)lane & 7u) + S_h * half;    // my entry of the list
+    uint32_t e = ((uint32_t)lane & kJMask) + S_h * half;  // my entry of the list
     uint32_t st = (slot < (uint32_t)S && e < my_n) ? (uint32_t)F_ITEM : (uint32_t)F_DONE;
     uint32_t tp = 0, chunk = 0, seq = 0, my_t = 0xffffffffu, my_cell = 0;
     uint4 d0 = make_uint4(0, 0, 0, 0), d1 = d0, d2 = d0, d3 = d0, nrm = d0;
@@ -826,7 +872,9 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
     unsigned char* sbase = smem + slot * L::kSlotBytes;
     const uint32_t my_done = (op == kOpCP) ? bar_cell + 8 * slot : bar_done + 8 * slot;
     // this warp's quarter of the cell: lanes 32 * wig ..., columns 24 * cell ...
-    const uint32_t taddr = tmem_base + ((uint32_t)(32 * wig) << 16) + kCellColumns * cell;
+    const bool in_tmem = cell < (uint32_t)kLansTmemCells;
+    const uint32_t taddr = tmem_base + ((uint32_t)(32 * wig) << 16) + kCellColumns * (in_tmem ? cell : 0u);
+    unsigned char* scell = smem + L::kSmemCellOff + (in_tmem ? 0 : (int)(cell - kLansTmemCells)) * L::kSmemCellBytes;
     if (op != kOpCP) {  // first use of the slot's data: wait for the copies
       ok = ring_wait(bar_data + 8 * slot, dpar, P.hdr, kErrData, slot, P.wait_ns);
       if (!__all_sync(0xffffffffu, ok)) break;
@@ -860,10 +908,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
       publishes = true;
     } else if (whole && op == kOpCP) {
       F4 rp[kBVecs], um[kBVecs], ug[kBVecs];
-      tmem_ld_vecs(taddr, rp);
-      tmem_ld_vecs(taddr + 4 * kLansVecs, um);
-      tmem_ld_vecs(taddr + 8 * kLansVecs, ug);
-      tmem_wait_ld();
+      park_load(in_tmem, taddr, scell, gtid, rp, um, ug);
       __syncwarp();
       if (lane == 0) mbar_arrive(my_done);  // the cell may be given to another chunk
 #pragma unroll
@@ -929,16 +974,14 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
           }
         if (op == kOpBP) {
           // m and v are final; p, update_m and update_g wait in tensor memory for the norms
-          tmem_st_vecs(taddr, rp);
-          tmem_st_vecs(taddr + 4 * kLansVecs, ua);
-          tmem_st_vecs(taddr + 8 * kLansVecs, ub);
+          park_store(in_tmem, taddr, scell, gtid, rp, ua, ub);
 #pragma unroll
           for (int q = 0; q < kBVecs; ++q) {
             const int e = q * (kGroupThreads * kVec) + gtid * kVec;
             Elem<float>::template store4<kStream>(gm + e, rm[q], pol);
             Elem<float>::template store4<kStream>(gv + e, rv[q], pol);
           }
-          tmem_wait_st();
+          if (in_tmem) tmem_wait_st();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_cell + 8 * cell);  // this warp's part is parked
         }
@@ -967,10 +1010,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
     } else if (op == kOpCP) {
       // stage 2 from the parked chunk: p, update_m, update_g are in tensor memory
       F4 rp[kBVecs], um[kBVecs], ug[kBVecs];
-      tmem_ld_vecs(taddr, rp);
-      tmem_ld_vecs(taddr + 4 * kLansVecs, um);
-      tmem_ld_vecs(taddr + 8 * kLansVecs, ug);
-      tmem_wait_ld();
+      park_load(in_tmem, taddr, scell, gtid, rp, um, ug);
       __syncwarp();
       if (lane == 0) mbar_arrive(my_done);
 #pragma unroll
@@ -1078,10 +1118,8 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
         }
         if (op == kOpBP) {
           // p, update_m and update_g wait in tensor memory for the norms
-          tmem_st_vecs(taddr, rp);
-          tmem_st_vecs(taddr + 4 * kLansVecs, ua);
-          tmem_st_vecs(taddr + 8 * kLansVecs, ub);
-          tmem_wait_st();
+          park_store(in_tmem, taddr, scell, gtid, rp, ua, ub);
+          if (in_tmem) tmem_wait_st();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_cell + 8 * cell);
         }
@@ -1194,10 +1232,12 @@ int lans_slots(int g_dtype) { return g_dtype == RAFB200_F32 ? kLansSlots32 : kLa
 int lans_a_elems(int g_dtype) { return g_dtype == RAFB200_F32 ? kLansAElems32 : kLansAElems16; }
 
 // How many chunks of one tensor may wait on chip at the same time, for a grid with
-// `cells_total` tensor-memory cells (blocks x kLansCells): four fifths, so that every block -
-// the parked items are dealt out evenly - keeps cells for the tensors before and after it.
+// `cells_total` cells (blocks x kLansCells): five eighths.  Every block - the parked items are
+// dealt out evenly - then keeps cells for the tensors before and after a large one, whose
+// stage 1 overlaps the wait for the large tensor's norms (measured on the BERT-large list:
+// 2.20 ms at 5/8, 2.25 ms at 4/5, 2.27 ms at 3/8).
 uint32_t lans_park_cap(int64_t cells_total) {
-  int64_t cap = cells_total * 4 / 5;
+  const int64_t cap = cells_total * 5 / 8;
   return (uint32_t)(cap < 0 ? 0 : cap);
 }
 
@@ -1275,8 +1315,9 @@ std::vector<Item> build_lans_schedule(const std::vector<int64_t>& numel, int a_e
 // themselves, so that a tensor's parked items spread evenly over the blocks whatever they
 // are interleaved with.  Inside a block the r-th item of either sort goes to the list of
 // the even slots when (r % slots) is even, else to the list of the odd slots: the two lists
-// get work in proportion to their slots, and of any 17 consecutive parked items at most 10
-// land in the even list (11 cells) and 9 in the odd one (10 cells).
+// get work in proportion to their slots, and of any 19 consecutive parked items (the most a
+// block gets of one tensor, see lans_park_cap) at most 11 land in either list, which has 14 or
+// 15 cells of its own.
 // Result: off[0 .. 2 * grid] (list 2b = even slots of block b, 2b + 1 = odd slots),
 // followed (8-byte aligned) by the items.
 std::vector<uint32_t> partition_lans_items(const std::vector<Item>& sched, int grid, int slots) {
@@ -1382,12 +1423,12 @@ using namespace rafb200;
 // Everything rafb200_lans keeps in caller-provided device memory (header, per-tensor
 // control words, descriptor row, work-item table) for ONE tensor of at most
 // kStaticMaxElems elements, as a statically allocated device array: every GPU that
-// loads this library holds these 76 KB until the process exits.
+// loads this library holds these 74 KB until the process exits.
 constexpr int64_t kStaticMaxElems = 4ll << 20;  // 4,194,304 elements
 constexpr uint32_t kStaticMaxB = (uint32_t)(kStaticMaxElems / kLansElems);
 constexpr uint32_t kStaticMaxA = (uint32_t)((kStaticMaxElems + kLansAElems32 - 1) / kLansAElems32);
 constexpr size_t kStaticCtlOff = 128, kStaticDescOff = 256, kStaticOffOff = 512, kStaticItemsOff = 2048;
-constexpr int kStaticMaxGrid = (int)((kStaticItemsOff - kStaticOffOff) / 4) - 1;  // 383 blocks
+constexpr int kStaticMaxGrid = ((int)((kStaticItemsOff - kStaticOffOff) / 4) - 1) / 2;  // 191 blocks (two lists each)
 constexpr size_t kStaticBytes = kStaticItemsOff + (size_t)(kStaticMaxA + 2 * kStaticMaxB) * sizeof(Item);
 static __device__ __align__(256) unsigned char g_lans_static_scratch[kStaticBytes];
 

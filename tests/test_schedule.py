@@ -33,7 +33,7 @@ def schedule(numels, g_dtype, with_norm, slots_total, lead_elems, gap_items):
 
 
 def park_cap(cells_total):
-    return cells_total * 4 // 5
+    return cells_total * 5 // 8
 
 
 def check(numels, g_dtype, with_norm, slots_total, lead_elems, gap_items):
@@ -77,12 +77,12 @@ def test_schedule_of_the_benchmark_shapes(with_norm):
     from bench import bert_large_shapes, gpt2_medium_shapes, numel
 
     for shapes, g_dtype in ((bert_large_shapes(), 1), (gpt2_medium_shapes(), 2)):
-        check([numel(s) for s in shapes], g_dtype, with_norm, 148 * 21, 8 << 20, 0)
+        check([numel(s) for s in shapes], g_dtype, with_norm, 148 * 29, 8 << 20, 0)
 
 
 @settings(max_examples=30, deadline=None)
 @given(st.lists(st.one_of(st.integers(0, 5), st.integers(0, 70000), st.integers(0, 1_000_000)), min_size=0, max_size=10),
-       st.sampled_from([0, 1, 2]), st.booleans(), st.sampled_from([1, 3, 21, 147, 3108]),
+       st.sampled_from([0, 1, 2]), st.booleans(), st.sampled_from([1, 3, 29, 147, 4292]),
        st.sampled_from([0, 1, ELEMS, 1 << 20, 8 << 20]), st.sampled_from([0, 1, 7, 300, 5000]))
 def test_schedule_invariants_random_lists(numels, g_dtype, with_norm, slots_total, lead_elems, gap_items):
     check(numels, g_dtype, with_norm, slots_total, lead_elems, gap_items)
@@ -98,6 +98,6 @@ def test_schedule_rejects_bad_arguments():
     one = (C.c_int64 * 1)(10000)
     assert lib.rafb200_lans_schedule(1, one, 0, 1, 0, 0, 0, None, 0, C.byref(count)) == 1  # no slots
     small = (C.c_uint32 * 2)()
-    # 3 gradient-norm items of 4096 + 10 chunks of 1024, 8 of them parked, 2 streamed twice
+    # 3 gradient-norm items of 4096 + 10 chunks of 1024, 6 of them parked, 4 streamed twice
     assert lib.rafb200_lans_schedule(1, one, 0, 1, 10, 0, 0, small, 1, C.byref(count)) == 1
-    assert count.value == 3 + 10 + 2
+    assert count.value == 3 + 10 + 4
