@@ -480,6 +480,34 @@ typedef struct {
   int average;          /* 1: gradients are averaged over ranks ("avg"), 0: summed */
 } rafb200_hyper;
 
+/* ------------------------------------------------------------------------- */
+/* Symmetric memory (no counterpart in the reference)                          */
+/* ------------------------------------------------------------------------- */
+/*
+ * Device memory that every rank of ONE node has mapped, for the collectives this
+ * library runs with its own kernels (rafb200_zero_attach_symmetric).  Each rank
+ * allocates `bytes` (rounded up to the driver's granularity) with a shareable
+ * handle, the ranks exchange the handles over abstract unix sockets named after
+ * `key` (any string that is the same on every rank of the job and different
+ * between jobs on the machine, e.g. "<master address>:<port>") and map each
+ * other's memory; with want_multicast != 0, on GPUs that support it, rank 0 also
+ * creates an NVSwitch multicast object that every rank binds its memory to.
+ * Collective: every rank calls it, in the same order if it is called more than
+ * once; a rank that does not arrive costs the others `timeout_ms`, after which
+ * they get RAFB200_TIMEOUT and nothing stays allocated.  The memory is zero-
+ * filled by the caller, not here.  rafb200_symm_pointers: peer[q] = rank q's
+ * memory as addressable from this process (peer[rank] = this rank's own), and
+ * the multicast address or NULL.  rafb200_symm_free synchronises the device and
+ * unmaps everything; every rank frees, after the last kernel that used the
+ * peers' memory has finished everywhere.
+ */
+typedef struct rafb200_symm_s* rafb200_symm_t;
+RAFB200_API int rafb200_symm_alloc(int world_size, int rank, int device, size_t bytes, const char* key,
+                                   int want_multicast, int timeout_ms, rafb200_symm_t* symm);
+RAFB200_API size_t rafb200_symm_bytes(rafb200_symm_t symm);
+RAFB200_API int rafb200_symm_pointers(rafb200_symm_t symm, void** peer, void** multicast);
+RAFB200_API int rafb200_symm_free(rafb200_symm_t symm);
+
 typedef struct rafb200_zero_s* rafb200_zero_t;
 
 RAFB200_API int rafb200_zero_create(rafb200_plan_t plan, rafb200_comm_t comm, int g_dtype,

@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -154,15 +155,15 @@ class ZeroStep:
         check(_lib.load().rafb200_zero_launch_counts(self.handle, C.byref(a), C.byref(b)))
         return a.value, b.value
 
-    def attach_symmetric(self, group=None, comm_blocks: int = 0, multicast: bool = True):
+    def attach_symmetric(self, group=None, comm_blocks: int = 0, multicast: bool = True,
+                         allocator: str = "library", key: Optional[str] = None, timeout_ms: int = 60000):
         """Switch the collectives of this step from NCCL to the library's own kernels over
-        symmetric memory.  torch.distributed._symmetric_memory provides the plumbing only:
-        one allocation mapped into every rank of ``group`` (default: the world group, which
-        must be initialised) plus its NVSwitch multicast address.  Call on every rank,
-        before :meth:`bind`."""
-        import torch.distributed as td
-        import torch.distributed._symmetric_memory as symm
-
+        symmetric memory: one allocation mapped into every rank plus, with ``multicast``, its
+        NVSwitch multicast address.  ``allocator="library"`` takes the memory from
+        rafb200_symm_alloc (``key``: a string common to the ranks of this job, default
+        MASTER_ADDR:MASTER_PORT); ``allocator="torch"`` from torch.distributed._symmetric_memory
+        on ``group`` (default: the world group, which must be initialised).  Call on every
+        rank, before :meth:`bind`."""
         lib = _lib.load()
         gb, pb, sb = C.c_size_t(), C.c_size_t(), C.c_size_t()
         check(lib.rafb200_zero_flat_bytes(self.handle, C.byref(gb), C.byref(pb), C.byref(sb)))
@@ -173,20 +174,50 @@ class ZeroStep:
         sig_off, g_off = 0, up(sb.value)
         p_off = g_off + up(gb.value)
         total = p_off + up(pb.value)
-        buf = symm.empty(total, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
-        handle = symm.rendezvous(buf, group if group is not None else td.group.WORLD)
-        buf.zero_()  # padding rows, alignment gaps and barrier words all start at zero
-        torch.cuda.synchronize()
-        handle.barrier()
-        torch.cuda.synchronize()
-        bases = [int(x) for x in handle.buffer_ptrs]
-        mc = int(handle.multicast_ptr) if multicast else 0
+        n, rank = self.comm.size, self.comm.rank
+        if allocator == "library":
+            if key is None:
+                key = f"{os.environ.get('MASTER_ADDR', 'local')}:{os.environ.get('MASTER_PORT', '0')}"
+            h = C.c_void_p()
+            check(lib.rafb200_symm_alloc(n, rank, torch.cuda.current_device(), total, key.encode(),
+                                         1 if multicast else 0, int(timeout_ms), C.byref(h)))
+            ptrs = (C.c_void_p * n)()
+            mcp = C.c_void_p()
+            check(lib.rafb200_symm_pointers(h, ptrs, C.byref(mcp)))
+            bases = [int(ptrs[q]) for q in range(n)]
+            mc = int(mcp.value or 0)
+            buf = _device_view(bases[rank], total, torch.uint8)
+            buf.zero_()  # padding rows, alignment gaps and barrier words all start at zero
+            torch.cuda.synchronize()
+            if n > 1:  # every rank has cleared its memory before any rank's kernels touch it
+                from . import distributed as dist
+
+                token = torch.zeros(1, device="cuda")
+                check(lib.rafb200_allreduce(self.comm.handle, token.data_ptr(), token.data_ptr(), 1,
+                                            dist.dtype_code(token.dtype), b"sum", None))
+                torch.cuda.synchronize()
+            self._symm = (buf, h)
+            self._symm_lib = h
+        elif allocator == "torch":
+            import torch.distributed as td
+            import torch.distributed._symmetric_memory as symm
+
+            buf = symm.empty(total, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+            handle = symm.rendezvous(buf, group if group is not None else td.group.WORLD)
+            buf.zero_()
+            torch.cuda.synchronize()
+            handle.barrier()
+            torch.cuda.synchronize()
+            bases = [int(x) for x in handle.buffer_ptrs]
+            mc = int(handle.multicast_ptr) if multicast else 0
+            self._symm = (buf, handle)  # keeps the mapping alive
+        else:
+            raise ValueError(f"unknown allocator {allocator!r}")
         pa = _lib.ptr_array
         check(lib.rafb200_zero_attach_symmetric(
             self.handle, pa([b + g_off for b in bases]), (mc + g_off) if mc else None,
             pa([b + p_off for b in bases]), (mc + p_off) if mc else None,
             pa([b + sig_off for b in bases]), int(comm_blocks)))
-        self._symm = (buf, handle)  # keeps the mapping alive
         self.declare_arena(buf)
         self._arena = (g_off, p_off)
         self.multicast = bool(mc)
@@ -257,6 +288,16 @@ class ZeroStep:
             torch.cuda.synchronize()
             _lib.load().rafb200_zero_destroy(self.handle)
             self.handle = None
+        if getattr(self, "_symm_lib", None):
+            # the peers may still be reading this rank's memory: leave together
+            if self.comm.size > 1:
+                token = torch.zeros(1, device="cuda")
+                check(_lib.load().rafb200_allreduce(self.comm.handle, token.data_ptr(), token.data_ptr(), 1, 0,
+                                                    b"sum", None))
+                torch.cuda.synchronize()
+            self._symm = None
+            _lib.load().rafb200_symm_free(self._symm_lib)
+            self._symm_lib = None
 
     def __del__(self):
         try:

@@ -126,8 +126,10 @@ def check_collectives(comm):
 
 
 # collectives by NCCL / own kernels with / without multicast / own kernels on gradients and
-# parameters that live inside the symmetric buffer (no pack and unpack copies)
-MODES = ["nccl", "multimem", "peer", "view"]
+# parameters that live inside the symmetric buffer (no pack and unpack copies) - these three on
+# memory from rafb200_symm_alloc - / own kernels with multicast on memory from
+# torch.distributed._symmetric_memory
+MODES = ["nccl", "multimem", "peer", "view", "torch"]
 # ... and each of them again with all steps queued back to back: no host synchronisation and no
 # status read between steps, so the values also cover the ordering ACROSS steps (the fence at the
 # start of a step, barrier epochs, the all-gather of step s overlapping the reduce-scatter of
@@ -144,7 +146,7 @@ def run_zero(comm, out_dir, tag):
         z = ZeroStep(plan, comm, g_dtype, p_dtype, optimizer)
         gviews = pviews = None
         if mode != "nccl":
-            z.attach_symmetric(multicast=(mode != "peer"))
+            z.attach_symmetric(multicast=(mode != "peer"), allocator="torch" if mode == "torch" else "library")
             if mode != "peer":
                 assert z.multicast, "no multicast address on this box"
             if mode == "view":
