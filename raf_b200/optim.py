@@ -108,9 +108,12 @@ class _ZeroWrapper:
         self.zero_opt_level = dcfg.zero_opt_level
         n = comm.size if dcfg.zero_opt_level else 1
         rank = comm.rank if dcfg.zero_opt_level else 0
-        if n != comm.size:
-            raise NotImplementedError("zero_opt_level 0 on several ranks (plain all-reduce data "
-                                      "parallelism) is outside the ZeRO path")
+        # zero_opt_level 0 on several ranks: plain data parallelism - every rank keeps the whole
+        # state, the gradients are averaged in place by _allreduce (what AutoDataParallel inserts,
+        # src/pass/data_parallel.cc) and the update runs unsharded
+        self._allreduce_first = n != comm.size
+        if self._allreduce_first:
+            comm = self._local_comm = dist.Communicator(1, 0, torch.cuda.current_device())
         self.plan = Plan([tuple(p.shape) for p in self.model_params], n, rank,
                          int(dcfg.group_bucket_size))
         gdt = grad_dtype if grad_dtype is not None else self.dtype
@@ -147,11 +150,16 @@ class _ZeroWrapper:
                            self._w, self._m, self._v if self.optimizer != "sgd" else None)
             self._bound = key
         self.step_no += 1
+        if self._allreduce_first:
+            dist.allreduce(list(grads), "avg")
         self.zero.step(self.hyper, self.step_no)
 
     def close(self):
         self.zero.close()
         self.plan.close()
+        if getattr(self, "_local_comm", None) is not None:
+            self._local_comm.close()
+            self._local_comm = None
 
 
 def with_sgd(learning_rate=0.1, momentum=0.01):

@@ -203,12 +203,42 @@ def run_zero(comm, out_dir, tag):
         plan.close()
 
 
+def check_plain_data_parallel(comm):
+    """zero_opt_level 0 on several ranks: gradients averaged by _allreduce, unsharded update
+    (python/raf/optim/sgd.py:118-150 with the data-parallel pass instead of the ZeRO one)."""
+    from raf_b200 import optim
+
+    n, r = comm.size, comm.rank
+    cfg = dist.get_config()
+    before = cfg.dumps()
+    cfg.zero_opt_level = 0
+    cfg.enable_data_parallel = True
+    try:
+        rng = np.random.default_rng(5)
+        x0 = {f"w{i}": torch.from_numpy((rng.standard_normal(s) * 0.02).astype(np.float32)).cuda()
+              for i, s in enumerate([(33, 7), (5,), (1024,)])}
+        want = {k: v.clone() for k, v in x0.items()}
+        opt = optim.with_sgd(learning_rate=0.1, momentum=0.01)(x0)
+        grads = [local_grad(r, 1, i, v.numel(), "float32", 1.0).cuda().reshape(v.shape) for i, v in enumerate(x0.values())]
+        opt.step(grads)
+        torch.cuda.synchronize()
+        for i, (k, v) in enumerate(want.items()):
+            total = sum(local_grad(q, 1, i, v.numel(), "float32", 1.0) for q in range(n)).reshape(v.shape) / n
+            assert torch.allclose(grads[i].cpu(), total, rtol=0, atol=0), "gradients are averaged in place"
+            exp = v.cpu() - 0.1 * total  # v1 = 0.01 * 0 + g ; x1 = x0 - lr * v1
+            assert torch.allclose(x0[k].cpu(), exp, rtol=1e-7, atol=1e-9), (k, (x0[k].cpu() - exp).abs().max())
+        opt.close()
+    finally:
+        cfg.loads(before)
+
+
 def main():
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     import torch.distributed as td
 
     comm = dist.init_from_env(timeout_ms=120000)
     check_collectives(comm)
+    check_plain_data_parallel(comm)
     # torch.distributed only carries the symmetric-memory rendezvous of the two non-NCCL modes
     td.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     for mode in MODES:
