@@ -1,41 +1,46 @@
-// raf.op.lans as ONE persistent kernel that keeps a tensor on chip between its passes.
+// raf.op.lans as ONE persistent kernel that keeps a chunk on chip between its two stages.
 //
 // The reference runs four norm reductions and two element-wise stages as about
 // fifty launches with a global dependency between them
 // (src/op/dialect/cuda/kernels/multi_tensor_lans.cu:401-450) and moves about 68 bytes
 // per element.  The dependencies are real: stage 1 needs ||g|| of the whole tensor,
 // stage 2 needs ||p||, ||update_m|| and ||update_g|| of the whole tensor.  Here one
-// block per SM owns a set of shared-memory SLOTS of 1024 elements (g, p, m, v); a
-// slot is filled once by the TMA unit and keeps its data while the tensor-wide norm it
-// waits for is being completed by the other blocks:
+// block per SM owns shared-memory SLOTS of 1024 elements (g, p, m, v), filled by the TMA
+// unit, and CELLS of 1024 elements (p, update_m, update_g) in which a chunk waits while the
+// other blocks complete the tensor-wide norms: 21 cells in the SM's tensor memory
+// (tcgen05.alloc / st / ld - no MMA is issued, the 256 KB serve as scratchpad) and 8 in
+// shared memory.
 //   item A    (7168 / 4096 elements of g)  sum of squares of the scaled gradient -> ||g||.
 //             Runs a few million elements ahead of the rest, so ||g|| is final
-//             when a tensor's other items are drawn (the re-read of g comes from L2).
+//             when a tensor's other items come up (the re-read of g comes from L2).
 //   item BCp  "parked": load g, p, m, v once; when ||g|| is final compute stage 1,
-//             store m and v, leave p, update_m, update_g in the slot and add the
-//             sums of squares to the tensor's accumulators; when the three norms are
-//             final, finish stage 2 from the slot and store p and the model-dtype copy.
+//             store m and v, move p, update_m, update_g into a cell and add the sums of
+//             squares to the tensor's accumulators; when the three norms are final,
+//             finish stage 2 from the cell and store p and the model-dtype copy.
 //             DRAM traffic: every array read once and written once.
-//   items Bs + Cs  "streamed", for the part of a tensor that exceeds what the grid can
-//             park (about two thirds of all slots): Bs computes the sums and stores
+//   items Bs + Cs  "streamed", for the part of a tensor that exceeds what the grid may
+//             park (five eighths of all cells): Bs computes the sums and stores
 //             nothing, Cs loads the chunk again, recomputes stage 1 with the same
 //             instructions (same bits) and stores everything.
-// The host fixes the order of the items and deals them out to the blocks in turn, so
-// every block runs its own list in order.  An item only ever waits for items that come
-// earlier in the global order, and a tensor's parked items never fill all the slots of a
-// block, so the bounded waits below cannot deadlock.
+// The host fixes the order of the items and deals them out to the blocks in turn - inside a
+// block to the list of its even or of its odd slots - so every list is run in order.  An
+// item only ever waits for items that come earlier in the global order; cells are granted
+// by the parked items' running numbers (a later item takes one only while a free cell
+// remains for every earlier item without one), and a tensor has fewer parked items in a list
+// than the list has cells: the bounded waits below cannot deadlock.
 //
-// Roles inside a block (608 threads):
+// Roles inside a block (640 threads):
 //   warps 0-15  four consumer groups of four warps; group q serves the slots s with
-//               s % 4 == q, so the threads that park a chunk are the ones that finish it.
-//               When an item's last operation is done, warp 0 of the group starts the next
-//               resolved item in the slot right away (bulk copies + first operation).
-//   warp 16     prefetcher: resolves the block's items ahead of their use (item ->
-//               descriptor -> the norms its first operation needs are final) into a ring.
-//   warp 17     parker: lane s polls the norm words of the tensor whose chunk is parked in
-//               slot s and queues the chunk's second half; lanes that wait for the same
-//               tensor share one load, so one round trip to L2 serves every slot.
-//   warp 18     publisher: collects the groups' partial sums, adds them (in double
+//               s % 4 == q.  The warps of a group take turns in the bookkeeping after an
+//               operation: free the slot or cell, take the slot's next item from its
+//               mailbox and start it (bulk copies + first operation).
+//   warps 16,17 prefetchers, one per list: a lane per mailbox resolves the items ahead of
+//               their use (item -> descriptor -> the norms its first operation needs are
+//               final -> a cell if it parks -> mailbox).
+//   warp 18     parker: owns the tensor-memory allocation; lane c polls the norm words of the
+//               tensor whose chunk is parked in cell c and queues the chunk's second half;
+//               lanes that wait for the same tensor share one load.
+//   warp 19     publisher: collects the groups' partial sums, adds them (in double
 //               precision) to the tensor's accumulators, counts arrivals; the last
 //               arrival takes the square root and publishes the norm together with its
 //               "final" bit in one word.

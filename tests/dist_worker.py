@@ -232,6 +232,50 @@ def check_plain_data_parallel(comm):
         cfg.loads(before)
 
 
+def check_wait_expiry(comm):
+    """A rank that never joins a step: the others' cross-GPU barrier gives up after its (short)
+    limit, the step reports RAFB200_DEVICE_WAIT_EXPIRED instead of hanging, the next step is
+    refused on the host, and the context stays usable.  Plain peer loads, no multicast."""
+    import time
+
+    from raf_b200._lib import RafB200Error
+
+    n, r = comm.size, comm.rank
+    plan = Plan(SHAPES, n, r, BUCKET)
+    z = ZeroStep(plan, comm, "float32", "float32", "sgd")
+    z.attach_symmetric(multicast=False)
+    z.set_wait_limit(200)
+    ses = [int(x) for x in plan.shard_elems]
+    grads = [torch.zeros(numel(s), device="cuda") for s in SHAPES]
+    params = [torch.zeros(numel(s), device="cuda") for s in SHAPES]
+    tp = [torch.zeros(se, device="cuda") for se in ses]
+    tm = [torch.zeros(se, device="cuda") for se in ses]
+    z.bind(grads, params, tp, tm, None)
+    hyper = make_hyper("sgd", learning_rate=0.1, mu=0.9, weight_decay=0.0, grad_scale=1.0, average=1)
+    dist.allreduce(torch.zeros(1, device="cuda"))
+    torch.cuda.synchronize()
+    if r != n - 1:
+        z.step(hyper, 1)
+        try:
+            z.status()
+            raise AssertionError("the step completed although one rank never joined it")
+        except RafB200Error as e:
+            assert e.status == 5, e  # RAFB200_DEVICE_WAIT_EXPIRED
+        try:
+            z.step(hyper, 2)
+            raise AssertionError("a step was queued after a wait had expired")
+        except RafB200Error as e:
+            assert e.status == 5, e
+        # the context is intact: ordinary work still runs
+        assert float((torch.ones(1000, device="cuda") * 2).sum()) == 2000.0
+    else:
+        time.sleep(1.0)  # takes no part in the step; leaves only when the others are done waiting
+    dist.allreduce(torch.zeros(1, device="cuda"))
+    torch.cuda.synchronize()
+    z.close()
+    plan.close()
+
+
 def main():
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     import torch.distributed as td
@@ -246,6 +290,7 @@ def main():
     torch.cuda.synchronize()
     td.barrier()
     torch.cuda.synchronize()
+    check_wait_expiry(comm)
     comm.close()
     td.destroy_process_group()
     print(f"rank {comm.rank}: ok", flush=True)
