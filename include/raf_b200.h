@@ -548,6 +548,22 @@ RAFB200_API int rafb200_zero_step(rafb200_zero_t zero, const rafb200_hyper* hype
  * layer of this package does).  Call between rafb200_zero_create and
  * rafb200_zero_bind, on every rank or on none.
  */
+/*
+ * LANS with the collectives INSIDE the update kernel (symmetric mode only; no counterpart
+ * in the reference, whose collectives are separate NCCL launches, nccl.cc:189-190,308,387).
+ * mode 1: the kernel's gradient-norm items read the sum over ranks of their chunk through
+ * the switch (multimem.ld_reduce, or the peers one by one without a multicast address), write
+ * it to the local gradient block for the later stages and square what they wrote; the
+ * reduce-scatter kernels disappear.  mode 2: in addition stage 2 stores the model-dtype copy
+ * into every rank's parameter buffer (multimem.st, or peer stores); the all-gather kernels
+ * disappear too.  A step is then: pack (tensors bound outside the buffer) -> one barrier ->
+ * ONE update launch over all tensors -> one barrier -> unpack, on the compute stream; link
+ * traffic and memory traffic interleave inside the kernel instead of running as separate
+ * kernels.  Needs normalize_grad (the gradient-norm pass is what reads the gradients); a step
+ * without it takes the bucketed pipeline.  Call after rafb200_zero_attach_symmetric and
+ * before rafb200_zero_bind, with the same mode on every rank.
+ */
+RAFB200_API int rafb200_zero_set_fused(rafb200_zero_t zero, int mode);
 RAFB200_API int rafb200_zero_flat_bytes(rafb200_zero_t zero, size_t* g_bytes, size_t* p_bytes,
                                         size_t* signal_bytes);
 RAFB200_API int rafb200_zero_attach_symmetric(rafb200_zero_t zero, void* const* g_peer, void* g_mc,

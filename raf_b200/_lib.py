@@ -77,6 +77,7 @@ SIGNATURES = {
     "rafb200_dist_config_set": (_i, [_vp]),
     "rafb200_stream_get": (_i, [_i, _i, _i, _P(_vp)]),
     "rafb200_stream_release_all": (_i, []),
+    "rafb200_zero_set_fused": (_i, [_vp, _i]),
     "rafb200_symm_alloc": (_i, [_i, _i, _i, C.c_size_t, C.c_char_p, _i, _i, _P(_vp)]),
     "rafb200_symm_bytes": (C.c_size_t, [_vp]),
     "rafb200_symm_pointers": (_i, [_vp, _vp, _P(_vp)]),

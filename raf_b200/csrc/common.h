@@ -119,6 +119,20 @@ struct LansHeader {
   float inv_bc2;
 };
 
+constexpr int kSymmMaxWorld = 16;   // ranks of one NVLink domain addressed by value
+
+// Collectives inside the LANS kernel (see LansParams in lans.cu): where the symmetric gradient
+// and parameter buffers are mapped.  Set on a list by tensor_list_set_fuse, together with each
+// tensor's byte offset inside the symmetric gradient buffer, which then takes the place of
+// TensorDesc::first_chunk / nchunks (low / high word) - the LANS kernel reads neither.
+struct LansFuse {
+  int world = 0, rank = 0, fuse_rs = 0, fuse_ag = 0;
+  const char* g_mc = nullptr;
+  char* p_mc = nullptr;
+  const char* g_peer[kSymmMaxWorld] = {};
+  char* p_peer[kSymmMaxWorld] = {};
+};
+
 }  // namespace rafb200
 
 // The opaque list object of the C ABI.
@@ -147,4 +161,9 @@ struct rafb200_tensor_list_s {
   int lans_grid = 0;        // blocks the LANS schedule was built for
   bool custom_items = false;
   uint64_t wait_ns = 2000000000ull;  // bound of every wait inside the LANS kernel
+  rafb200::LansFuse fuse;            // collectives inside the LANS kernel, off by default
 };
+
+namespace rafb200 {
+int tensor_list_set_fuse(rafb200_tensor_list_s* l, const LansFuse& f, const int64_t* sym_off_bytes);
+}

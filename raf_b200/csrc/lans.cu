@@ -51,6 +51,8 @@
 #include <type_traits>
 
 #include "common.h"
+#include "symm.h"
+#include "symm_dev.cuh"
 #include "update_core.cuh"
 
 namespace rafb200 {
@@ -72,7 +74,53 @@ struct LansParams {
   const float* step_dev;
   int bias_correction;
   uint64_t wait_ns;  // bound of every wait inside the kernel
+  // Collectives inside the kernel (n > 1, symmetric memory; all zero otherwise).
+  // fuse_rs: an A item does not read the local gradient but the SUM over ranks of the chunk -
+  // through the multicast address (g_mc) or peer by peer (g_peer) - at byte offset
+  // TensorDesc::sym_off + chunk start, writes it to the local gradient block (desc.g) for the
+  // later stages and squares what it wrote.  fuse_ag: the model-dtype copy (`out`, which then
+  // lies in this rank's mapping p_peer[rank] of the symmetric parameter buffer) is stored into
+  // every rank's buffer: through p_mc, or to the peers one by one.
+  int world, rank, fuse_rs, fuse_ag;
+  const char* g_mc;
+  char* p_mc;
+  const char* g_peer[kSymmMaxWorld];
+  char* p_peer[kSymmMaxWorld];
 };
+
+// The model-dtype copy of four elements, into every rank's parameter buffer.
+template <typename OT>
+__device__ __forceinline__ void store_out_everywhere(const LansParams& P, OT* local, const F4& v) {
+  uint32_t w[4];
+  if (sizeof(OT) == 4) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) w[j] = __float_as_uint(v.x[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const OT lo = Elem<OT>::from_f32(v.x[2 * j]), hi = Elem<OT>::from_f32(v.x[2 * j + 1]);
+      w[j] = (uint32_t)(*reinterpret_cast<const unsigned short*>(&lo)) |
+             ((uint32_t)(*reinterpret_cast<const unsigned short*>(&hi)) << 16);
+    }
+  }
+  const size_t delta = (size_t)(reinterpret_cast<char*>(local) - P.p_peer[P.rank]);
+  if (P.p_mc) {
+    if (sizeof(OT) == 4) mc_st(P.p_mc + delta, make_uint4(w[0], w[1], w[2], w[3]));
+    else mc_st8(P.p_mc + delta, make_uint2(w[0], w[1]));
+  } else {
+    for (int q = 0; q < P.world; ++q) {
+      char* dst = P.p_peer[q] + delta;
+      if (sizeof(OT) == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+      else *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+    }
+  }
+}
+template <typename OT>
+__device__ __forceinline__ void store_out_everywhere1(const LansParams& P, OT* local, float x) {
+  const size_t delta = (size_t)(reinterpret_cast<char*>(local) - P.p_peer[P.rank]);
+  const OT val = Elem<OT>::from_f32(x);
+  for (int q = 0; q < P.world; ++q) *reinterpret_cast<OT*>(P.p_peer[q] + delta) = val;
+}
 
 __device__ __forceinline__ uint64_t global_ns() {
   uint64_t t;
@@ -652,11 +700,15 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
           const int64_t left = numel - start;
           const int n = left < per ? (int)left : per;
           constexpr int gran = 16 / (int)sizeof(GT);  // elements per 16 bytes of gradient
-          const int nbulk = (flags & kFlagBulk) ? (n / gran) * gran : 0;
+          const bool through_switch = kind == kKindA && P.fuse_rs != 0;
+          const int nbulk = ((flags & kFlagBulk) && !through_switch) ? (n / gran) * gran : 0;
           const uint32_t op = kind == kKindA ? kOpA : kind == kKindBs ? kOpB : kind == kKindCs ? kOpC : kOpBP;
           SlotMeta& mt = s_ring[mb];
           mt.g = dg + start * (int64_t)sizeof(GT);
-          mt.p = dp + start;
+          // an A item that reads through the switch gets the byte offset of its chunk inside the
+          // symmetric gradient buffer instead of p, which it does not use
+          mt.p = through_switch ? reinterpret_cast<float*>((((uint64_t)d3.y << 32) | d3.x) + (uint64_t)start * sizeof(GT))
+                                : dp + start;
           mt.m = dm + start;
           mt.v = dv + start;
           mt.out = dout ? dout + start * (int64_t)sizeof(OT) : nullptr;
@@ -847,6 +899,16 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
   const int grp = warp >> 2, wig = warp & 3, gtid = tid & (kGroupThreads - 1);
   Policies pol;
   pol.init();
+  // the model-dtype copy: a local store, or - with the all-gather inside the kernel - a store
+  // into every rank's parameter buffer
+  auto put_out4 = [&](OT* dst, const F4& v) {
+    if (P.fuse_ag) store_out_everywhere<OT>(P, dst, v);
+    else Elem<OT>::template store4<kStream>(dst, v, pol);
+  };
+  auto put_out1 = [&](OT* dst, float x) {
+    if (P.fuse_ag) store_out_everywhere1<OT>(P, dst, x);
+    else *dst = Elem<OT>::from_f32(x);
+  };
   for (uint32_t i = 0;; ++i) {
     const uint32_t qi = (uint32_t)grp * kQueueDepth + (i % kQueueDepth);
     bool ok = ring_wait(bar_queue + 8 * qi, (i / kQueueDepth) & 1u, P.hdr, kErrRing, 0x1000u | (uint32_t)grp,
@@ -891,7 +953,65 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
     // code without per-vector tests; ragged or unaligned items take the general code below.
     // Both add an element's square into the same accumulator in the same order.
     const bool whole = nbulk == ((op == kOpA) ? L::kAElems : kLansElems);
-    if (whole && op == kOpA) {
+    if (op == kOpA && P.fuse_rs) {
+      // Reduce-scatter inside the kernel: the chunk's sum over ranks, 16 bytes per access, in
+      // fp32 with one rounding - written to the local gradient block for the later stages and
+      // squared as written.  The symmetric layout pads every row block to 16 bytes with zeros,
+      // so the last vector may run past n without harm.
+      constexpr int kDT = sizeof(GT) == 4 ? RAFB200_F32 : (std::is_same<GT, __half>::value ? RAFB200_F16 : RAFB200_BF16);
+      constexpr int kEV = 16 / (int)sizeof(GT);                 // elements per access
+      constexpr int kAcc = L::kAElems / (kGroupThreads * kEV);  // accesses per thread: 7 | 8
+      const size_t off = (size_t)reinterpret_cast<uintptr_t>(gp);
+      char* dst = const_cast<char*>(reinterpret_cast<const char*>(gg));
+      const int nvec = (n + kEV - 1) / kEV;
+      if (lane == 0) mbar_arrive(my_done);  // nothing of the slot is used
+      uint4 r[kAcc];
+      if (P.g_mc) {
+#pragma unroll
+        for (int u = 0; u < kAcc; ++u) {
+          const int i = gtid + u * kGroupThreads;
+          r[u] = (i < nvec) ? mc_ld_reduce<kDT>(P.g_mc + off + (size_t)i * 16) : make_uint4(0, 0, 0, 0);
+        }
+      } else {
+        // peer by peer in a fixed order; four accesses in flight per thread
+#pragma unroll
+        for (int u0 = 0; u0 < kAcc; u0 += 4) {
+          float acc[4][8];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[u][j] = 0.f;
+          for (int q = 0; q < P.world; ++q) {
+            uint4 t[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const int i = gtid + (u0 + u) * kGroupThreads;
+              t[u] = (u0 + u < kAcc && i < nvec) ? peer_ld(P.g_peer[q] + off + (size_t)i * 16) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) accumulate<kDT>(acc[u], t[u]);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (u0 + u < kAcc) r[u0 + u] = round_once<kDT>(acc[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kAcc; ++u) {
+        const int i = gtid + u * kGroupThreads;
+        if (i >= nvec) continue;
+        *reinterpret_cast<uint4*>(dst + (size_t)i * 16) = r[u];
+        float sq[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        accumulate<kDT>(sq, r[u]);  // the rounded values, as stage 1 will read them
+#pragma unroll
+        for (int j = 0; j < (kEV < 8 ? kEV : 8); ++j) {
+          const float x = sq[j] * s1.gscale;
+          acc0 = fmaf(x, x, acc0);
+        }
+      }
+      __threadfence();  // the block of another SM that waits for ||g|| reads these stores next
+      publishes = true;
+    } else if (whole && op == kOpA) {
       constexpr int kPasses = L::kAElems / (kGroupThreads * kVec);
       constexpr int kBatch = kPasses % 7 == 0 ? 7 : 8;  // vectors in flight per thread
       static_assert(kPasses % kBatch == 0, "an A item is whole batches of passes");
@@ -927,7 +1047,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
       if (gout) {
 #pragma unroll
         for (int q = 0; q < kBVecs; ++q)
-          Elem<OT>::template store4<kStream>(gout + q * (kGroupThreads * kVec) + gtid * kVec, rp[q], pol);
+          put_out4(gout + q * (kGroupThreads * kVec) + gtid * kVec, rp[q]);
       }
     } else if (whole) {
       F4 rg[kBVecs], rp[kBVecs], rm[kBVecs], rv[kBVecs], ua[kBVecs], ub[kBVecs];
@@ -965,7 +1085,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
         if (gout) {
 #pragma unroll
           for (int q = 0; q < kBVecs; ++q)
-            Elem<OT>::template store4<kStream>(gout + q * (kGroupThreads * kVec) + gtid * kVec, rp[q], pol);
+            put_out4(gout + q * (kGroupThreads * kVec) + gtid * kVec, rp[q]);
         }
       } else {
         publishes = true;
@@ -1026,13 +1146,13 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
           rp[q].x[j] = fmaf(ratio_g, ug[q].x[j], fmaf(ratio_m, um[q].x[j], rp[q].x[j]));
         if (e < nbulk) {
           Elem<float>::template store4<kStream>(gp + e, rp[q], pol);
-          if (gout) Elem<OT>::template store4<kStream>(gout + e, rp[q], pol);
+          if (gout) put_out4(gout + e, rp[q]);
         } else {
 #pragma unroll
           for (int j = 0; j < kVec; ++j)
             if (e + j < n) {
               gp[e + j] = rp[q].x[j];
-              if (gout) gout[e + j] = Elem<OT>::from_f32(rp[q].x[j]);
+              if (gout) put_out1(gout + e + j, rp[q].x[j]);
             }
         }
       }
@@ -1084,7 +1204,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
             Elem<float>::template store4<kStream>(gp + e, rp[q], pol);
             Elem<float>::template store4<kStream>(gm + e, rm[q], pol);
             Elem<float>::template store4<kStream>(gv + e, rv[q], pol);
-            if (gout) Elem<OT>::template store4<kStream>(gout + e, rp[q], pol);
+            if (gout) put_out4(gout + e, rp[q]);
           } else {
 #pragma unroll
             for (int j = 0; j < kVec; ++j)
@@ -1092,7 +1212,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
                 gp[e + j] = rp[q].x[j];
                 gm[e + j] = rm[q].x[j];
                 gv[e + j] = rv[q].x[j];
-                if (gout) gout[e + j] = Elem<OT>::from_f32(rp[q].x[j]);
+                if (gout) put_out1(gout + e + j, rp[q].x[j]);
               }
           }
         }
@@ -1466,8 +1586,23 @@ int rafb200_lans(rafb200_tensor_list_t list, int step, const float* step_dev, fl
   if (list->total_elems == 0) return RAFB200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-  LansParams P;
+  LansParams P{};
   P.descs = list->dev_desc;
+  const LansFuse& fu = list->fuse;
+  if (fu.fuse_rs || fu.fuse_ag) {
+    RAFB200_REQUIRE(!fu.fuse_rs || normalize_grad,
+                    "rafb200_lans: reading the gradients through the switch needs the gradient-norm pass");
+    P.world = fu.world;
+    P.rank = fu.rank;
+    P.fuse_rs = fu.fuse_rs;
+    P.fuse_ag = fu.fuse_ag;
+    P.g_mc = fu.g_mc;
+    P.p_mc = fu.p_mc;
+    for (int q = 0; q < kSymmMaxWorld; ++q) {
+      P.g_peer[q] = fu.g_peer[q];
+      P.p_peer[q] = fu.p_peer[q];
+    }
+  }
   const uint32_t* table = normalize_grad ? list->dev_lans_lists : list->dev_lans_lists_nonorm;
   const size_t head = (2 * (size_t)list->lans_grid + 1 + 1) & ~(size_t)1;
   P.block_off = table;
@@ -1542,7 +1677,7 @@ int rafb200_lans_tensor_static(const void* g, int g_dtype, float* p, float* m, f
   const uint32_t cap = lans_park_cap((int64_t)grid * kLansCells);
   const uint32_t n_park = n_b < cap ? n_b : cap;
 
-  LansParams P;
+  LansParams P{};
   P.descs = reinterpret_cast<const TensorDesc*>(ws + kStaticDescOff);
   P.block_off = reinterpret_cast<const uint32_t*>(ws + kStaticOffOff);
   P.items = reinterpret_cast<const Item*>(ws + kStaticItemsOff);

@@ -4,7 +4,6 @@
 
 namespace rafb200 {
 
-constexpr int kSymmMaxWorld = 16;   // ranks of one NVLink domain addressed by value
 constexpr int kSymmLanes = 4;       // independent barrier sequences per signal pad
 constexpr size_t kSymmSignalBytes = kSymmLanes * kSymmMaxWorld * sizeof(uint32_t);
 

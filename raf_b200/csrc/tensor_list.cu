@@ -67,6 +67,25 @@ static int rebuild_lans_schedule(rafb200_tensor_list_s* l) {
 
 using namespace rafb200;
 
+namespace rafb200 {
+int tensor_list_set_fuse(rafb200_tensor_list_s* l, const LansFuse& f, const int64_t* sym_off_bytes) {
+  RAFB200_REQUIRE(l && (f.fuse_rs == 0 || sym_off_bytes), "tensor_list_set_fuse: NULL argument");
+  RAFB200_REQUIRE(f.world >= 1 && f.world <= kSymmMaxWorld && f.rank >= 0 && f.rank < f.world,
+                  "tensor_list_set_fuse: rank %d of %d", f.rank, f.world);
+  l->fuse = f;
+  if (f.fuse_rs) {
+    for (int i = 0; i < l->k; ++i) {
+      RAFB200_REQUIRE(sym_off_bytes[i] >= 0 && sym_off_bytes[i] % 16 == 0,
+                      "tensor_list_set_fuse: offset of tensor %d is not a multiple of 16 bytes", i);
+      l->host_desc[i].first_chunk = (uint32_t)((uint64_t)sym_off_bytes[i] & 0xffffffffu);
+      l->host_desc[i].nchunks = (uint32_t)((uint64_t)sym_off_bytes[i] >> 32);
+    }
+    l->bound = false;  // the rows travel with the next bind
+  }
+  return RAFB200_OK;
+}
+}  // namespace rafb200
+
 extern "C" {
 
 const char* rafb200_last_error(void) { return g_last_error; }

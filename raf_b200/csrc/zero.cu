@@ -183,6 +183,12 @@ struct rafb200_zero_s {
   cudaEvent_t ev_gather = nullptr;
   int comm_blocks = 128;
   int kernels_per_step = 0, collectives_per_step = 0;
+  // LANS with the collectives inside the update kernel (rafb200_zero_set_fused): one list over
+  // all tensors, one launch per step, two cross-GPU barriers per step instead of two per bucket
+  int fused = 0;  // 0 off, 1 reduce-scatter inside the kernel, 2 all-gather too
+  rafb200_tensor_list_t fused_list = nullptr;
+  void* fused_ws = nullptr;
+  size_t fused_ws_bytes = 0;
 };
 
 using namespace rafb200;
@@ -269,6 +275,8 @@ int rafb200_plan_totals(rafb200_plan_t plan, int64_t* elems, int64_t* padded_ele
 
 int rafb200_zero_destroy(rafb200_zero_t z) {
   if (!z) return RAFB200_OK;
+  if (z->fused_list) rafb200_tensor_list_destroy(z->fused_list);
+  if (z->fused_ws) cudaFree(z->fused_ws);
   for (auto* set : {&z->buckets, &z->hbuckets})
    for (auto& b : *set) {
     if (b.list) rafb200_tensor_list_destroy(b.list);
@@ -436,6 +444,11 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
   z->collectives_per_step = 0;
   // Tables that a kernel of an earlier step may still be reading are replaced below.
   RAFB200_CUDA(cudaDeviceSynchronize());
+  // for the one-launch form (z->fused): every tensor's reduced-gradient block, its block of
+  // the local parameter buffer and its byte offset inside the symmetric gradient buffer
+  std::vector<const void*> fused_g((size_t)k, nullptr);
+  std::vector<void*> fused_out((size_t)k, nullptr);
+  std::vector<int64_t> fused_off((size_t)k, 0);
   for (auto* set : {&z->buckets, &z->hbuckets})
    for (auto& b : *set) {
     const bool counted = (set == &z->buckets);
@@ -474,6 +487,11 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
         const size_t red = (size_t)(b.base_elems / z->n + b.off[j]) * gs;
         lg[j] = z->g_red + red;
         rs_segs.push_back(SymmSeg{(size_t)(b.g_flat - z->g_flat) + block(z->rank) * gs, red, bs * gs});
+        if (counted) {
+          fused_g[(size_t)i] = lg[j];
+          fused_out[(size_t)i] = lo[j];
+          fused_off[(size_t)i] = (int64_t)rs_segs.back().off;
+        }
         ag_segs.push_back(SymmSeg{(size_t)(b.p_flat - z->p_flat) + block(z->rank) * ps, 0, bs * ps});
       }
       // A caller tensor that IS the tensor's region of the flat buffer needs no copy.
@@ -538,8 +556,41 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
       else if (b.slot_elems > 0) z->collectives_per_step += 2;  // NCCL calls
     }
   }
+  if (z->fused && z->symmetric) {
+    if (!z->fused_list) {
+      int rc = rafb200_tensor_list_create(k, z->plan.shard_elems.data(), z->g_dtype, z->param_dtype, &z->fused_list);
+      if (rc != RAFB200_OK) return rc;
+      z->fused_ws_bytes = rafb200_lans_workspace_bytes(z->fused_list);
+      RAFB200_CUDA(cudaMalloc(&z->fused_ws, z->fused_ws_bytes));
+    }
+    LansFuse f;
+    f.world = z->n;
+    f.rank = z->rank;
+    f.fuse_rs = 1;
+    f.fuse_ag = z->fused >= 2 ? 1 : 0;
+    f.g_mc = static_cast<const char*>(z->g_mc);
+    f.p_mc = static_cast<char*>(z->p_mc);
+    for (int q = 0; q < z->n; ++q) {
+      f.g_peer[q] = static_cast<const char*>(z->g_peers.ptr[q]);
+      f.p_peer[q] = static_cast<char*>(z->p_peers.ptr[q]);
+    }
+    int rc = tensor_list_set_fuse(z->fused_list, f, fused_off.data());
+    if (rc != RAFB200_OK) return rc;
+    rc = rafb200_tensor_list_bind(z->fused_list, fused_g.data(), z->p.data(), z->m.data(),
+                                  z->v.empty() ? nullptr : z->v.data(), fused_out.data(), nullptr);
+    if (rc != RAFB200_OK) return rc;
+  }
   RAFB200_CUDA(cudaStreamSynchronize(nullptr));  // descriptor tables are in place
   z->bound = true;
+  return RAFB200_OK;
+}
+
+int rafb200_zero_set_fused(rafb200_zero_t z, int mode) {
+  RAFB200_REQUIRE(z && mode >= 0 && mode <= 2, "rafb200_zero_set_fused: mode must be 0, 1 or 2");
+  RAFB200_REQUIRE(mode == 0 || (z->symmetric && z->optimizer == RAFB200_OPT_LANS),
+                  "rafb200_zero_set_fused: needs LANS and attached symmetric memory");
+  RAFB200_REQUIRE(!z->bound, "rafb200_zero_set_fused: call before rafb200_zero_bind");
+  z->fused = mode;
   return RAFB200_OK;
 }
 
@@ -801,6 +852,40 @@ static int step_impl(rafb200_zero_t z, const rafb200_hyper* h, int step, void* c
     for (auto& b : bl) {
       if (host) RAFB200_CUDA(cudaStreamWaitEvent(cs, b.h2d_done, 0));
       int rc = run_update(z, b, h, step, gscale, cs);
+      if (rc != RAFB200_OK) return rc;
+      if ((rc = copy_out(b)) != RAFB200_OK) return rc;
+    }
+    return finish();
+  }
+  if (z->fused && z->symmetric && z->optimizer == RAFB200_OPT_LANS && h->normalize_grad && z->stage_mask == 31) {
+    // The step as one update launch: pack -> every rank's gradients are in place (barrier) ->
+    // the LANS kernel, whose gradient-norm items read the sum over ranks through the switch
+    // and, with z->fused == 2, whose stage 2 stores the model-dtype copy into every rank's
+    // buffer -> (otherwise the all-gather kernels) -> everything has landed (barrier) -> unpack.
+    // All on the compute stream; link-bound and memory-bound items interleave inside the kernel.
+    for (auto& b : z->buckets) {
+      if (host) RAFB200_CUDA(cudaStreamWaitEvent(cs, b.h2d_done, 0));
+      int rc = launch_seg_copy(b.dev_pack, b.dev_pack_items, b.n_pack_items, gs, z->sm_count, cs);
+      if (rc != RAFB200_OK) return rc;
+    }
+    int rc = symm_barrier(z->sig_peers, z->n, z->rank, 0, ++z->epoch[0], z->wait_limit_ns, z->dev_err,
+                          z->host_err_dev, cs);
+    if (rc != RAFB200_OK) return rc;
+    rc = rafb200_lans(z->fused_list, step, nullptr, h->learning_rate, h->beta1, h->beta2, h->eps,
+                      h->bias_correction, h->weight_decay, h->grad_averaging, h->mode, h->normalize_grad,
+                      gscale, z->fused_ws, z->fused_ws_bytes, cs);
+    if (rc != RAFB200_OK) return rc;
+    if (z->fused < 2)
+      for (auto& b : z->buckets) {
+        rc = symm_allgather(z->p_peers, z->p_mc, z->p_flat, b.dev_ag_segs, b.dev_ag_items, b.n_ag_items, z->n,
+                            z->rank, z->comm_blocks, cs);
+        if (rc != RAFB200_OK) return rc;
+      }
+    rc = symm_barrier(z->sig_peers, z->n, z->rank, 1, ++z->epoch[1], z->wait_limit_ns, z->dev_err,
+                      z->host_err_dev, cs);
+    if (rc != RAFB200_OK) return rc;
+    for (auto& b : z->buckets) {
+      rc = launch_seg_copy(b.dev_unpack, b.dev_unpack_items, b.n_unpack_items, ps, z->sm_count, cs);
       if (rc != RAFB200_OK) return rc;
       if ((rc = copy_out(b)) != RAFB200_OK) return rc;
     }

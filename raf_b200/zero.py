@@ -222,6 +222,11 @@ class ZeroStep:
         self._arena = (g_off, p_off)
         self.multicast = bool(mc)
 
+    def set_fused(self, mode: int):
+        """LANS with the collectives inside the update kernel: 1 = reduce-scatter, 2 = all-gather
+        too (rafb200_zero_set_fused).  After attach_symmetric, before bind, on every rank."""
+        check(_lib.load().rafb200_zero_set_fused(self.handle, int(mode)))
+
     def arena_views(self):
         """(grads, params): per tensor a view of its region of the symmetric gradient /
         parameter buffer in the tensor's own shape, or None where the shard size is not a

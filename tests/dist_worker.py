@@ -128,8 +128,10 @@ def check_collectives(comm):
 # collectives by NCCL / own kernels with / without multicast / own kernels on gradients and
 # parameters that live inside the symmetric buffer (no pack and unpack copies) - these three on
 # memory from rafb200_symm_alloc - / own kernels with multicast on memory from
-# torch.distributed._symmetric_memory
-MODES = ["nccl", "multimem", "peer", "view", "torch"]
+# torch.distributed._symmetric_memory / LANS with the collectives inside the update kernel:
+# reduce-scatter only, both with multicast, both with peer loads and stores
+MODES = ["nccl", "multimem", "peer", "view", "torch", "fusedrs", "fusedm", "fusedp"]
+FUSED = {"fusedrs": 1, "fusedm": 2, "fusedp": 2}  # LANS with the collectives inside the update kernel
 # ... and each of them again with all steps queued back to back: no host synchronisation and no
 # status read between steps, so the values also cover the ordering ACROSS steps (the fence at the
 # start of a step, barrier epochs, the all-gather of step s overlapping the reduce-scatter of
@@ -146,10 +148,13 @@ def run_zero(comm, out_dir, tag):
         z = ZeroStep(plan, comm, g_dtype, p_dtype, optimizer)
         gviews = pviews = None
         if mode != "nccl":
-            z.attach_symmetric(multicast=(mode != "peer"), allocator="torch" if mode == "torch" else "library")
-            if mode != "peer":
+            z.attach_symmetric(multicast=(mode not in ("peer", "fusedp")),
+                               allocator="torch" if mode == "torch" else "library")
+            if mode not in ("peer", "fusedp"):
                 assert z.multicast, "no multicast address on this box"
-            if mode == "view":
+            if mode in FUSED and optimizer == "lans":
+                z.set_fused(FUSED[mode])
+            if mode == "view" or mode in FUSED:
                 gviews, pviews = z.arena_views()
                 assert any(x is not None for x in gviews) and any(x is None for x in gviews)
         rng = np.random.default_rng(0)
@@ -195,7 +200,7 @@ def run_zero(comm, out_dir, tag):
             saved[f"v_{i}"] = tv[i].cpu().numpy()
             saved[f"param_{i}"] = params[i].float().cpu().numpy()
         kernels, collectives = z.launch_counts()
-        if mode == "view":
+        if mode == "view" or mode in FUSED:
             assert kernels <= 7 * plan.num_buckets
         saved["counts"] = np.array([kernels, collectives, plan.num_buckets])
         np.savez(os.path.join(out_dir, f"case{case}_{tag}_rank{r}.npz"), **saved)
