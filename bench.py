@@ -489,6 +489,9 @@ def main():
                          "pointers) or NCCL; auto = peer at N = 2, multicast from N = 4, NCCL if symmetric "
                          "memory cannot be set up")
     ap.add_argument("--comm-blocks", type=int, default=0, help="thread blocks per collective kernel")
+    ap.add_argument("--fused", type=int, default=-1, choices=[-1, 0, 1, 2],
+                    help="LANS at N > 1: collectives inside the update kernel (1 reduce-scatter, 2 all-gather "
+                         "too, 0 the bucketed pipeline of separate kernels; -1 = the default for N)")
     ap.add_argument("--no-views", action="store_true",
                     help="symmetric modes: keep gradients and parameters in separate tensors "
                          "(pack / unpack copies) instead of inside the symmetric buffer")
@@ -582,11 +585,16 @@ def main():
     # Gradient sets: the step leaves the caller's gradients untouched, so a set can be reused;
     # two sets alternate when ranks exchange data.
     nsets = 1 if world == 1 else 2
+    if args.fused < 0:
+        # LANS: the collectives inside the update kernel (measured 2.12 / 1.69 ms at 2 / 4 GPUs
+        # against 2.25 / 2.17 ms for the bucketed pipeline of separate kernels)
+        args.fused = 2 if (world > 1 and wl["optimizer"] == "lans" and args.stages is False) else 0
     if args.collectives == "auto":
-        # two ranks: plain peer loads / stores beat the switch-side reduction (measured 2.25 ms
-        # against 2.47 ms); from four ranks on the multicast kernels win
-        args.collectives = "peer" if world == 2 else "multimem"
-    if world > 1 and not args.update_blocks and wl["optimizer"] == "lans":
+        # separate kernels on two ranks: plain peer loads / stores beat the switch-side
+        # reduction (2.25 ms against 2.47 ms); inside the update kernel, and from four ranks on,
+        # the multicast forms win
+        args.collectives = "peer" if (world == 2 and args.fused == 0) else "multimem"
+    if world > 1 and not args.update_blocks and wl["optimizer"] == "lans" and args.fused < 2:
         # leave SMs to the collective kernels that run beside the update
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         args.update_blocks = sms - 16
@@ -607,6 +615,8 @@ def main():
                 z.attach_symmetric(comm_blocks=args.comm_blocks, multicast=(args.collectives == "multimem"))
                 if args.collectives == "multimem" and not z.multicast:
                     collectives_used = "peer (no multicast address available)"
+                if args.fused > 0 and wl["optimizer"] == "lans":
+                    z.set_fused(args.fused)
             except Exception as exc:  # symmetric memory is plumbing: without it NCCL still works
                 collectives_used = f"nccl (symmetric memory unavailable: {type(exc).__name__})"
                 args.collectives = "nccl"
@@ -827,6 +837,8 @@ def main():
                        "elements": total, "shard_elements_per_rank": shard_elems,
                        "bucket_elems": wl["bucket_elems"], "buckets": plan.num_buckets if world > 1 else 1,
                        "gradient_sets": nsets, "collectives": collectives_used,
+                       "collectives_inside_update_kernel": (["no", "reduce-scatter", "reduce-scatter and all-gather"][args.fused]
+                                                            if world > 1 and args.collectives != "nccl" and wl["optimizer"] == "lans" else "no"),
                        "tensors_inside_symmetric_buffer": views_used,
                        "l2": (f"inputs larger than L2 ({wl['bytes_per_elem'] * shard_elems >> 20} MiB touched per step per rank)"
                               if wl['bytes_per_elem'] * shard_elems > L2_BYTES else

@@ -579,6 +579,11 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
     rc = rafb200_tensor_list_bind(z->fused_list, fused_g.data(), z->p.data(), z->m.data(),
                                   z->v.empty() ? nullptr : z->v.data(), fused_out.data(), nullptr);
     if (rc != RAFB200_OK) return rc;
+    // what such a step launches: pack / unpack where needed, two barriers, one update, and the
+    // all-gather kernels unless they are inside the update too
+    z->kernels_per_step = 3;
+    for (auto& b : z->buckets)
+      z->kernels_per_step += (b.n_pack_items > 0) + (b.n_unpack_items > 0) + ((z->fused < 2 && b.n_ag_items > 0) ? 1 : 0);
   }
   RAFB200_CUDA(cudaStreamSynchronize(nullptr));  // descriptor tables are in place
   z->bound = true;
@@ -857,14 +862,15 @@ static int step_impl(rafb200_zero_t z, const rafb200_hyper* h, int step, void* c
     }
     return finish();
   }
-  if (z->fused && z->symmetric && z->optimizer == RAFB200_OPT_LANS && h->normalize_grad && z->stage_mask == 31) {
+  // (the host-buffer form keeps the bucketed pipeline: there the copies from and to the host
+  // bound the step, and they overlap with the buckets' kernels)
+  if (z->fused && !host && z->symmetric && z->optimizer == RAFB200_OPT_LANS && h->normalize_grad && z->stage_mask == 31) {
     // The step as one update launch: pack -> every rank's gradients are in place (barrier) ->
     // the LANS kernel, whose gradient-norm items read the sum over ranks through the switch
     // and, with z->fused == 2, whose stage 2 stores the model-dtype copy into every rank's
     // buffer -> (otherwise the all-gather kernels) -> everything has landed (barrier) -> unpack.
     // All on the compute stream; link-bound and memory-bound items interleave inside the kernel.
     for (auto& b : z->buckets) {
-      if (host) RAFB200_CUDA(cudaStreamWaitEvent(cs, b.h2d_done, 0));
       int rc = launch_seg_copy(b.dev_pack, b.dev_pack_items, b.n_pack_items, gs, z->sm_count, cs);
       if (rc != RAFB200_OK) return rc;
     }
@@ -887,7 +893,6 @@ static int step_impl(rafb200_zero_t z, const rafb200_hyper* h, int step, void* c
     for (auto& b : z->buckets) {
       rc = launch_seg_copy(b.dev_unpack, b.dev_unpack_items, b.n_unpack_items, ps, z->sm_count, cs);
       if (rc != RAFB200_OK) return rc;
-      if ((rc = copy_out(b)) != RAFB200_OK) return rc;
     }
     return finish();
   }
