@@ -594,7 +594,7 @@ def main():
         # reduction (2.25 ms against 2.47 ms); inside the update kernel, and from four ranks on,
         # the multicast forms win
         args.collectives = "peer" if (world == 2 and args.fused == 0) else "multimem"
-    if world > 1 and not args.update_blocks and wl["optimizer"] == "lans" and args.fused < 2:
+    if world > 1 and not args.update_blocks and wl["optimizer"] == "lans":
         # leave SMs to the collective kernels that run beside the update
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         args.update_blocks = sms - 16
