@@ -588,7 +588,7 @@ def main():
     if args.fused < 0:
         # LANS: the collectives inside the update kernel (measured 2.12 / 1.69 ms at 2 / 4 GPUs
         # against 2.25 / 2.17 ms for the bucketed pipeline of separate kernels)
-        args.fused = 2 if (world > 1 and wl["optimizer"] == "lans" and args.stages is False) else 0
+        args.fused = 2 if (world > 1 and args.stages is False) else 0
     if args.collectives == "auto":
         # separate kernels on two ranks: plain peer loads / stores beat the switch-side
         # reduction (2.25 ms against 2.47 ms); inside the update kernel, and from four ranks on,
@@ -615,7 +615,7 @@ def main():
                 z.attach_symmetric(comm_blocks=args.comm_blocks, multicast=(args.collectives == "multimem"))
                 if args.collectives == "multimem" and not z.multicast:
                     collectives_used = "peer (no multicast address available)"
-                if args.fused > 0 and wl["optimizer"] == "lans":
+                if args.fused > 0:
                     z.set_fused(args.fused)
             except Exception as exc:  # symmetric memory is plumbing: without it NCCL still works
                 collectives_used = f"nccl (symmetric memory unavailable: {type(exc).__name__})"
@@ -838,7 +838,7 @@ def main():
                        "bucket_elems": wl["bucket_elems"], "buckets": plan.num_buckets if world > 1 else 1,
                        "gradient_sets": nsets, "collectives": collectives_used,
                        "collectives_inside_update_kernel": (["no", "reduce-scatter", "reduce-scatter and all-gather"][args.fused]
-                                                            if world > 1 and args.collectives != "nccl" and wl["optimizer"] == "lans" else "no"),
+                                                            if world > 1 and args.collectives != "nccl" else "no"),
                        "tensors_inside_symmetric_buffer": views_used,
                        "l2": (f"inputs larger than L2 ({wl['bytes_per_elem'] * shard_elems >> 20} MiB touched per step per rank)"
                               if wl['bytes_per_elem'] * shard_elems > L2_BYTES else

@@ -1,8 +1,10 @@
 // SGD-momentum and Adam update kernels (single pass, HBM-bound: every byte is
 // touched once), raf.op.cast / group_cast and fuse_tensor / defuse_tensor.
 #include <cmath>
+#include <type_traits>
 
 #include "common.h"
+#include "symm_dev.cuh"
 #include "update_core.cuh"
 
 namespace rafb200 {
@@ -20,6 +22,83 @@ __global__ void __launch_bounds__(kBlockThreads)
     const TensorDesc d = descs[item.tensor_phase & kTensorMask];
     ChunkView c = chunk_view(d, item.chunk, sizeof(GT), sizeof(OT));
     update_chunk<NSTATE, GT, OT>(c, op, pol);
+  }
+}
+
+// The same update with the collectives inside (n > 1, symmetric memory; no counterpart in the
+// reference): the gradient is the sum over ranks of the chunk, read through the multicast
+// address or peer by peer at TensorDesc's symmetric offset (kept in first_chunk / nchunks) and
+// also written to the rank's local gradient block; the model-dtype copy goes into every rank's
+// parameter buffer.  The symmetric layout is 16-byte aligned and zero-padded per row block.
+template <int NSTATE, typename GT, typename OT, typename Op>
+__global__ void __launch_bounds__(kBlockThreads)
+    update_list_fused_kernel(const TensorDesc* __restrict__ descs, const Item* __restrict__ items,
+                             uint32_t nitems, Op op, LansFuse fu) {
+  constexpr int kDT = sizeof(GT) == 4 ? RAFB200_F32 : (std::is_same<GT, __half>::value ? RAFB200_F16 : RAFB200_BF16);
+  Policies pol;
+  pol.init();
+  const int tid = threadIdx.x;
+  for (uint32_t it = blockIdx.x; it < nitems; it += gridDim.x) {
+    const Item item = items[it];
+    const TensorDesc d = descs[item.tensor_phase & kTensorMask];
+    const ChunkView c = chunk_view(d, item.chunk, sizeof(GT), sizeof(OT));
+    const size_t sym = ((((size_t)d.nchunks) << 32) | d.first_chunk) + (size_t)item.chunk * kChunkElems * sizeof(GT);
+    GT* gred = const_cast<GT*>(static_cast<const GT*>(c.g));
+    OT* out = static_cast<OT*>(c.out);
+    const int len4 = c.len & ~(kVec - 1);
+    for (int base = 0; base < len4; base += kUnroll * kPassElems) {
+      F4 rg[kUnroll], rp[kUnroll], rm[kUnroll], rv[kUnroll];
+      uint32_t bits[kUnroll][4];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int e = base + u * kPassElems + tid * kVec;
+        if (e < len4) {
+          reduced4<kDT>(fu.g_mc, fu.g_peer, fu.world, sym + (size_t)e * sizeof(GT), rg[u].x, bits[u]);
+          rp[u] = Elem<float>::template load4<kStream>(c.p + e, pol);
+          rm[u] = Elem<float>::template load4<kStream>(c.m + e, pol);
+          if (NSTATE == 2) rv[u] = Elem<float>::template load4<kStream>(c.v + e, pol);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int e = base + u * kPassElems + tid * kVec;
+        if (e < len4) {
+          if (sizeof(GT) == 4) *reinterpret_cast<uint4*>(gred + e) = make_uint4(bits[u][0], bits[u][1], bits[u][2], bits[u][3]);
+          else *reinterpret_cast<uint2*>(gred + e) = make_uint2(bits[u][0], bits[u][1]);
+#pragma unroll
+          for (int j = 0; j < kVec; ++j) {
+            float vv = NSTATE == 2 ? rv[u].x[j] : 0.f;
+            op(rg[u].x[j], rp[u].x[j], rm[u].x[j], vv);
+            if (NSTATE == 2) rv[u].x[j] = vv;
+          }
+          Elem<float>::template store4<kDefault>(c.p + e, rp[u], pol);
+          Elem<float>::template store4<kDefault>(c.m + e, rm[u], pol);
+          if (NSTATE == 2) Elem<float>::template store4<kDefault>(c.v + e, rv[u], pol);
+          if (out) {
+            if (fu.fuse_ag) store4_everywhere<OT>(fu.p_mc, fu.p_peer, fu.world, fu.rank, out + e, rp[u]);
+            else Elem<OT>::template store4<kDefault>(out + e, rp[u], pol);
+          }
+        }
+      }
+    }
+    // the last one to three elements of a tensor: element by element, peer by peer
+    for (int e = len4 + tid; e < c.len; e += kBlockThreads) {
+      float acc = 0.f;
+      for (int q = 0; q < fu.world; ++q)
+        acc += Elem<GT>::to_f32(*reinterpret_cast<const volatile GT*>(fu.g_peer[q] + sym + (size_t)e * sizeof(GT)));
+      const GT rounded = Elem<GT>::from_f32(acc);
+      gred[e] = rounded;
+      float gg = Elem<GT>::to_f32(rounded);
+      float pp = c.p[e], mm = c.m[e], vv = NSTATE == 2 ? c.v[e] : 0.f;
+      op(gg, pp, mm, vv);
+      c.p[e] = pp;
+      c.m[e] = mm;
+      if (NSTATE == 2) c.v[e] = vv;
+      if (out) {
+        if (fu.fuse_ag) store1_everywhere<OT>(fu.p_peer, fu.world, fu.rank, out + e, pp);
+        else out[e] = Elem<OT>::from_f32(pp);
+      }
+    }
   }
 }
 
@@ -52,6 +131,21 @@ static int grid_for(uint32_t nitems, int device) {
 template <int NSTATE, typename Op, typename GT>
 static int launch_list_out(const rafb200_tensor_list_s* l, const Op& op, cudaStream_t s) {
   const int grid = grid_for(l->n_items, l->device);
+  if (l->fuse.fuse_rs) {
+    switch (l->out_dtype) {
+      case RAFB200_F32:
+        update_list_fused_kernel<NSTATE, GT, float><<<grid, kBlockThreads, 0, s>>>(l->dev_desc, l->dev_items, l->n_items, op, l->fuse);
+        break;
+      case RAFB200_F16:
+        update_list_fused_kernel<NSTATE, GT, __half><<<grid, kBlockThreads, 0, s>>>(l->dev_desc, l->dev_items, l->n_items, op, l->fuse);
+        break;
+      default:
+        update_list_fused_kernel<NSTATE, GT, __nv_bfloat16><<<grid, kBlockThreads, 0, s>>>(l->dev_desc, l->dev_items, l->n_items, op, l->fuse);
+        break;
+    }
+    RAFB200_CUDA(cudaGetLastError());
+    return RAFB200_OK;
+  }
   switch (l->out_dtype) {
     case RAFB200_F32:
       update_list_kernel<NSTATE, GT, float><<<grid, kBlockThreads, 0, s>>>(l->dev_desc, l->dev_items, l->n_items, op);

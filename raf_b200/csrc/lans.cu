@@ -88,38 +88,14 @@ struct LansParams {
   char* p_peer[kSymmMaxWorld];
 };
 
-// The model-dtype copy of four elements, into every rank's parameter buffer.
+// The model-dtype copy of four elements (or one), into every rank's parameter buffer.
 template <typename OT>
 __device__ __forceinline__ void store_out_everywhere(const LansParams& P, OT* local, const F4& v) {
-  uint32_t w[4];
-  if (sizeof(OT) == 4) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) w[j] = __float_as_uint(v.x[j]);
-  } else {
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const OT lo = Elem<OT>::from_f32(v.x[2 * j]), hi = Elem<OT>::from_f32(v.x[2 * j + 1]);
-      w[j] = (uint32_t)(*reinterpret_cast<const unsigned short*>(&lo)) |
-             ((uint32_t)(*reinterpret_cast<const unsigned short*>(&hi)) << 16);
-    }
-  }
-  const size_t delta = (size_t)(reinterpret_cast<char*>(local) - P.p_peer[P.rank]);
-  if (P.p_mc) {
-    if (sizeof(OT) == 4) mc_st(P.p_mc + delta, make_uint4(w[0], w[1], w[2], w[3]));
-    else mc_st8(P.p_mc + delta, make_uint2(w[0], w[1]));
-  } else {
-    for (int q = 0; q < P.world; ++q) {
-      char* dst = P.p_peer[q] + delta;
-      if (sizeof(OT) == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-      else *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
-    }
-  }
+  store4_everywhere<OT>(P.p_mc, P.p_peer, P.world, P.rank, local, v);
 }
 template <typename OT>
 __device__ __forceinline__ void store_out_everywhere1(const LansParams& P, OT* local, float x) {
-  const size_t delta = (size_t)(reinterpret_cast<char*>(local) - P.p_peer[P.rank]);
-  const OT val = Elem<OT>::from_f32(x);
-  for (int q = 0; q < P.world; ++q) *reinterpret_cast<OT*>(P.p_peer[q] + delta) = val;
+  store1_everywhere<OT>(P.p_peer, P.world, P.rank, local, x);
 }
 
 __device__ __forceinline__ uint64_t global_ns() {

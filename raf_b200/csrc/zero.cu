@@ -183,7 +183,7 @@ struct rafb200_zero_s {
   cudaEvent_t ev_gather = nullptr;
   int comm_blocks = 128;
   int kernels_per_step = 0, collectives_per_step = 0;
-  // LANS with the collectives inside the update kernel (rafb200_zero_set_fused): one list over
+  // The collectives inside the update kernel (rafb200_zero_set_fused): one list over
   // all tensors, one launch per step, two cross-GPU barriers per step instead of two per bucket
   int fused = 0;  // 0 off, 1 reduce-scatter inside the kernel, 2 all-gather too
   rafb200_tensor_list_t fused_list = nullptr;
@@ -560,8 +560,10 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
     if (!z->fused_list) {
       int rc = rafb200_tensor_list_create(k, z->plan.shard_elems.data(), z->g_dtype, z->param_dtype, &z->fused_list);
       if (rc != RAFB200_OK) return rc;
-      z->fused_ws_bytes = rafb200_lans_workspace_bytes(z->fused_list);
-      RAFB200_CUDA(cudaMalloc(&z->fused_ws, z->fused_ws_bytes));
+      if (z->optimizer == RAFB200_OPT_LANS) {
+        z->fused_ws_bytes = rafb200_lans_workspace_bytes(z->fused_list);
+        RAFB200_CUDA(cudaMalloc(&z->fused_ws, z->fused_ws_bytes));
+      }
     }
     LansFuse f;
     f.world = z->n;
@@ -592,8 +594,7 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
 
 int rafb200_zero_set_fused(rafb200_zero_t z, int mode) {
   RAFB200_REQUIRE(z && mode >= 0 && mode <= 2, "rafb200_zero_set_fused: mode must be 0, 1 or 2");
-  RAFB200_REQUIRE(mode == 0 || (z->symmetric && z->optimizer == RAFB200_OPT_LANS),
-                  "rafb200_zero_set_fused: needs LANS and attached symmetric memory");
+  RAFB200_REQUIRE(mode == 0 || z->symmetric, "rafb200_zero_set_fused: attach symmetric memory first");
   RAFB200_REQUIRE(!z->bound, "rafb200_zero_set_fused: call before rafb200_zero_bind");
   z->fused = mode;
   return RAFB200_OK;
@@ -864,7 +865,7 @@ static int step_impl(rafb200_zero_t z, const rafb200_hyper* h, int step, void* c
   }
   // (the host-buffer form keeps the bucketed pipeline: there the copies from and to the host
   // bound the step, and they overlap with the buckets' kernels)
-  if (z->fused && !host && z->symmetric && z->optimizer == RAFB200_OPT_LANS && h->normalize_grad && z->stage_mask == 31) {
+  if (z->fused && !host && z->symmetric && (z->optimizer != RAFB200_OPT_LANS || h->normalize_grad) && z->stage_mask == 31) {
     // The step as one update launch: pack -> every rank's gradients are in place (barrier) ->
     // the LANS kernel, whose gradient-norm items read the sum over ranks through the switch
     // and, with z->fused == 2, whose stage 2 stores the model-dtype copy into every rank's
@@ -877,9 +878,15 @@ static int step_impl(rafb200_zero_t z, const rafb200_hyper* h, int step, void* c
     int rc = symm_barrier(z->sig_peers, z->n, z->rank, 0, ++z->epoch[0], z->wait_limit_ns, z->dev_err,
                           z->host_err_dev, cs);
     if (rc != RAFB200_OK) return rc;
-    rc = rafb200_lans(z->fused_list, step, nullptr, h->learning_rate, h->beta1, h->beta2, h->eps,
-                      h->bias_correction, h->weight_decay, h->grad_averaging, h->mode, h->normalize_grad,
-                      gscale, z->fused_ws, z->fused_ws_bytes, cs);
+    if (z->optimizer == RAFB200_OPT_SGD)
+      rc = rafb200_sgd_list(z->fused_list, h->learning_rate, h->mu, h->weight_decay, gscale, cs);
+    else if (z->optimizer == RAFB200_OPT_ADAM)
+      rc = rafb200_adam(z->fused_list, step, nullptr, h->learning_rate, h->beta1, h->beta2, h->eps,
+                        h->bias_correction, h->weight_decay, h->mode, gscale, cs);
+    else
+      rc = rafb200_lans(z->fused_list, step, nullptr, h->learning_rate, h->beta1, h->beta2, h->eps,
+                        h->bias_correction, h->weight_decay, h->grad_averaging, h->mode, h->normalize_grad,
+                        gscale, z->fused_ws, z->fused_ws_bytes, cs);
     if (rc != RAFB200_OK) return rc;
     if (z->fused < 2)
       for (auto& b : z->buckets) {

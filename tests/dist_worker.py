@@ -131,7 +131,7 @@ def check_collectives(comm):
 # torch.distributed._symmetric_memory / LANS with the collectives inside the update kernel:
 # reduce-scatter only, both with multicast, both with peer loads and stores
 MODES = ["nccl", "multimem", "peer", "view", "torch", "fusedrs", "fusedm", "fusedp"]
-FUSED = {"fusedrs": 1, "fusedm": 2, "fusedp": 2}  # LANS with the collectives inside the update kernel
+FUSED = {"fusedrs": 1, "fusedm": 2, "fusedp": 2}  # the collectives inside the update kernel
 # ... and each of them again with all steps queued back to back: no host synchronisation and no
 # status read between steps, so the values also cover the ordering ACROSS steps (the fence at the
 # start of a step, barrier epochs, the all-gather of step s overlapping the reduce-scatter of
@@ -152,7 +152,7 @@ def run_zero(comm, out_dir, tag):
                                allocator="torch" if mode == "torch" else "library")
             if mode not in ("peer", "fusedp"):
                 assert z.multicast, "no multicast address on this box"
-            if mode in FUSED and optimizer == "lans":
+            if mode in FUSED:
                 z.set_fused(FUSED[mode])
             if mode == "view" or mode in FUSED:
                 gviews, pviews = z.arena_views()
