@@ -593,7 +593,9 @@ def main():
         # separate kernels on two ranks: plain peer loads / stores beat the switch-side
         # reduction (2.25 ms against 2.47 ms); inside the update kernel, and from four ranks on,
         # the multicast forms win
-        args.collectives = "peer" if (world == 2 and args.fused == 0) else "multimem"
+        # (two ranks, SGD / Adam inside the kernel: peer accesses again, 0.20 / 1.82 ms against
+        # 0.31 / 1.99 ms through the switch, which at two ranks also carries the rank's own half)
+        args.collectives = "peer" if (world == 2 and (args.fused == 0 or wl["optimizer"] != "lans")) else "multimem"
     if world > 1 and not args.update_blocks and wl["optimizer"] == "lans":
         # leave SMs to the collective kernels that run beside the update
         sms = torch.cuda.get_device_properties(dev).multi_processor_count

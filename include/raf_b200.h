@@ -549,7 +549,7 @@ RAFB200_API int rafb200_zero_step(rafb200_zero_t zero, const rafb200_hyper* hype
  * rafb200_zero_bind, on every rank or on none.
  */
 /*
- * LANS with the collectives INSIDE the update kernel (symmetric mode only; no counterpart
+ * The collectives INSIDE the update kernel (symmetric mode only; no counterpart
  * in the reference, whose collectives are separate NCCL launches, nccl.cc:189-190,308,387).
  * mode 1: the kernel's gradient-norm items read the sum over ranks of their chunk through
  * the switch (multimem.ld_reduce, or the peers one by one without a multicast address), write

@@ -30,6 +30,8 @@ __global__ void __launch_bounds__(kBlockThreads)
 // address or peer by peer at TensorDesc's symmetric offset (kept in first_chunk / nchunks) and
 // also written to the rank's local gradient block; the model-dtype copy goes into every rank's
 // parameter buffer.  The symmetric layout is 16-byte aligned and zero-padded per row block.
+// passes in flight per thread (four were measured slower: 128 registers, half the resident blocks)
+constexpr int kFusedUnroll = 2;
 template <int NSTATE, typename GT, typename OT, typename Op>
 __global__ void __launch_bounds__(kBlockThreads)
     update_list_fused_kernel(const TensorDesc* __restrict__ descs, const Item* __restrict__ items,
@@ -46,21 +48,47 @@ __global__ void __launch_bounds__(kBlockThreads)
     GT* gred = const_cast<GT*>(static_cast<const GT*>(c.g));
     OT* out = static_cast<OT*>(c.out);
     const int len4 = c.len & ~(kVec - 1);
-    for (int base = 0; base < len4; base += kUnroll * kPassElems) {
-      F4 rg[kUnroll], rp[kUnroll], rm[kUnroll], rv[kUnroll];
-      uint32_t bits[kUnroll][4];
+    for (int base = 0; base < len4; base += kFusedUnroll * kPassElems) {
+      F4 rg[kFusedUnroll], rp[kFusedUnroll], rm[kFusedUnroll], rv[kFusedUnroll];
+      uint32_t bits[kFusedUnroll][4];
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
+      for (int u = 0; u < kFusedUnroll; ++u) {
         const int e = base + u * kPassElems + tid * kVec;
+        if (sizeof(GT) == 2) {
+          // 16-bit gradients: a pair of lanes shares one 16-byte access (eight elements); the even
+          // lane makes it - the row block's zero padding covers a missing partner - and hands the
+          // upper half over.  Every lane of the warp takes part in the exchange.
+          uint4 raw = make_uint4(0, 0, 0, 0);
+          if ((tid & 1) == 0 && e < len4) {
+            const size_t off = sym + (size_t)e * sizeof(GT);
+            if (fu.g_mc) {
+              raw = mc_ld_reduce<kDT>(fu.g_mc + off);
+            } else {
+              float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+              for (int q = 0; q < fu.world; ++q) accumulate<kDT>(acc, peer_ld(fu.g_peer[q] + off));
+              raw = round_once<kDT>(acc);
+            }
+          }
+          const uint32_t hi0 = __shfl_sync(0xffffffffu, raw.z, (tid & 31) & ~1);
+          const uint32_t hi1 = __shfl_sync(0xffffffffu, raw.w, (tid & 31) & ~1);
+          bits[u][0] = (tid & 1) ? hi0 : raw.x;
+          bits[u][1] = (tid & 1) ? hi1 : raw.y;
+          bits[u][2] = bits[u][3] = 0;
+          float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          accumulate<kDT>(f, make_uint4(bits[u][0], bits[u][1], 0u, 0u));
+#pragma unroll
+          for (int j = 0; j < 4; ++j) rg[u].x[j] = f[j];
+        }
         if (e < len4) {
-          reduced4<kDT>(fu.g_mc, fu.g_peer, fu.world, sym + (size_t)e * sizeof(GT), rg[u].x, bits[u]);
+          if (sizeof(GT) == 4)
+            reduced4<kDT>(fu.g_mc, fu.g_peer, fu.world, sym + (size_t)e * sizeof(GT), rg[u].x, bits[u]);
           rp[u] = Elem<float>::template load4<kStream>(c.p + e, pol);
           rm[u] = Elem<float>::template load4<kStream>(c.m + e, pol);
           if (NSTATE == 2) rv[u] = Elem<float>::template load4<kStream>(c.v + e, pol);
         }
       }
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
+      for (int u = 0; u < kFusedUnroll; ++u) {
         const int e = base + u * kPassElems + tid * kVec;
         if (e < len4) {
           if (sizeof(GT) == 4) *reinterpret_cast<uint4*>(gred + e) = make_uint4(bits[u][0], bits[u][1], bits[u][2], bits[u][3]);
