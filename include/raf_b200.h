@@ -551,7 +551,7 @@ RAFB200_API int rafb200_zero_step(rafb200_zero_t zero, const rafb200_hyper* hype
 /*
  * The collectives INSIDE the update kernel (symmetric mode only; no counterpart
  * in the reference, whose collectives are separate NCCL launches, nccl.cc:189-190,308,387).
- * mode 1: the kernel's gradient-norm items read the sum over ranks of their chunk through
+ * LANS, mode 1: the kernel's gradient-norm items read the sum over ranks of their chunk through
  * the switch (multimem.ld_reduce, or the peers one by one without a multicast address), write
  * it to the local gradient block for the later stages and square what they wrote; the
  * reduce-scatter kernels disappear.  mode 2: in addition stage 2 stores the model-dtype copy
@@ -559,8 +559,10 @@ RAFB200_API int rafb200_zero_step(rafb200_zero_t zero, const rafb200_hyper* hype
  * disappear too.  A step is then: pack (tensors bound outside the buffer) -> one barrier ->
  * ONE update launch over all tensors -> one barrier -> unpack, on the compute stream; link
  * traffic and memory traffic interleave inside the kernel instead of running as separate
- * kernels.  Needs normalize_grad (the gradient-norm pass is what reads the gradients); a step
- * without it takes the bucketed pipeline.  Call after rafb200_zero_attach_symmetric and
+ * kernels.  SGD and Adam do the same in their single pass (mode 1: the gradient is read as
+ * the sum over ranks; mode 2: the copy is stored everywhere too).  LANS needs normalize_grad
+ * (the gradient-norm pass is what reads the gradients); a LANS step without it, and every step
+ * of the host-buffer form, takes the bucketed pipeline.  Call after rafb200_zero_attach_symmetric and
  * before rafb200_zero_bind, with the same mode on every rank.
  */
 RAFB200_API int rafb200_zero_set_fused(rafb200_zero_t zero, int mode);
