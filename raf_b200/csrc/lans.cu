@@ -399,7 +399,9 @@ __device__ __forceinline__ uint32_t ld_shared_volatile(const uint32_t* p) {
   return *reinterpret_cast<const volatile uint32_t*>(p);
 }
 
-template <typename GT, typename OT>
+// FUSED: the instantiation with the collectives inside (LansParams::fuse_rs / fuse_ag); the
+// plain one carries none of that code.
+template <typename GT, typename OT, bool FUSED>
 __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams P) {
   extern __shared__ __align__(128) unsigned char smem[];
   using L = LansGeo<GT>;
@@ -676,7 +678,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
           const int64_t left = numel - start;
           const int n = left < per ? (int)left : per;
           constexpr int gran = 16 / (int)sizeof(GT);  // elements per 16 bytes of gradient
-          const bool through_switch = kind == kKindA && P.fuse_rs != 0;
+          const bool through_switch = FUSED && kind == kKindA && P.fuse_rs != 0;
           const int nbulk = ((flags & kFlagBulk) && !through_switch) ? (n / gran) * gran : 0;
           const uint32_t op = kind == kKindA ? kOpA : kind == kKindBs ? kOpB : kind == kKindCs ? kOpC : kOpBP;
           SlotMeta& mt = s_ring[mb];
@@ -878,11 +880,11 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
   // the model-dtype copy: a local store, or - with the all-gather inside the kernel - a store
   // into every rank's parameter buffer
   auto put_out4 = [&](OT* dst, const F4& v) {
-    if (P.fuse_ag) store_out_everywhere<OT>(P, dst, v);
+    if (FUSED && P.fuse_ag) store_out_everywhere<OT>(P, dst, v);
     else Elem<OT>::template store4<kStream>(dst, v, pol);
   };
   auto put_out1 = [&](OT* dst, float x) {
-    if (P.fuse_ag) store_out_everywhere1<OT>(P, dst, x);
+    if (FUSED && P.fuse_ag) store_out_everywhere1<OT>(P, dst, x);
     else *dst = Elem<OT>::from_f32(x);
   };
   for (uint32_t i = 0;; ++i) {
@@ -929,7 +931,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
     // code without per-vector tests; ragged or unaligned items take the general code below.
     // Both add an element's square into the same accumulator in the same order.
     const bool whole = nbulk == ((op == kOpA) ? L::kAElems : kLansElems);
-    if (op == kOpA && P.fuse_rs) {
+    if (FUSED && op == kOpA && P.fuse_rs) {
       // Reduce-scatter inside the kernel: the chunk's sum over ranks, 16 bytes per access, in
       // fp32 with one rounding - written to the local gradient block for the later stages and
       // squared as written.  The symmetric layout pads every row block to 16 bytes with zeros,
@@ -987,7 +989,148 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
       }
       __threadfence();  // the block of another SM that waits for ||g|| reads these stores next
       publishes = true;
-    } else if (whole && op == kOpA) {
+    } else if (__builtin_expect(!whole, 0)) {
+      // ragged or unaligned items: kept out of the way of the straight-line code below
+      if (op == kOpA) {
+        constexpr int kPasses = L::kAElems / (kGroupThreads * kVec);
+#pragma unroll 2
+        for (int q = 0; q < kPasses; ++q) {
+          const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+          F4 r;
+          if (e < nbulk) {
+            r = Elem<GT>::smem4(sbase + e * sizeof(GT));
+          } else {
+#pragma unroll
+            for (int j = 0; j < kVec; ++j) r.x[j] = (e + j < n) ? Elem<GT>::to_f32(gg[e + j]) : 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < kVec; ++j) {
+            const float x = r.x[j] * s1.gscale;
+            acc0 = fmaf(x, x, acc0);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(my_done);
+        publishes = true;
+      } else if (op == kOpCP) {
+        // stage 2 from the parked chunk: p, update_m, update_g are in tensor memory
+        F4 rp[kBVecs], um[kBVecs], ug[kBVecs];
+        park_load(in_tmem, taddr, scell, gtid, rp, um, ug);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(my_done);
+#pragma unroll
+        for (int q = 0; q < kBVecs; ++q) {
+          const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+#pragma unroll
+          for (int j = 0; j < kVec; ++j)
+            rp[q].x[j] = fmaf(ratio_g, ug[q].x[j], fmaf(ratio_m, um[q].x[j], rp[q].x[j]));
+          if (e < nbulk) {
+            Elem<float>::template store4<kStream>(gp + e, rp[q], pol);
+            if (gout) put_out4(gout + e, rp[q]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kVec; ++j)
+              if (e + j < n) {
+                gp[e + j] = rp[q].x[j];
+                if (gout) put_out1(gout + e + j, rp[q].x[j]);
+              }
+          }
+        }
+      } else {
+        // ---- B (sums only), BP (sums, store m and v, park p / update_m / update_g), C ----
+        F4 rg[kBVecs], rp[kBVecs], rm[kBVecs], rv[kBVecs];
+#pragma unroll
+        for (int q = 0; q < kBVecs; ++q) {
+          const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+          if (e < nbulk) {
+            rg[q] = Elem<GT>::smem4(sbase + e * sizeof(GT));
+            rp[q] = Elem<float>::smem4(sbase + L::kGBytes + e * 4);
+            rm[q] = Elem<float>::smem4(sbase + L::kGBytes + L::kFBytes + e * 4);
+            rv[q] = Elem<float>::smem4(sbase + L::kGBytes + 2 * L::kFBytes + e * 4);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kVec; ++j) {
+              const bool in = e + j < n;
+              rg[q].x[j] = in ? Elem<GT>::to_f32(gg[e + j]) : 0.f;
+              rp[q].x[j] = in ? gp[e + j] : 0.f;
+              rm[q].x[j] = in ? gm[e + j] : 0.f;
+              rv[q].x[j] = in ? gv[e + j] : 0.f;
+            }
+          }
+        }
+        __syncwarp();  // values are in registers: the slot can be refilled
+        if (lane == 0) mbar_arrive(my_done);
+        // stage 1 of the thread's eight elements, `mode` resolved once
+        F4 ua[kBVecs], ub[kBVecs];
+        auto stage1 = [&](auto mode_tag) {
+          constexpr int kMode = decltype(mode_tag)::value;
+#pragma unroll
+          for (int q = 0; q < kBVecs; ++q)
+#pragma unroll
+            for (int j = 0; j < kVec; ++j)
+              s1.template apply<kMode>(rg[q].x[j], rp[q].x[j], rm[q].x[j], rv[q].x[j], cs, ua[q].x[j], ub[q].x[j]);
+        };
+        if (s1.mode == 0) stage1(std::integral_constant<int, 0>{});
+        else stage1(std::integral_constant<int, 1>{});
+        if (op == kOpC) {
+#pragma unroll
+          for (int q = 0; q < kBVecs; ++q) {
+            const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+            // p - ratio_m*update_m - ratio_g*update_g  (:385; the ratios carry the minus sign)
+#pragma unroll
+            for (int j = 0; j < kVec; ++j)
+              rp[q].x[j] = fmaf(ratio_g, ub[q].x[j], fmaf(ratio_m, ua[q].x[j], rp[q].x[j]));
+            if (e < nbulk) {  // aligned: 16-byte stores
+              Elem<float>::template store4<kStream>(gp + e, rp[q], pol);
+              Elem<float>::template store4<kStream>(gm + e, rm[q], pol);
+              Elem<float>::template store4<kStream>(gv + e, rv[q], pol);
+              if (gout) put_out4(gout + e, rp[q]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < kVec; ++j)
+                if (e + j < n) {
+                  gp[e + j] = rp[q].x[j];
+                  gm[e + j] = rm[q].x[j];
+                  gv[e + j] = rv[q].x[j];
+                  if (gout) put_out1(gout + e + j, rp[q].x[j]);
+                }
+            }
+          }
+        } else {
+          publishes = true;
+#pragma unroll
+          for (int q = 0; q < kBVecs; ++q) {
+            const int e = q * (kGroupThreads * kVec) + gtid * kVec;
+#pragma unroll
+            for (int j = 0; j < kVec; ++j) {
+              acc0 = fmaf(rp[q].x[j], rp[q].x[j], acc0);
+              acc1 = fmaf(ua[q].x[j], ua[q].x[j], acc1);
+              acc2 = fmaf(ub[q].x[j], ub[q].x[j], acc2);
+            }
+            if (op == kOpBP) {  // m and v are final
+              if (e < nbulk) {
+                Elem<float>::template store4<kStream>(gm + e, rm[q], pol);
+                Elem<float>::template store4<kStream>(gv + e, rv[q], pol);
+              } else {
+#pragma unroll
+                for (int j = 0; j < kVec; ++j)
+                  if (e + j < n) {
+                    gm[e + j] = rm[q].x[j];
+                    gv[e + j] = rv[q].x[j];
+                  }
+              }
+            }
+          }
+          if (op == kOpBP) {
+            // p, update_m and update_g wait in tensor memory for the norms
+            park_store(in_tmem, taddr, scell, gtid, rp, ua, ub);
+            if (in_tmem) tmem_wait_st();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_cell + 8 * cell);
+          }
+        }
+          }
+    } else if (op == kOpA) {
       constexpr int kPasses = L::kAElems / (kGroupThreads * kVec);
       constexpr int kBatch = kPasses % 7 == 0 ? 7 : 8;  // vectors in flight per thread
       static_assert(kPasses % kBatch == 0, "an A item is whole batches of passes");
@@ -1007,7 +1150,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
       __syncwarp();
       if (lane == 0) mbar_arrive(my_done);
       publishes = true;
-    } else if (whole && op == kOpCP) {
+    } else if (op == kOpCP) {
       F4 rp[kBVecs], um[kBVecs], ug[kBVecs];
       park_load(in_tmem, taddr, scell, gtid, rp, um, ug);
       __syncwarp();
@@ -1025,7 +1168,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
         for (int q = 0; q < kBVecs; ++q)
           put_out4(gout + q * (kGroupThreads * kVec) + gtid * kVec, rp[q]);
       }
-    } else if (whole) {
+    } else {
       F4 rg[kBVecs], rp[kBVecs], rm[kBVecs], rv[kBVecs], ua[kBVecs], ub[kBVecs];
 #pragma unroll
       for (int q = 0; q < kBVecs; ++q) {
@@ -1085,144 +1228,6 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
           if (in_tmem) tmem_wait_st();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_cell + 8 * cell);  // this warp's part is parked
-        }
-      }
-    } else if (op == kOpA) {
-      constexpr int kPasses = L::kAElems / (kGroupThreads * kVec);
-#pragma unroll 2
-      for (int q = 0; q < kPasses; ++q) {
-        const int e = q * (kGroupThreads * kVec) + gtid * kVec;
-        F4 r;
-        if (e < nbulk) {
-          r = Elem<GT>::smem4(sbase + e * sizeof(GT));
-        } else {
-#pragma unroll
-          for (int j = 0; j < kVec; ++j) r.x[j] = (e + j < n) ? Elem<GT>::to_f32(gg[e + j]) : 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < kVec; ++j) {
-          const float x = r.x[j] * s1.gscale;
-          acc0 = fmaf(x, x, acc0);
-        }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(my_done);
-      publishes = true;
-    } else if (op == kOpCP) {
-      // stage 2 from the parked chunk: p, update_m, update_g are in tensor memory
-      F4 rp[kBVecs], um[kBVecs], ug[kBVecs];
-      park_load(in_tmem, taddr, scell, gtid, rp, um, ug);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(my_done);
-#pragma unroll
-      for (int q = 0; q < kBVecs; ++q) {
-        const int e = q * (kGroupThreads * kVec) + gtid * kVec;
-#pragma unroll
-        for (int j = 0; j < kVec; ++j)
-          rp[q].x[j] = fmaf(ratio_g, ug[q].x[j], fmaf(ratio_m, um[q].x[j], rp[q].x[j]));
-        if (e < nbulk) {
-          Elem<float>::template store4<kStream>(gp + e, rp[q], pol);
-          if (gout) put_out4(gout + e, rp[q]);
-        } else {
-#pragma unroll
-          for (int j = 0; j < kVec; ++j)
-            if (e + j < n) {
-              gp[e + j] = rp[q].x[j];
-              if (gout) put_out1(gout + e + j, rp[q].x[j]);
-            }
-        }
-      }
-    } else {
-      // ---- B (sums only), BP (sums, store m and v, park p / update_m / update_g), C ----
-      F4 rg[kBVecs], rp[kBVecs], rm[kBVecs], rv[kBVecs];
-#pragma unroll
-      for (int q = 0; q < kBVecs; ++q) {
-        const int e = q * (kGroupThreads * kVec) + gtid * kVec;
-        if (e < nbulk) {
-          rg[q] = Elem<GT>::smem4(sbase + e * sizeof(GT));
-          rp[q] = Elem<float>::smem4(sbase + L::kGBytes + e * 4);
-          rm[q] = Elem<float>::smem4(sbase + L::kGBytes + L::kFBytes + e * 4);
-          rv[q] = Elem<float>::smem4(sbase + L::kGBytes + 2 * L::kFBytes + e * 4);
-        } else {
-#pragma unroll
-          for (int j = 0; j < kVec; ++j) {
-            const bool in = e + j < n;
-            rg[q].x[j] = in ? Elem<GT>::to_f32(gg[e + j]) : 0.f;
-            rp[q].x[j] = in ? gp[e + j] : 0.f;
-            rm[q].x[j] = in ? gm[e + j] : 0.f;
-            rv[q].x[j] = in ? gv[e + j] : 0.f;
-          }
-        }
-      }
-      __syncwarp();  // values are in registers: the slot can be refilled
-      if (lane == 0) mbar_arrive(my_done);
-      // stage 1 of the thread's eight elements, `mode` resolved once
-      F4 ua[kBVecs], ub[kBVecs];
-      auto stage1 = [&](auto mode_tag) {
-        constexpr int kMode = decltype(mode_tag)::value;
-#pragma unroll
-        for (int q = 0; q < kBVecs; ++q)
-#pragma unroll
-          for (int j = 0; j < kVec; ++j)
-            s1.template apply<kMode>(rg[q].x[j], rp[q].x[j], rm[q].x[j], rv[q].x[j], cs, ua[q].x[j], ub[q].x[j]);
-      };
-      if (s1.mode == 0) stage1(std::integral_constant<int, 0>{});
-      else stage1(std::integral_constant<int, 1>{});
-      if (op == kOpC) {
-#pragma unroll
-        for (int q = 0; q < kBVecs; ++q) {
-          const int e = q * (kGroupThreads * kVec) + gtid * kVec;
-          // p - ratio_m*update_m - ratio_g*update_g  (:385; the ratios carry the minus sign)
-#pragma unroll
-          for (int j = 0; j < kVec; ++j)
-            rp[q].x[j] = fmaf(ratio_g, ub[q].x[j], fmaf(ratio_m, ua[q].x[j], rp[q].x[j]));
-          if (e < nbulk) {  // aligned: 16-byte stores
-            Elem<float>::template store4<kStream>(gp + e, rp[q], pol);
-            Elem<float>::template store4<kStream>(gm + e, rm[q], pol);
-            Elem<float>::template store4<kStream>(gv + e, rv[q], pol);
-            if (gout) put_out4(gout + e, rp[q]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < kVec; ++j)
-              if (e + j < n) {
-                gp[e + j] = rp[q].x[j];
-                gm[e + j] = rm[q].x[j];
-                gv[e + j] = rv[q].x[j];
-                if (gout) put_out1(gout + e + j, rp[q].x[j]);
-              }
-          }
-        }
-      } else {
-        publishes = true;
-#pragma unroll
-        for (int q = 0; q < kBVecs; ++q) {
-          const int e = q * (kGroupThreads * kVec) + gtid * kVec;
-#pragma unroll
-          for (int j = 0; j < kVec; ++j) {
-            acc0 = fmaf(rp[q].x[j], rp[q].x[j], acc0);
-            acc1 = fmaf(ua[q].x[j], ua[q].x[j], acc1);
-            acc2 = fmaf(ub[q].x[j], ub[q].x[j], acc2);
-          }
-          if (op == kOpBP) {  // m and v are final
-            if (e < nbulk) {
-              Elem<float>::template store4<kStream>(gm + e, rm[q], pol);
-              Elem<float>::template store4<kStream>(gv + e, rv[q], pol);
-            } else {
-#pragma unroll
-              for (int j = 0; j < kVec; ++j)
-                if (e + j < n) {
-                  gm[e + j] = rm[q].x[j];
-                  gv[e + j] = rv[q].x[j];
-                }
-            }
-          }
-        }
-        if (op == kOpBP) {
-          // p, update_m and update_g wait in tensor memory for the norms
-          park_store(in_tmem, taddr, scell, gtid, rp, ua, ub);
-          if (in_tmem) tmem_wait_st();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar_cell + 8 * cell);
         }
       }
     }
@@ -1465,18 +1470,24 @@ int lans_grid(int sm_count, int max_blocks) {
   return g < 1 ? 1 : g;
 }
 
-template <typename GT, typename OT>
-static int launch_lans_t(int device, int grid, const LansParams& P, cudaStream_t s) {
+template <typename GT, typename OT, bool FUSED>
+static int launch_lans_f(int device, int grid, const LansParams& P, cudaStream_t s) {
   static bool configured[64] = {false};
   const int dev = (device >= 0 && device < 64) ? device : 0;
   const int smem = LansGeo<GT>::kTotal;
   if (!configured[dev]) {
-    RAFB200_CUDA(cudaFuncSetAttribute(lans_kernel<GT, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    RAFB200_CUDA(cudaFuncSetAttribute(lans_kernel<GT, OT, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured[dev] = true;
   }
-  lans_kernel<GT, OT><<<(unsigned)grid, kLansThreads, smem, s>>>(P);
+  lans_kernel<GT, OT, FUSED><<<(unsigned)grid, kLansThreads, smem, s>>>(P);
   RAFB200_CUDA(cudaGetLastError());
   return RAFB200_OK;
+}
+
+template <typename GT, typename OT>
+static int launch_lans_t(int device, int grid, const LansParams& P, cudaStream_t s) {
+  if (P.fuse_rs || P.fuse_ag) return launch_lans_f<GT, OT, true>(device, grid, P, s);
+  return launch_lans_f<GT, OT, false>(device, grid, P, s);
 }
 
 template <typename GT>
