@@ -100,6 +100,28 @@ RAFB200_API int rafb200_tensor_list_tune(rafb200_tensor_list_t list, int64_t lea
  * then reports RAFB200_DEVICE_WAIT_EXPIRED.  The reference has no in-kernel
  * waits: its passes are separate launches. */
 RAFB200_API int rafb200_tensor_list_set_wait_limit(rafb200_tensor_list_t list, int limit_ms);
+/* The collectives inside the update kernels, for a caller that manages symmetric memory
+ * and the cross-rank barriers itself (rafb200_zero_set_fused does both for the ZeRO step; no
+ * counterpart in the reference).  After this call rafb200_sgd_list / rafb200_adam /
+ * rafb200_lans on the list
+ *   - with reduce_scatter != 0 take the gradient of tensor i not from its bound `g` but as
+ *     the SUM over ranks of the bytes at g_offset_bytes[i] (a multiple of 16; the tensor's
+ *     region zero-padded to 16 bytes) inside the symmetric gradient buffer - through g_mc
+ *     (multimem.ld_reduce) when it is not NULL, else rank by rank from g_peer[0..world) in
+ *     a fixed order, fp32 accumulation, one rounding to the gradient dtype - and WRITE that
+ *     sum to the bound `g` (16-byte aligned, padded likewise); LANS needs normalize_grad
+ *     for this (its gradient-norm pass is what reads the gradients);
+ *   - with all_gather != 0 store the model-dtype copy, whose bound `out` must lie inside
+ *     p_peer[rank], at the same offset into every rank's buffer: through p_mc
+ *     (multimem.st) when it is not NULL, else one store per rank.
+ * The caller orders the ranks: every rank's gradients are in place before any rank
+ * launches, and nobody reads the parameter buffers before every rank's kernel is done.
+ * world <= 16.  Takes effect with the next rafb200_tensor_list_bind. */
+RAFB200_API int rafb200_tensor_list_set_symmetric(rafb200_tensor_list_t list, int world, int rank,
+                                                  const void* const* g_peer, const void* g_mc,
+                                                  void* const* p_peer, void* p_mc,
+                                                  const int64_t* g_offset_bytes, int reduce_scatter,
+                                                  int all_gather);
 /* Replaces the work-item table of the LANS kernel for this list by the caller's
  * (same encoding as rafb200_lans_schedule; used with and without gradient
  * normalisation), for experiments with other orders.  The caller is responsible

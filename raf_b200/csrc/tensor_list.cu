@@ -212,6 +212,31 @@ int rafb200_tensor_list_destroy(rafb200_tensor_list_t l) {
   return RAFB200_OK;
 }
 
+int rafb200_tensor_list_set_symmetric(rafb200_tensor_list_t l, int world, int rank, const void* const* g_peer,
+                                      const void* g_mc, void* const* p_peer, void* p_mc,
+                                      const int64_t* g_offset_bytes, int reduce_scatter, int all_gather) {
+  RAFB200_REQUIRE(l, "rafb200_tensor_list_set_symmetric: NULL list");
+  RAFB200_REQUIRE(world >= 1 && world <= kSymmMaxWorld && rank >= 0 && rank < world,
+                  "rafb200_tensor_list_set_symmetric: rank %d of %d (at most %d ranks)", rank, world, kSymmMaxWorld);
+  RAFB200_REQUIRE(!reduce_scatter || (g_peer && g_offset_bytes),
+                  "rafb200_tensor_list_set_symmetric: the gradient buffers and offsets are required");
+  RAFB200_REQUIRE(!all_gather || p_peer, "rafb200_tensor_list_set_symmetric: the parameter buffers are required");
+  LansFuse f;
+  f.world = world;
+  f.rank = rank;
+  f.fuse_rs = reduce_scatter ? 1 : 0;
+  f.fuse_ag = all_gather ? 1 : 0;
+  f.g_mc = static_cast<const char*>(g_mc);
+  f.p_mc = static_cast<char*>(p_mc);
+  for (int q = 0; q < world; ++q) {
+    if (g_peer) f.g_peer[q] = static_cast<const char*>(g_peer[q]);
+    if (p_peer) f.p_peer[q] = static_cast<char*>(p_peer[q]);
+    RAFB200_REQUIRE(!reduce_scatter || f.g_peer[q], "rafb200_tensor_list_set_symmetric: NULL gradient buffer of rank %d", q);
+    RAFB200_REQUIRE(!all_gather || f.p_peer[q], "rafb200_tensor_list_set_symmetric: NULL parameter buffer of rank %d", q);
+  }
+  return tensor_list_set_fuse(l, f, g_offset_bytes);
+}
+
 int64_t rafb200_tensor_list_total_elems(rafb200_tensor_list_t l) { return l ? l->total_elems : 0; }
 
 int rafb200_tensor_list_tune(rafb200_tensor_list_t l, int64_t lead_elems, int gap_items,

@@ -92,6 +92,18 @@ class TensorList:
         """Bound of every wait inside the LANS kernel (default 2 s)."""
         check(_lib.load().rafb200_tensor_list_set_wait_limit(self.handle, int(limit_ms)))
 
+    def set_symmetric(self, rank, g_peers, p_peers, g_offsets_bytes, g_mc=0, p_mc=0, reduce_scatter=True,
+                      all_gather=True):
+        """The collectives inside the update kernels (rafb200_tensor_list_set_symmetric):
+        ``g_peers`` / ``p_peers`` = every rank's gradient / parameter buffer as addressable here
+        (device addresses), ``g_offsets_bytes`` = each tensor's offset inside the gradient buffer."""
+        world = len(g_peers)
+        off = _lib.i64_array([int(x) for x in g_offsets_bytes])
+        check(_lib.load().rafb200_tensor_list_set_symmetric(
+            self.handle, world, int(rank), _lib.ptr_array([int(x) for x in g_peers]), int(g_mc) or None,
+            _lib.ptr_array([int(x) for x in p_peers]), int(p_mc) or None, off, int(bool(reduce_scatter)),
+            int(bool(all_gather))))
+
     def set_lans_items(self, items):
         """Replace the LANS work-item table: ``items`` is an (n, 2) uint32 array."""
         import numpy as np
