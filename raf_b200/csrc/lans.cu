@@ -307,14 +307,14 @@ constexpr int kParkWarp = kConsumerWarps + 2;    // 18: finishes parked chunks
 constexpr int kPubWarp = kConsumerWarps + 3;     // 19: adds partial sums to the tensors' accumulators
 constexpr int kLansThreads = (kConsumerWarps + 4) * 32;  // 640
 constexpr int kQueueDepth = 64;                  // > slots per group + parked cells + end marker
-constexpr int kRing = 64;                        // mailboxes: kMailboxes per slot
+constexpr int kMail = 64;                        // mailboxes of a block: kMailboxes per slot
 constexpr uint32_t kMbEmpty = 0, kMbFull = 1, kMbTaking = 2, kMbIdle = 3;
 constexpr uint32_t kSeqBits = 11, kSeqMask = (1u << kSeqBits) - 1u;  // see partition_lans_items
 constexpr int kBVecs = kLansElems / (kGroupThreads * kVec);  // 2 vectors per thread per chunk
 static_assert(kBVecs * kGroupThreads * kVec == kLansElems, "a chunk is whole passes of a group");
 
 // A resolved work item: everything a group needs to run it.  The same 64 bytes serve as
-// ring entry and as the description of what a slot currently holds.
+// mailbox entry and as the description of what a slot currently holds.
 struct __align__(16) SlotMeta {
   const void* g;  // global addresses of the item's first element (stores, unaligned fallback)
   float* p;
@@ -342,16 +342,11 @@ static_assert(sizeof(RedSlot) == 64, "RedSlot is 64 bytes");
 
 // Block-wide control words in shared memory.
 struct LansCtrl {
-  int avail;            // ring entries published and not yet claimed
-  uint32_t head;        // next ring entry to claim
-  uint32_t consumed;    // ring entries copied out (their ring slot may be rewritten)
   uint32_t done_items;  // items of this block that have finished
-  uint32_t cell_seq;    // parked items that were given a cell so far (they get theirs in list order)
   uint32_t mb_state[64]; // mailbox kMailboxes * slot + round % kMailboxes, see kMb*
-  uint32_t parked_mask; // slots whose chunk waits for its tensor's norms
   uint32_t tail[kGroups];
   uint32_t item_cnt[16], pub_cnt[16], op_cnt[16];  // per slot: parities of its barriers
-  uint32_t cell_free;    // tensor-memory cells nobody holds
+  uint32_t cell_free;    // cells nobody holds
   uint32_t cell_parked;  // cells whose chunk waits for its tensor's norms
   uint32_t tmem_base;    // address the allocation returned
   uint32_t cellop_cnt[32], cell_grp[32];  // per cell: parity of its barrier, group that parked it
@@ -379,12 +374,12 @@ struct LansGeo {
   // power of two) lanes = mailboxes
   static constexpr int kJBits = kSlots <= 8 ? 2 : 3;
   static constexpr uint32_t kMailboxes = 32u >> kJBits;
-  static_assert(kSlots <= 16 && kSlots * (int)kMailboxes <= kRing && kLansCells <= 31, "per-slot tables and masks");
+  static_assert(kSlots <= 16 && kSlots * (int)kMailboxes <= kMail && kLansCells <= 31, "per-slot tables and masks");
   static constexpr int kSmemCellBytes = 3 * kFBytes;  // p, update_m, update_g
   static constexpr int kSmemCellOff = kSlots * kSlotBytes;
   static constexpr int kMetaOff = kSmemCellOff + kLansSmemCells * kSmemCellBytes;
-  static constexpr int kRingOff = kMetaOff + kSlots * (int)sizeof(SlotMeta);
-  static constexpr int kRedOff = kRingOff + kRing * (int)sizeof(SlotMeta);
+  static constexpr int kMailOff = kMetaOff + kSlots * (int)sizeof(SlotMeta);
+  static constexpr int kRedOff = kMailOff + kMail * (int)sizeof(SlotMeta);
   static constexpr int kQueueOff = kRedOff + kSlots * (int)sizeof(RedSlot);
   static constexpr int kCellOff = kQueueOff + kGroups * kQueueDepth * 16;
   static constexpr int kCtrlOff = kCellOff + kLansCells * (int)sizeof(CellMeta);
@@ -408,7 +403,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
   constexpr int S = L::kSlots;
   constexpr uint32_t kMailboxes = L::kMailboxes;
   SlotMeta* s_meta = reinterpret_cast<SlotMeta*>(smem + L::kMetaOff);
-  SlotMeta* s_ring = reinterpret_cast<SlotMeta*>(smem + L::kRingOff);
+  SlotMeta* s_mail = reinterpret_cast<SlotMeta*>(smem + L::kMailOff);
   RedSlot* s_red = reinterpret_cast<RedSlot*>(smem + L::kRedOff);
   uint4* s_queue = reinterpret_cast<uint4*>(smem + L::kQueueOff);
   LansCtrl* ctrl = reinterpret_cast<LansCtrl*>(smem + L::kCtrlOff);
@@ -481,7 +476,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
   // Starts the item in mailbox `h` of slot `slot`: copies it into the slot's description,
   // issues the bulk copies and queues the item's first operation.  Called by a single thread.
   auto start_from_mailbox = [&](uint32_t slot, uint32_t h) {
-    const uint4* src = reinterpret_cast<const uint4*>(&s_ring[kMailboxes * slot + h]);
+    const uint4* src = reinterpret_cast<const uint4*>(&s_mail[kMailboxes * slot + h]);
     uint4* dst = reinterpret_cast<uint4*>(&s_meta[slot]);
     const uint4 e0 = src[0], e1 = src[1], e2 = src[2], e3 = src[3];
     dst[0] = e0;
@@ -681,7 +676,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
           const bool through_switch = FUSED && kind == kKindA && P.fuse_rs != 0;
           const int nbulk = ((flags & kFlagBulk) && !through_switch) ? (n / gran) * gran : 0;
           const uint32_t op = kind == kKindA ? kOpA : kind == kKindBs ? kOpB : kind == kKindCs ? kOpC : kOpBP;
-          SlotMeta& mt = s_ring[mb];
+          SlotMeta& mt = s_mail[mb];
           mt.g = dg + start * (int64_t)sizeof(GT);
           // an A item that reads through the switch gets the byte offset of its chunk inside the
           // symmetric gradient buffer instead of p, which it does not use
@@ -735,9 +730,8 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
 
   if (warp == kParkWarp) {
     // ================================= parker =================================
-    // Lane c looks after tensor-memory cell c: queues the second half of the chunk parked
-    // there when the tensor's norms are final.  Lane s < S also refills slot s when it ran
-    // empty while the ring had nothing to offer.
+    // Lane c looks after cell c: queues the second half of the chunk parked there when the
+    // tensor's norms are final.
     const bool active = lane < S;
     const uint32_t bit = 1u << lane;
     uint64_t t_parked = 0;
@@ -873,7 +867,7 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
   // q*512 + 4*gtid: 16-byte shared-memory accesses without bank conflicts, coalesced
   // 16-byte stores.  Lanes past the end of a ragged chunk hold zeros, which add nothing
   // to any sum.  One warp of the group (they take turns) also turns the slot over when an
-  // item's last operation is done: it starts the next item of the ring in it right away.
+  // item's last operation is done: it starts the slot's next item from its mailbox right away.
   const int grp = warp >> 2, wig = warp & 3, gtid = tid & (kGroupThreads - 1);
   Policies pol;
   pol.init();
@@ -1241,8 +1235,8 @@ __global__ void __launch_bounds__(kLansThreads, 1) lans_kernel(const LansParams 
           atomicOr(&ctrl->cell_free, 1u << cell);
           atomicAdd(&ctrl->done_items, 1u);
         } else if (ok) {
-          // The other three warps have let go of the slot too: the next item of the ring
-          // starts in it; with the ring empty the parker takes over.
+          // The other three warps have let go of the slot too: its next item starts in it, or
+          // the slot is marked idle and the prefetcher starts the item when it has one.
           if (op != kOpBP) atomicAdd(&ctrl->done_items, 1u);
           take_next(slot);
           if (op == kOpBP) {
