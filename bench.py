@@ -489,7 +489,7 @@ def main():
                          "pointers) or NCCL; auto = peer at N = 2, multicast from N = 4, NCCL if symmetric "
                          "memory cannot be set up")
     ap.add_argument("--comm-blocks", type=int, default=0, help="thread blocks per collective kernel")
-    ap.add_argument("--fused", type=int, default=-1, choices=[-1, 0, 1, 2],
+    ap.add_argument("--fused", type=int, default=-1, choices=[-1, 0, 1, 2, 3],
                     help="LANS at N > 1: collectives inside the update kernel (1 reduce-scatter, 2 all-gather "
                          "too, 0 the bucketed pipeline of separate kernels; -1 = the default for N)")
     ap.add_argument("--no-views", action="store_true",
@@ -589,6 +589,11 @@ def main():
         # LANS: the collectives inside the update kernel (measured 2.12 / 1.69 ms at 2 / 4 GPUs
         # against 2.25 / 2.17 ms for the bucketed pipeline of separate kernels)
         args.fused = 2 if (world > 1 and args.stages is False) else 0
+        if args.fused and world == 2 and wl["optimizer"] == "lans":
+            # two ranks: the gradients through the switch, the copies as peer stores (1.97 ms
+            # against 2.10 ms with both through the switch, which there also carries the rank's
+            # own half of every multicast)
+            args.fused = 3
     if args.collectives == "auto":
         # separate kernels on two ranks: plain peer loads / stores beat the switch-side
         # reduction (2.25 ms against 2.47 ms); inside the update kernel, and from four ranks on,
@@ -839,7 +844,7 @@ def main():
                        "elements": total, "shard_elements_per_rank": shard_elems,
                        "bucket_elems": wl["bucket_elems"], "buckets": plan.num_buckets if world > 1 else 1,
                        "gradient_sets": nsets, "collectives": collectives_used,
-                       "collectives_inside_update_kernel": (["no", "reduce-scatter", "reduce-scatter and all-gather"][args.fused]
+                       "collectives_inside_update_kernel": (["no", "reduce-scatter", "reduce-scatter and all-gather", "reduce-scatter and all-gather (peer stores)"][args.fused]
                                                             if world > 1 and args.collectives != "nccl" else "no"),
                        "tensors_inside_symmetric_buffer": views_used,
                        "l2": (f"inputs larger than L2 ({wl['bytes_per_elem'] * shard_elems >> 20} MiB touched per step per rank)"

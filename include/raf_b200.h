@@ -584,7 +584,9 @@ RAFB200_API int rafb200_zero_step(rafb200_zero_t zero, const rafb200_hyper* hype
  * kernels.  SGD and Adam do the same in their single pass (mode 1: the gradient is read as
  * the sum over ranks; mode 2: the copy is stored everywhere too).  LANS needs normalize_grad
  * (the gradient-norm pass is what reads the gradients); a LANS step without it, and every step
- * of the host-buffer form, takes the bucketed pipeline.  Call after rafb200_zero_attach_symmetric and
+ * of the host-buffer form, takes the bucketed pipeline.  mode 3 = mode 2 with the copies going
+ * out as one store per peer even when a multicast address exists (the better choice on two
+ * ranks, where the switch would also carry the rank's own half).  Call after rafb200_zero_attach_symmetric and
  * before rafb200_zero_bind, with the same mode on every rank.
  */
 RAFB200_API int rafb200_zero_set_fused(rafb200_zero_t zero, int mode);

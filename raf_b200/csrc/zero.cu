@@ -185,7 +185,7 @@ struct rafb200_zero_s {
   int kernels_per_step = 0, collectives_per_step = 0;
   // The collectives inside the update kernel (rafb200_zero_set_fused): one list over
   // all tensors, one launch per step, two cross-GPU barriers per step instead of two per bucket
-  int fused = 0;  // 0 off, 1 reduce-scatter inside the kernel, 2 all-gather too
+  int fused = 0;  // 0 off, 1 reduce-scatter inside the kernel, 2 all-gather too, 3 = 2 with peer stores
   rafb200_tensor_list_t fused_list = nullptr;
   void* fused_ws = nullptr;
   size_t fused_ws_bytes = 0;
@@ -571,7 +571,7 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
     f.fuse_rs = 1;
     f.fuse_ag = z->fused >= 2 ? 1 : 0;
     f.g_mc = static_cast<const char*>(z->g_mc);
-    f.p_mc = static_cast<char*>(z->p_mc);
+    f.p_mc = z->fused == 3 ? nullptr : static_cast<char*>(z->p_mc);  // 3: the copies go out as peer stores
     for (int q = 0; q < z->n; ++q) {
       f.g_peer[q] = static_cast<const char*>(z->g_peers.ptr[q]);
       f.p_peer[q] = static_cast<char*>(z->p_peers.ptr[q]);
@@ -593,7 +593,7 @@ int rafb200_zero_bind(rafb200_zero_t z, void* const* grads, void* const* params,
 }
 
 int rafb200_zero_set_fused(rafb200_zero_t z, int mode) {
-  RAFB200_REQUIRE(z && mode >= 0 && mode <= 2, "rafb200_zero_set_fused: mode must be 0, 1 or 2");
+  RAFB200_REQUIRE(z && mode >= 0 && mode <= 3, "rafb200_zero_set_fused: mode must be 0 .. 3");
   RAFB200_REQUIRE(mode == 0 || z->symmetric, "rafb200_zero_set_fused: attach symmetric memory first");
   RAFB200_REQUIRE(!z->bound, "rafb200_zero_set_fused: call before rafb200_zero_bind");
   z->fused = mode;

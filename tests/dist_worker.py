@@ -129,9 +129,10 @@ def check_collectives(comm):
 # parameters that live inside the symmetric buffer (no pack and unpack copies) - these three on
 # memory from rafb200_symm_alloc - / own kernels with multicast on memory from
 # torch.distributed._symmetric_memory / LANS with the collectives inside the update kernel:
-# reduce-scatter only, both with multicast, both with peer loads and stores
-MODES = ["nccl", "multimem", "peer", "view", "torch", "fusedrs", "fusedm", "fusedp"]
-FUSED = {"fusedrs": 1, "fusedm": 2, "fusedp": 2}  # the collectives inside the update kernel
+# reduce-scatter only, both with multicast, both with peer loads and stores, reduction through
+# the switch with peer stores
+MODES = ["nccl", "multimem", "peer", "view", "torch", "fusedrs", "fusedm", "fusedp", "fusedx"]
+FUSED = {"fusedrs": 1, "fusedm": 2, "fusedp": 2, "fusedx": 3}  # the collectives inside the update kernel
 # ... and each of them again with all steps queued back to back: no host synchronisation and no
 # status read between steps, so the values also cover the ordering ACROSS steps (the fence at the
 # start of a step, barrier epochs, the all-gather of step s overlapping the reduce-scatter of
