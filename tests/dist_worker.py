@@ -152,7 +152,7 @@ def run_zero(comm, out_dir, tag):
             z.attach_symmetric(multicast=(mode not in ("peer", "fusedp")),
                                allocator="torch" if mode == "torch" else "library")
             if mode not in ("peer", "fusedp"):
-                assert z.multicast, "no multicast address on this box"
+                assert z.multicast, "no multicast address available"
             if mode in FUSED:
                 z.set_fused(FUSED[mode])
             if mode == "view" or mode in FUSED:
