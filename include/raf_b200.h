@@ -221,6 +221,18 @@ RAFB200_API int rafb200_lans(rafb200_tensor_list_t list, int step, const float* 
 RAFB200_API int rafb200_lans_schedule(int k, const int64_t* numel, int g_dtype, int with_norm_phase,
                                       int cells_total, int64_t lead_elems, int gap_items,
                                       uint32_t* items, size_t capacity, size_t* count);
+/* How that order is dealt out to a persistent grid of `grid` blocks (host only; for
+ * inspection and tests): block b runs two lists, 2b (its even slots) and 2b + 1 (its odd
+ * slots); list h = items[offsets[h] .. offsets[h + 1]) in the encoding above, where the
+ * second word of a kind-3 item also carries, in its top 11 bits, the item's running number
+ * among the kind-3 items of its list (cells are granted by these numbers).  offsets has
+ * 2 * grid + 1 entries.  cells_even / cells_odd = the cells a block's even / odd list may
+ * use: a list never holds more kind-3 items of one tensor than that, which is what makes
+ * the kernel's waits for cells deadlock-free.  items / offsets may be NULL. */
+RAFB200_API int rafb200_lans_partition(int k, const int64_t* numel, int g_dtype, int with_norm_phase,
+                                       int grid, int64_t lead_elems, int gap_items, uint32_t* offsets,
+                                       uint32_t* items, size_t capacity, size_t* count,
+                                       int* cells_even, int* cells_odd);
 /* Synchronises `stream`, then reports whether the last rafb200_lans on this
  * workspace completed (RAFB200_OK) or a bounded device wait expired.
  * norms_host (optional, 4*k floats, tensor-major) receives

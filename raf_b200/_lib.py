@@ -56,6 +56,7 @@ SIGNATURES = {
     "rafb200_lans_schedule": (_i, [_i, _vp, _i, _i, _i, _i64, _i, _vp, _sz, _P(_sz)]),
     "rafb200_tensor_list_set_wait_limit": (_i, [_vp, _i]),
     "rafb200_tensor_list_set_lans_items": (_i, [_vp, _vp, _sz]),
+    "rafb200_lans_partition": (_i, [_i, _vp, _i, _i, _i, _i64, _i, _vp, _vp, _sz, _P(_sz), _P(_i), _P(_i)]),
     "rafb200_tensor_list_set_symmetric": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i]),
     "rafb200_lans_status": (_i, [_vp, _vp, _vp, _vp]),
     "rafb200_lans_tensor_static": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i, _i64, _i, _f, _f, _f, _f,

@@ -1705,6 +1705,35 @@ int rafb200_lans_schedule(int k, const int64_t* numel, int g_dtype, int with_nor
   return RAFB200_OK;
 }
 
+int rafb200_lans_partition(int k, const int64_t* numel, int g_dtype, int with_norm_phase, int grid,
+                           int64_t lead_elems, int gap_items, uint32_t* offsets, uint32_t* items,
+                           size_t capacity, size_t* count, int* cells_even, int* cells_odd) {
+  RAFB200_REQUIRE(k >= 0 && (k == 0 || numel) && count && grid >= 1 && lead_elems >= 0 && gap_items >= 0 &&
+                      dtype_valid(g_dtype),
+                  "rafb200_lans_partition: bad arguments");
+  std::vector<int64_t> n(k);
+  for (int i = 0; i < k; ++i) {
+    RAFB200_REQUIRE(numel[i] >= 0, "rafb200_lans_partition: numel[%d] < 0", i);
+    n[i] = numel[i];
+  }
+  const int64_t cells_total = (int64_t)grid * kLansCells;
+  const std::vector<Item> sched =
+      build_lans_schedule(n, lans_a_elems(g_dtype), with_norm_phase != 0, lans_park_cap(cells_total), lead_elems,
+                          gap_items > 0 ? gap_items : (int64_t)grid * lans_slots(g_dtype));
+  const std::vector<uint32_t> table = partition_lans_items(sched, grid, lans_slots(g_dtype));
+  const size_t head = (2 * (size_t)grid + 1 + 1) & ~(size_t)1;
+  *count = sched.size();
+  if (cells_even) *cells_even = (kLansCells + 1) / 2;
+  if (cells_odd) *cells_odd = kLansCells - (kLansCells + 1) / 2;
+  if (offsets)
+    for (int h = 0; h <= 2 * grid; ++h) offsets[h] = table[(size_t)h];
+  if (items) {
+    RAFB200_REQUIRE(capacity >= sched.size(), "rafb200_lans_partition: %zu items, room for %zu", sched.size(), capacity);
+    for (size_t i = 0; i < 2 * sched.size(); ++i) items[i] = table[head + i];
+  }
+  return RAFB200_OK;
+}
+
 int rafb200_lans_status(rafb200_tensor_list_t list, const void* workspace, float* norms_host,
                         void* stream) {
   RAFB200_REQUIRE(list && workspace, "rafb200_lans_status: NULL argument");

@@ -101,3 +101,72 @@ def test_schedule_rejects_bad_arguments():
     # 3 gradient-norm items of 4096 + 10 chunks of 1024, 6 of them parked, 4 streamed twice
     assert lib.rafb200_lans_schedule(1, one, 0, 1, 10, 0, 0, small, 1, C.byref(count)) == 1
     assert count.value == 3 + 10 + 4
+
+
+GAP = 1000  # the same distance between a tensor's stage-1 and update items in both calls
+
+
+def partition(numels, g_dtype, with_norm, grid):
+    from raf_b200 import _lib
+
+    lib = _lib.load()
+    arr = (C.c_int64 * len(numels))(*numels)
+    count, ce, co = C.c_size_t(), C.c_int(), C.c_int()
+    _lib.check(lib.rafb200_lans_partition(len(numels), arr, g_dtype, int(with_norm), grid, 8 << 20, GAP, None, None, 0,
+                                          C.byref(count), C.byref(ce), C.byref(co)))
+    off = np.zeros(2 * grid + 1, np.uint32)
+    items = np.zeros((count.value, 2), np.uint32)
+    _lib.check(lib.rafb200_lans_partition(len(numels), arr, g_dtype, int(with_norm), grid, 8 << 20, GAP,
+                                          off.ctypes.data, items.ctypes.data, count.value, C.byref(count),
+                                          C.byref(ce), C.byref(co)))
+    return off, items, ce.value, co.value
+
+
+def check_partition(numels, g_dtype, with_norm, grid):
+    """What the kernel's waits for cells rely on: every item in exactly one list, every list in
+    the global order, the parked items of a list numbered 0, 1, 2, ... and never more of one
+    tensor in a list than the list has cells."""
+    off, items, cells_even, cells_odd = partition(numels, g_dtype, with_norm, grid)
+    kind, tensor, chunk = schedule(numels, g_dtype, with_norm, grid * (cells_even + cells_odd), 8 << 20, GAP)
+    order = {key: pos for pos, key in enumerate(zip(kind.tolist(), tensor.tolist(), chunk.tolist()))}
+    assert off[0] == 0 and off[-1] == len(order) and np.all(np.diff(off.astype(np.int64)) >= 0)
+    seen = set()
+    sizes = []
+    for h in range(2 * grid):
+        rows = items[off[h]:off[h + 1]]
+        k = (rows[:, 0] >> 30).tolist()
+        t = (rows[:, 0] & ((1 << 30) - 1)).tolist()
+        c = (rows[:, 1] & ((1 << 21) - 1)).tolist()
+        seq = (rows[:, 1] >> 21).tolist()
+        pos = [order[key] for key in zip(k, t, c)]
+        assert pos == sorted(pos), "a list does not keep the global order"
+        seen.update(zip(k, t, c))
+        parked = [i for i, kk in enumerate(k) if kk == KIND_BCP]
+        assert [seq[i] for i in parked] == [j % 2048 for j in range(len(parked))]
+        assert all(seq[i] == 0 for i, kk in enumerate(k) if kk != KIND_BCP)
+        per_tensor = {}
+        for i in parked:
+            per_tensor[t[i]] = per_tensor.get(t[i], 0) + 1
+        limit = cells_even if h % 2 == 0 else cells_odd
+        assert not per_tensor or max(per_tensor.values()) <= limit, (h, max(per_tensor.values()), limit)
+        sizes.append(len(k))
+    assert len(seen) == len(order)
+    return sizes
+
+
+def test_partition_of_the_benchmark_shapes():
+    from bench import bert_large_shapes, gpt2_medium_shapes, numel
+
+    for shapes, g_dtype in ((bert_large_shapes(), 1), (gpt2_medium_shapes(), 2)):
+        for world in (1, 8):
+            numels = [-(-s[0] // world) * (numel(s) // s[0]) for s in shapes]
+            sizes = check_partition(numels, g_dtype, True, 148)
+            even, odd = sizes[0::2], sizes[1::2]
+            assert max(even) - min(even) <= 2 + len(numels) // 50 and max(odd) - min(odd) <= 2 + len(numels) // 50
+
+
+@settings(max_examples=25, deadline=None)
+@given(st.lists(st.one_of(st.integers(0, 5), st.integers(0, 70000), st.integers(0, 600_000)), min_size=0, max_size=8),
+       st.sampled_from([0, 1, 2]), st.booleans(), st.sampled_from([1, 2, 7, 148]))
+def test_partition_invariants_random_lists(numels, g_dtype, with_norm, grid):
+    check_partition(numels, g_dtype, with_norm, grid)
